@@ -1,0 +1,177 @@
+// Paged key/value cache: writing a step's keys and values into pages, and a general
+// attention kernel over the pages (any head size up to 256, any page size, query heads
+// grouped over fewer key/value heads, optional window), in 32-bit arithmetic for both
+// storage types.  It is the whole attention of the 32-bit path and the fallback of the
+// bfloat16 path for head sizes the tensor-core kernels do not take.
+//
+// Cache of one layer: K and V each [num_pages][n_kv_head][page_size][head_dim]; the
+// reference keeps [page][page_size][head][head_dim] (kernels/attention.cu:14,80).
+#include "common.cuh"
+#include <math.h>
+
+namespace cbis {
+
+// Row r of the step's projections goes to token slot slot_mapping[r] = page*page_size + offset
+// (reference: scatter_kv_kernel, kernels/attention.cu:7-19).  A negative slot writes nothing.
+template <typename TT>
+__global__ void kv_write_kernel(const TT* __restrict__ qkv, int ld, int k_off, int v_off, TT* __restrict__ kc,
+                                TT* __restrict__ vc, const int* __restrict__ slot_mapping, int n_kv_head,
+                                int hd, int ps) {
+  const int r = blockIdx.x;
+  const int slot = slot_mapping[r];
+  if (slot < 0) return;
+  const int page = slot / ps, off = slot % ps;
+  const TT* krow = qkv + (size_t)r * ld + k_off;
+  const TT* vrow = qkv + (size_t)r * ld + v_off;
+  const int width = n_kv_head * hd;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const int h = c / hd, i = c % hd;
+    const size_t dst = (((size_t)page * n_kv_head + h) * ps + off) * hd + i;
+    kc[dst] = krow[c];
+    vc[dst] = vrow[c];
+  }
+}
+
+// One warp per (row, query head).  The query at position p sees keys max(0, p-window+1)..p
+// (window 0: all keys 0..p; the loop bound is the causal mask, kernels/attention.cu:67-68,78).
+// Online softmax with running max m, normaliser l and accumulator acc as in
+// kernels/attention.cu:74-95, four keys at a time.  Lane i owns head dims i, i+32, ...
+template <typename TT, int NPER>
+__global__ void paged_attention_generic_kernel(
+    const TT* __restrict__ q, int q_ld, const TT* __restrict__ kc, const TT* __restrict__ vc,
+    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq,
+    const int* __restrict__ positions, TT* __restrict__ out, int out_ld, int n_rows, int n_head, int n_kv_head,
+    int hd, int ps, float scale, int window) {
+  const int lane = threadIdx.x & 31;
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n_rows * n_head) return;
+  const int row = w / n_head, h = w % n_head;
+  const int hk = h / (n_head / n_kv_head);
+  const int pos = positions[row];
+  const int* bt = block_table + (size_t)row_seq[row] * max_blocks;
+  const int kend = pos + 1;
+  const int kstart = window > 0 ? max(0, kend - window) : 0;
+
+  float qv[NPER], acc[NPER];
+#pragma unroll
+  for (int i = 0; i < NPER; ++i) {
+    const int dim = lane + 32 * i;
+    qv[i] = dim < hd ? to_f32(q[(size_t)row * q_ld + h * hd + dim]) : 0.f;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+
+  for (int j0 = kstart; j0 < kend; j0 += 4) {
+    float s[4];
+    const TT* vptr[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      float part = 0.f;
+      vptr[u] = nullptr;
+      if (j < kend) {
+        const int page = bt[j / ps];
+        const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j % ps)) * hd;
+        const TT* kp = kc + base;
+        vptr[u] = vc + base;
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+          const int dim = lane + 32 * i;
+          if (dim < hd) part = fmaf(qv[i], to_f32(kp[dim]), part);
+        }
+      }
+      s[u] = part;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s[u] = (j0 + u < kend) ? warp_sum(s[u]) * scale : -INFINITY;
+    const float m_new = fmaxf(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])), m);
+    const float corr = expf(m - m_new);  // first group: exp(-inf) = 0
+    float p[4];
+    float psum = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      p[u] = (j0 + u < kend) ? expf(s[u] - m_new) : 0.f;
+      psum += p[u];
+    }
+    l = l * corr + psum;
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int dim = lane + 32 * i;
+      float a = acc[i] * corr;
+      if (dim < hd) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (vptr[u]) a = fmaf(p[u], to_f32(vptr[u][dim]), a);
+      }
+      acc[i] = a;
+    }
+    m = m_new;
+  }
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int i = 0; i < NPER; ++i) {
+    const int dim = lane + 32 * i;
+    if (dim < hd) from_f32(out[(size_t)row * out_ld + h * hd + dim], acc[i] * inv);
+  }
+}
+
+}  // namespace cbis
+
+using namespace cbis;
+
+CBIS_EXPORT int cbis_kv_write(const void* qkv, int ld, int k_off, int v_off, void* kc, void* vc,
+                              const int* slot_mapping, int T, int n_kv_head, int hd, int ps, int dtype,
+                              void* stream) {
+  if (T <= 0) return CBIS_OK;
+  if (n_kv_head <= 0 || hd <= 0 || ps <= 0) return CBIS_ERR_BAD_SIZE;
+  const int width = n_kv_head * hd;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == CBIS_F32)
+    kv_write_kernel<float><<<T, threads, 0, st>>>((const float*)qkv, ld, k_off, v_off, (float*)kc, (float*)vc,
+                                                  slot_mapping, n_kv_head, hd, ps);
+  else if (dtype == CBIS_BF16)
+    kv_write_kernel<__nv_bfloat16><<<T, threads, 0, st>>>((const __nv_bfloat16*)qkv, ld, k_off, v_off,
+                                                          (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping,
+                                                          n_kv_head, hd, ps);
+  else
+    return CBIS_ERR_BAD_DTYPE;
+  return (int)cudaGetLastError();
+}
+
+template <typename TT>
+static int launch_generic(const void* q, int q_ld, const void* kc, const void* vc, const int* block_table,
+                          int max_blocks, const int* row_seq, const int* positions, void* out, int out_ld,
+                          int n_rows, int n_head, int n_kv_head, int hd, int ps, float scale, int window,
+                          cudaStream_t st) {
+  const int warps = 4;
+  const long long total = (long long)n_rows * n_head;
+  const int blocks = (int)((total + warps - 1) / warps);
+#define CBIS_LAUNCH(NPER)                                                                                      \
+  paged_attention_generic_kernel<TT, NPER><<<blocks, warps * 32, 0, st>>>(                                     \
+      (const TT*)q, q_ld, (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, \
+      out_ld, n_rows, n_head, n_kv_head, hd, ps, scale, window)
+  if (hd <= 32) CBIS_LAUNCH(1);
+  else if (hd <= 64) CBIS_LAUNCH(2);
+  else if (hd <= 128) CBIS_LAUNCH(4);
+  else CBIS_LAUNCH(8);
+#undef CBIS_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+CBIS_EXPORT int cbis_paged_attention_generic(const void* q, int q_ld, const void* kc, const void* vc,
+                                             const int* block_table, int max_blocks, const int* row_seq,
+                                             const int* positions, void* out, int out_ld, int n_rows, int n_head,
+                                             int n_kv_head, int hd, int ps, float scale, int window, int dtype,
+                                             void* stream) {
+  if (n_rows <= 0) return CBIS_OK;
+  if (hd <= 0 || hd > 256 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head) return CBIS_ERR_BAD_SIZE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == CBIS_F32)
+    return launch_generic<float>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld, n_rows,
+                                 n_head, n_kv_head, hd, ps, scale, window, st);
+  if (dtype == CBIS_BF16)
+    return launch_generic<__nv_bfloat16>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld,
+                                         n_rows, n_head, n_kv_head, hd, ps, scale, window, st);
+  return CBIS_ERR_BAD_DTYPE;
+}

@@ -1,0 +1,71 @@
+// Next-token choice on the device: greedy argmax (first maximum wins, as the host scan of
+// the reference does, src/server_demo.cpp:70-74) and temperature sampling by the Gumbel-max
+// rule, argmax_i(logit_i / temperature + g_i), g_i = -log(-log u_i).  u_i comes from a counter
+// generator keyed per (request, output index) by the host, so a draw depends neither on the
+// batch nor on how the prompt was cut.
+#include "common.cuh"
+#include <math.h>
+
+namespace cbis {
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
+                              const unsigned long long* __restrict__ keys, int* __restrict__ out, int V) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * ld;
+  const float temp = temperature ? temperature[r] : 0.f;
+  const unsigned long long key = keys ? keys[r] : 0ull;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = row[i];
+    if (temp > 0.f) {
+      const unsigned long long z = mix64(key + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull);
+      const float u = ((float)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);  // (0,1), exact in 24 bits
+      v = v / temp - logf(-logf(u));
+    }
+    if (v != v) v = -INFINITY;  // NaN never wins over a number
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if (lane == 0) { sval[warp] = best; sidx[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < nwarp ? sval[lane] : -INFINITY;
+    bi = lane < nwarp ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) out[r] = bi < V ? bi : 0;
+  }
+}
+
+}  // namespace cbis
+
+using namespace cbis;
+
+// logits [R, ld >= V] 32-bit; temperature[R] (<= 0: greedy) and keys[R] may be null (greedy).
+CBIS_EXPORT int cbis_sample(const float* logits, int ld, const float* temperature, const unsigned long long* keys,
+                            int* out, int R, int V, void* stream) {
+  if (R <= 0) return CBIS_OK;
+  if (V <= 0 || ld < V) return CBIS_ERR_BAD_SIZE;
+  const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
+  sample_kernel<<<R, threads, 0, (cudaStream_t)stream>>>(logits, ld, temperature, keys, out, V);
+  return (int)cudaGetLastError();
+}

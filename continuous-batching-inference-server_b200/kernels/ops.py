@@ -1,0 +1,175 @@
+"""Python faces of the CUDA kernels: argument checks, then a ctypes call on the current stream.
+
+Every function works on CUDA tensors only and raises if the kernel library is missing;
+nothing here falls back to torch operators.  The dense matrix products of the bfloat16
+path go to the library GEMM (cuBLASLt through ``torch``), as the reference's go to
+``cublasSgemm`` (kernels/linear.cu:25-27); everything around them is this package's own.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from .library import kernels
+
+F32, BF16 = 0, 1
+ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
+
+_STATUS = {-1: "unsupported dtype", -2: "a size that the kernel does not take",
+           -3: "misaligned pointer or stride", -4: "size too large for this kernel"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(status: int, what: str, detail: str = "") -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, 'error %d' % status)}{(' (' + detail + ')') if detail else ''}")
+    raise KernelError(f"{what}: CUDA error {status} at launch {detail}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is not supported (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels take CUDA tensors only; there is no CPU path")
+
+
+def embed_pos_add(tokens, positions, wte, wpe, out, err):
+    """out[r] = wte[tokens[r]] + wpe[positions[r]] in 32-bit; err (int32[1]) is set on a bad index."""
+    _need_cuda(tokens, positions, wte, wpe, out, err)
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and wte.is_contiguous()
+    assert tokens.dtype == torch.int32 and positions.dtype == torch.int32
+    st = kernels().cbis_embed_pos_add(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out),
+                                      c_int(T), c_int(d), c_int(wte.shape[0]),
+                                      c_int(wpe.shape[0] if wpe is not None else 0),
+                                      c_int(dtype_code(wte.dtype)), _ptr(err), _stream())
+    _check(st, "embed_pos_add", f"T={T} d={d}")
+
+
+def add_layernorm(x, delta, delta_bias, gamma, beta, eps, out, rows=None):
+    """x += delta + delta_bias (32-bit, in place unless ``rows``); out = LayerNorm(x) * gamma + beta.
+
+    ``rows`` (int32[R]) selects source rows: out[r] = LN(x[rows[r]] + ...), x is left as it is."""
+    _need_cuda(x, delta, delta_bias, gamma, beta, out, rows)
+    d = x.shape[-1]
+    R = rows.shape[0] if rows is not None else x.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == d
+    assert gamma.dtype == torch.float32 and beta.dtype == torch.float32
+    assert delta is None or (delta.is_contiguous() and delta.shape == x.shape)
+    assert delta_bias is None or delta_bias.dtype == torch.float32
+    assert out.shape[0] >= R
+    st = kernels().cbis_add_layernorm(_ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0),
+                                      _ptr(delta_bias), _ptr(gamma), _ptr(beta), c_float(eps), _ptr(out),
+                                      c_int(dtype_code(out.dtype)), _ptr(rows), c_int(R), c_int(d), _stream())
+    _check(st, "add_layernorm", f"rows={R} width={d}")
+
+
+def bias_act(x, bias, act):
+    """x = act(x + bias) in place, arithmetic in 32-bit."""
+    _need_cuda(x, bias)
+    M, N = x.shape
+    assert x.is_contiguous()
+    st = kernels().cbis_bias_act(_ptr(x), _ptr(bias), c_int(ACT[act]), c_int(M), c_int(N),
+                                 c_int(dtype_code(x.dtype)), _stream())
+    _check(st, "bias_act", f"M={M} N={N}")
+
+
+def linear_f32(x, w, bias, act, out, w_is_nk=False):
+    """out = act(x @ W + bias) on the FP32 units; W is [K,N], or [N,K] with ``w_is_nk``."""
+    _need_cuda(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0] if w_is_nk else w.shape[1]
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype == torch.float32
+    assert (w.shape[1] if w_is_nk else w.shape[0]) == K and w.is_contiguous()
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == N
+    st = kernels().cbis_linear_f32(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                   c_int(1 if w_is_nk else 0), c_int(ACT[act]), c_int(x.stride(0)),
+                                   c_int(out.stride(0)), _stream())
+    _check(st, "linear_f32", f"M={M} N={N} K={K}")
+
+
+def linear(x, w, bias, act=None, out_dtype=None, w_is_nk=False):
+    """act(x @ W + bias).  32-bit inputs: this package's FFMA kernel (no reduced-precision
+    matrix mode).  bfloat16 inputs: the library GEMM with 32-bit accumulation, then the
+    bias/activation kernel."""
+    M = x.shape[0]
+    N = w.shape[0] if w_is_nk else w.shape[1]
+    if x.dtype == torch.float32:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        linear_f32(x, w, bias, act, out, w_is_nk)
+        return out
+    _need_cuda(x, w)
+    out_dtype = out_dtype or x.dtype
+    wm = w.t() if w_is_nk else w
+    if out_dtype == torch.float32:
+        out = torch.mm(x, wm, out_dtype=torch.float32)
+    else:
+        out = torch.mm(x, wm)
+    if bias is not None or ACT[act]:
+        bias_act(out, bias, act)
+    return out
+
+
+def kv_write(qkv, k_off, v_off, k_cache, v_cache, slot_mapping, n_kv_head, head_dim, page_size):
+    """Rows of this step's K and V (columns k_off.. and v_off.. of qkv) go to their token slots."""
+    _need_cuda(qkv, k_cache, v_cache, slot_mapping)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] >= T
+    st = kernels().cbis_kv_write(_ptr(qkv), c_int(qkv.stride(0)), c_int(k_off), c_int(v_off), _ptr(k_cache),
+                                 _ptr(v_cache), _ptr(slot_mapping), c_int(T), c_int(n_kv_head), c_int(head_dim),
+                                 c_int(page_size), c_int(dtype_code(qkv.dtype)), _stream())
+    _check(st, "kv_write", f"T={T} kv_heads={n_kv_head} head_dim={head_dim} page={page_size}")
+
+
+def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions, out, n_head, n_kv_head,
+                            head_dim, page_size, scale, window=0):
+    """Attention of every row over its request's pages: keys max(0,p-window+1)..p for the query at p."""
+    _need_cuda(q, k_cache, v_cache, block_table, row_seq, positions, out)
+    T = q.shape[0]
+    if head_dim > 256:
+        raise KernelError(f"attention: head_dim={head_dim} is above the kernel's limit of 256")
+    if n_head % n_kv_head:
+        raise KernelError(f"attention: n_head={n_head} is not a multiple of n_kv_head={n_kv_head}")
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32
+    assert block_table.is_contiguous() and row_seq.dtype == torch.int32 and positions.dtype == torch.int32
+    st = kernels().cbis_paged_attention_generic(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(row_seq), _ptr(positions), _ptr(out), c_int(out.stride(0)), c_int(T), c_int(n_head), c_int(n_kv_head),
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(dtype_code(q.dtype)), _stream())
+    _check(st, "paged_attention_generic", f"T={T} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+
+
+def sample(logits, temperature, keys, out):
+    """out[r] = argmax_i(logits[r,i]) (temperature[r] <= 0 or None) or the Gumbel-max draw keyed by keys[r]."""
+    _need_cuda(logits, temperature, keys, out)
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    assert temperature is None or temperature.dtype == torch.float32
+    assert keys is None or keys.dtype == torch.int64
+    st = kernels().cbis_sample(_ptr(logits), c_int(logits.stride(0)), _ptr(temperature), _ptr(keys), _ptr(out),
+                               c_int(R), c_int(V), _stream())
+    _check(st, "sample", f"R={R} V={V}")

@@ -1,0 +1,136 @@
+"""The model: layers put together from registered parts as a ``ModelSpec`` says.
+
+The reference hard-wires one model in ``TransformerRunner::forward_step``
+(src/transformer.cpp:65-93): embed, L times (LN, QKV, scatter, attention, O + residual,
+LN, FC1, GELU, FC2 + residual), final LN, LM head on all rows.  Here the same order comes
+out of the spec's layer list and schedule; the head runs only on the rows whose logits
+are wanted.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelSpec, load_config
+from ..kernels import ops
+from ..parts import (make_block, make_feed_forward, make_mixer, make_norm, make_position)
+from ..weights import TensorDecl, check_tensors, read_model_tensors
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    if dtype not in _DTYPES:
+        raise ValueError(f"dtype {dtype!r} is not one of bfloat16, float32")
+    return _DTYPES[dtype]
+
+
+class Layer:
+    """A block with its parts and the tensor-name prefix of its weights."""
+
+    def __init__(self, spec, index: int):
+        self.spec, self.index = spec, index
+        extra = {"own_kv": False} if spec.cache_source is not None and spec.mixer.kind == "attention" else {}
+        self.mixer = make_mixer(spec.mixer, **extra)
+        self.feed_forward = make_feed_forward(spec.feed_forward)
+        self.norm_mixer = make_norm(spec.norm_mixer)
+        self.norm_feed_forward = make_norm(spec.norm_feed_forward)
+        self.block = make_block(spec.arrangement, self.mixer, self.feed_forward, self.norm_mixer,
+                                self.norm_feed_forward)
+        self.norm_names = tuple(spec.norm_prefixes)
+
+    def parts(self):
+        p = self.spec.prefix
+        return [(p, self.mixer), (p, self.feed_forward), (p + self.norm_names[0], self.norm_mixer),
+                (p + self.norm_names[1], self.norm_feed_forward)]
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.position = make_position(spec.position)
+        self.layers: List[Layer] = [Layer(ls, i) for i, ls in enumerate(spec.layers)]
+        for i in spec.schedule:
+            if not 0 <= i < len(self.layers):
+                raise ValueError(f"schedule names layer {i}; the model has {len(self.layers)} layers")
+        for ls in spec.layers:
+            if ls.cache_source is not None and not 0 <= ls.cache_source < len(self.layers):
+                raise ValueError(f"layer {ls.prefix!r} reads the cache of layer {ls.cache_source}, which does not exist")
+        self.final_norm = make_norm(spec.final_norm)
+        self.token_table: Optional[torch.Tensor] = None
+        self.head: Optional[torch.Tensor] = None
+        self.dtype: Optional[torch.dtype] = None
+        self.device = None
+
+    # ---- weights -------------------------------------------------------
+    def declared(self) -> List[TensorDecl]:
+        s = self.spec
+        decls = [TensorDecl(s.token_embedding, (s.vocab_size, s.width), "table")]
+        decls += self.position.tensors("")
+        for layer in self.layers:
+            for prefix, part in layer.parts():
+                decls += part.tensors(prefix)
+        decls += self.final_norm.tensors(s.final_norm_prefix)
+        if s.head is not None:
+            decls.append(TensorDecl(s.head, (s.vocab_size, s.width), "matrix"))
+        return decls
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype, device="cuda", where="weights") -> "Model":
+        dtype = resolve_dtype(dtype)
+        check_tensors(self.declared(), tensors, self.spec.ignored_tensors, where)
+        s = self.spec
+        self.dtype, self.device = dtype, torch.device(device)
+        self.token_table = tensors[s.token_embedding].to(device=device, dtype=dtype).contiguous()
+        self.position.load("", tensors, dtype, device)
+        for layer in self.layers:
+            for prefix, part in layer.parts():
+                part.load(prefix, tensors, dtype, device)
+        self.final_norm.load(s.final_norm_prefix, tensors, dtype, device)
+        self.head = (self.token_table if s.head is None
+                     else tensors[s.head].to(device=device, dtype=dtype).contiguous())
+        return self
+
+    def weight_bytes(self) -> int:
+        """Bytes of all weights a step reads (each once; a tied head counts once)."""
+        seen, total = set(), 0
+        def add(t):
+            nonlocal total
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        add(self.head)
+        for layer in self.layers:
+            for _, part in layer.parts():
+                for v in vars(part).values():
+                    add(v)
+        for v in vars(self.final_norm).values():
+            add(v)
+        return total
+
+    # ---- one step ------------------------------------------------------
+    def forward(self, ctx) -> torch.Tensor:
+        """Logits (float32 ``[R, vocab]``) at ``ctx.logit_rows`` for the rows of this step."""
+        x = self.position.embed(ctx, self.token_table)
+        pending = None
+        for li in self.spec.schedule:
+            layer = self.layers[li]
+            pending = layer.block.forward(ctx, x, pending, ctx.layer_cache(li), ctx.layer_state(li))
+        if ctx.n_logit_rows == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
+        h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
+        return ops.linear(h, self.head, None, None, out_dtype=torch.float32, w_is_nk=True)
+
+
+def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
+    return Model(spec).declared()
+
+
+def load_model(folder: str, dtype="bfloat16", device="cuda") -> Model:
+    """Model of ``folder`` (config.json chooses the architecture; model.safetensors by tensor name)."""
+    config = load_config(folder)
+    model = Model(config.model_spec())
+    model.config = config
+    model.load(read_model_tensors(folder), dtype, device, where=f"{folder}/model.safetensors")
+    return model

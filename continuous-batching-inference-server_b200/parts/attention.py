@@ -1,0 +1,63 @@
+"""Causal attention over the paged cache."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import CacheNeed, Delta, Mixer, register_mixer
+
+
+class PagedAttention(Mixer):
+    """q|k|v = h @ c_attn + b; this step's k and v go into the layer's pages; every row attends
+    to the keys of its request up to its own position (inside ``window`` if one is set), scores
+    scaled by ``scale``, softmax in 32-bit; the heads' outputs side by side go through c_proj
+    (reference: python/model.py:36-46, kernels/attention.cu:7-19 and 57-98,
+    src/transformer.cpp:71-83).  ``n_kv_head`` < ``n_head`` shares each key/value head among
+    n_head/n_kv_head query heads.  With ``own_kv=False`` the layer projects only queries and
+    reads the cache of another layer."""
+
+    def __init__(self, width: int, n_head: int, n_kv_head: int, head_dim: int, scale: float, window: int = 0,
+                 own_kv: bool = True, names=("attn.c_attn", "attn.c_proj")):
+        if n_head % n_kv_head:
+            raise ValueError(f"n_head={n_head} is not a multiple of n_kv_head={n_kv_head}")
+        self.width, self.n_head, self.n_kv_head, self.head_dim = int(width), int(n_head), int(n_kv_head), int(head_dim)
+        self.scale, self.window, self.own_kv = float(scale), int(window), bool(own_kv)
+        self.qkv_name, self.proj_name = names
+        self.d_q = self.n_head * self.head_dim
+        self.d_kv = self.n_kv_head * self.head_dim
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    @property
+    def qkv_width(self):
+        return self.d_q + (2 * self.d_kv if self.own_kv else 0)
+
+    def cache_need(self):
+        return CacheNeed(self.n_kv_head, self.head_dim, self.window) if self.own_kv else None
+
+    def tensors(self, prefix):
+        return [TensorDecl(f"{prefix}{self.qkv_name}.weight", (self.width, self.qkv_width)),
+                TensorDecl(f"{prefix}{self.qkv_name}.bias", (self.qkv_width,), "vector"),
+                TensorDecl(f"{prefix}{self.proj_name}.weight", (self.d_q, self.width)),
+                TensorDecl(f"{prefix}{self.proj_name}.bias", (self.width,), "vector")]
+
+    def load(self, prefix, tensors, dtype, device):
+        self.w_qkv = self._matrix(tensors[f"{prefix}{self.qkv_name}.weight"], dtype, device)
+        self.b_qkv = self._vector(tensors[f"{prefix}{self.qkv_name}.bias"], device)
+        self.w_o = self._matrix(tensors[f"{prefix}{self.proj_name}.weight"], dtype, device)
+        self.b_o = self._vector(tensors[f"{prefix}{self.proj_name}.bias"], device)
+
+    def forward(self, ctx, h, cache, state):
+        if cache is None:
+            raise RuntimeError("attention needs a cache: its own or the layer's it reads")
+        qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+        view = ctx.groups[cache.group]
+        if self.own_kv:
+            ops.kv_write(qkv, self.d_q, self.d_q + self.d_kv, cache.k, cache.v, view.slot_mapping,
+                         self.n_kv_head, self.head_dim, cache.page_size)
+        out = torch.empty((ctx.n_rows, self.d_q), dtype=qkv.dtype, device=qkv.device)
+        ctx.attention(self, qkv, cache, view, out)
+        return Delta(ops.linear(out, self.w_o, None, None, out_dtype=torch.float32), self.b_o)
+
+
+register_mixer("attention", PagedAttention)

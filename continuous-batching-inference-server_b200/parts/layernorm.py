@@ -1,0 +1,37 @@
+"""LayerNorm with the residual add folded in."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorDecl
+from .base import Delta, Norm, register_norm
+
+
+class LayerNorm(Norm):
+    """y = (x - mean) * rsqrt(var + eps) * weight + bias over the last dim, biased variance,
+    statistics in 32-bit (reference: kernels/elementwise.cu:21-57; eps is a literal there, :51)."""
+
+    def __init__(self, width: int, eps: float):
+        self.width, self.eps = int(width), float(eps)
+        self.weight = self.bias = None
+
+    def tensors(self, prefix):
+        return [TensorDecl(prefix + "weight", (self.width,), "vector"),
+                TensorDecl(prefix + "bias", (self.width,), "vector")]
+
+    def load(self, prefix, tensors, dtype, device):
+        self.weight = self._vector(tensors[prefix + "weight"], device)
+        self.bias = self._vector(tensors[prefix + "bias"], device)
+
+    def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
+        n = rows.shape[0] if rows is not None else x.shape[0]
+        out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
+        ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None,
+                          self.weight, self.bias, self.eps, out, rows)
+        return out
+
+
+register_norm("layernorm", LayerNorm)
