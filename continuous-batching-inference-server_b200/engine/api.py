@@ -1,0 +1,196 @@
+"""Python entry point: an engine over a model folder or over seeded random weights.
+
+The reference's Python side is its oracle, ``build_model(seed)`` and ``TinyGPT()(idx)``
+(python/model.py:63-77); its serving loop lives in C++ ``main`` functions
+(src/server_demo.cpp:101-213).  Here ``build_model(config, seed)`` gives an ``Engine`` with
+random weights of that configuration, ``Engine(folder)`` loads a model folder, and
+``generate`` runs the continuous-batching loop: schedule, one step, sample, update.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache import CachePool
+from ..config import config_from_dict, load_config
+from ..kernels import ops
+from ..kernels.library import host
+from ..models import Model, load_model, resolve_dtype
+from ..sampling import SamplingParams, request_key
+from ..weights import InitScheme, random_tensors
+from .runner import ModelRunner, StepEntry
+
+
+@dataclass
+class RequestOutput:
+    request_id: int
+    tokens: List[int]
+    finish_reason: str
+
+
+class Engine:
+    def __init__(self, model: Union[str, Model], *, dtype="bfloat16", page_size: int = 16,
+                 num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_num_seqs: int = 16,
+                 max_batched_tokens: int = 512, prefill_chunk: Optional[int] = None,
+                 memory_fraction: float = 0.85, device: str = "cuda"):
+        """``model``: a folder with config.json and model.safetensors, or a loaded ``Model``.
+        Engine options in the reference's terms: ``page_size`` = kPageSize (include/config.hpp:20),
+        ``num_pages`` = kMaxPages, ``max_num_seqs`` = kMaxSlots, ``max_batched_tokens`` =
+        kMaxTotalRows (src/server_demo.cpp:27-29).  ``prefill_chunk`` cuts prompts into portions
+        (src/bench_tiering.cpp:78 uses 512); default: the token budget."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("the engine needs a CUDA device (sm_100a); there is no CPU path")
+        self.model = load_model(model, dtype, device) if isinstance(model, str) else model
+        self.pool = CachePool(self.model, page_size=page_size, num_pages=num_pages, max_tokens=max_tokens,
+                              max_requests=max_num_seqs, memory_fraction=memory_fraction, device=device)
+        self.runner = ModelRunner(self.model, self.pool, max_batched_tokens=max_batched_tokens,
+                                  max_num_seqs=max_num_seqs)
+        self.limits = dict(max_num_seqs=max_num_seqs, max_batched_tokens=max_batched_tokens,
+                           prefill_chunk=prefill_chunk or max_batched_tokens,
+                           max_positions=self.model.spec.max_positions)
+        self.scheduler = host().Scheduler(self.pool.manager, host().SchedulerLimits(**self.limits))
+        self._params: Dict[int, SamplingParams] = {}
+        self._next_id = 0
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---- construction from random weights --------------------------------------
+    @classmethod
+    def from_random(cls, config, seed: int = 1234, *, init: InitScheme = InitScheme(), dtype="bfloat16",
+                    weight_dtype: Optional[torch.dtype] = None, device: str = "cuda", **options) -> "Engine":
+        """Random weights of ``config`` (a typed configuration, a dict of config.json keys, or a path
+        to a config.json), drawn on the device; nothing is written to disk."""
+        if isinstance(config, str):
+            with open(config if config.endswith(".json") else os.path.join(config, "config.json")) as f:
+                config = json.load(f)
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        model = Model(config.model_spec())
+        model.config = config
+        wd = weight_dtype or (torch.bfloat16 if resolve_dtype(dtype) == torch.bfloat16 else torch.float32)
+        tensors = random_tensors(model.declared(), seed, init, wd, device=device)
+        model.load(tensors, dtype, device, where="random weights")
+        del tensors
+        return cls(model, dtype=dtype, device=device, **options)
+
+    # ---- requests ---------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[int] = None) -> int:
+        params = params or SamplingParams()
+        rid = self._next_id if request_id is None else int(request_id)
+        self._next_id = max(self._next_id, rid + 1)
+        prompt = [int(t) for t in prompt]
+        V = self.model.spec.vocab_size
+        bad = [t for t in prompt if not 0 <= t < V]
+        if bad:
+            raise ValueError(f"request {rid}: token id {bad[0]} outside the vocabulary of {V}")
+        eos = -1 if params.eos_token_id is None else int(params.eos_token_id)
+        self.scheduler.add(rid, prompt, int(params.max_new_tokens), eos, bool(params.ignore_eos))
+        self._params[rid] = params
+        return rid
+
+    def has_unfinished(self) -> bool:
+        return not self.scheduler.idle()
+
+    @torch.no_grad()
+    def step(self) -> List[RequestOutput]:
+        """One engine step: plan, run, sample, update.  Returns the requests that finished."""
+        plan = self.scheduler.schedule()
+        if not plan:
+            return []
+        for slot in self.scheduler.take_new_slots():
+            self.pool.clear_state(slot)
+        entries = [StepEntry(p.slot, p.start, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
+        logits = self.runner.step(entries)
+        self.steps += 1
+        self.tokens_run += sum(len(p.tokens) for p in plan)
+        sampling = [p for p in plan if p.sample]
+        if not sampling:
+            return []
+        tokens = self._sample(logits, sampling)
+        done = self.scheduler.update([(p.request_id, int(t)) for p, t in zip(sampling, tokens)])
+        out = []
+        for f in done:
+            self._params.pop(f.request_id, None)
+            out.append(RequestOutput(f.request_id, list(f.output), f.reason))
+        return out
+
+    def _sample(self, logits: torch.Tensor, sampling) -> List[int]:
+        R = logits.shape[0]
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        params = [self._params[p.request_id] for p in sampling]
+        if all(q.temperature <= 0 for q in params):
+            ops.sample(logits, None, None, out)
+        else:
+            temps = torch.tensor([float(q.temperature) for q in params], dtype=torch.float32).to(logits.device)
+            keys = torch.tensor([request_key(q.seed, p.request_id, p.output_index) for p, q in zip(sampling, params)],
+                                dtype=torch.int64).to(logits.device)
+            ops.sample(logits, temps, keys, out)
+        return out.cpu().tolist()
+
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:
+        """Runs all prompts to their end under continuous batching; returns each one's new tokens.
+        Request i of the call has id ``first_id + i``, the key of its sampling stream."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        ids = [self.add_request(p, q) for p, q in zip(prompts, params)]
+        results: Dict[int, List[int]] = {}
+        while self.has_unfinished():
+            for o in self.step():
+                results[o.request_id] = o.tokens
+        return [results[i] for i in ids]
+
+    # ---- the bare step, for replay and checks -----------------------------------
+    def open_request(self, request_id: int = 0) -> int:
+        """Takes a request slot outside the scheduler (replay); returns the slot."""
+        slot = self.pool.manager.admit(int(request_id))
+        if slot < 0:
+            raise RuntimeError(f"all {self.pool.max_requests} request slots are taken")
+        self.pool.clear_state(slot)
+        return slot
+
+    def close_request(self, slot: int) -> None:
+        self.pool.manager.release(slot)
+
+    @torch.no_grad()
+    def forward_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Takes pages for the entries' tokens, runs them as ONE step, returns float32 logits
+        ``[wanted, vocab]``.  Pages behind a window are given back before the next step."""
+        mgr = self.pool.manager
+        for e in entries:
+            mgr.release_out_of_window(e.slot)
+        for e in entries:
+            if mgr.length(e.slot) != e.start:
+                raise ValueError(f"slot {e.slot}: holds {mgr.length(e.slot)} tokens, the entry starts at {e.start}")
+            if not mgr.append(e.slot, len(e.tokens)):
+                raise RuntimeError(f"slot {e.slot}: no pages left for {len(e.tokens)} more tokens "
+                                   f"(free pages per group: {[mgr.free_pages(g) for g in range(mgr.num_groups())]})")
+        return self.runner.step(entries)
+
+    @torch.no_grad()
+    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Logits ``[T, vocab]`` of one whole sequence, as the reference's ``model(idx)``
+        (python/model.py:63-70), through the step function in portions of the token budget."""
+        slot = self.open_request(-1)
+        try:
+            outs, pos = [], 0
+            while pos < len(tokens):
+                n = min(self.runner.max_tokens, len(tokens) - pos)
+                outs.append(self.forward_step([StepEntry(slot, pos, list(tokens[pos:pos + n]), list(range(n)))]))
+                pos += n
+            return torch.cat(outs)
+        finally:
+            self.close_request(slot)
+
+
+def build_model(config, seed: int = 1234, **options) -> Engine:
+    """Engine with seeded random weights of ``config`` (the reference's ``build_model(seed)``,
+    python/model.py:73-77, builds its one fixed-size model the same way)."""
+    return Engine.from_random(config, seed, **options)

@@ -1,0 +1,193 @@
+"""The scheduler's decisions (CPU): admission, portions under a token budget, decoding, finishing,
+freeing, and what happens when pages run out."""
+import random
+
+import pytest
+
+from cbis_b200.kernels.library import host
+
+
+def make(num_pages=64, page=4, max_seqs=4, budget=16, chunk=8, positions=64, window=0):
+    h = host()
+    cache = h.CacheManager([h.GroupSpec(page, num_pages, window)], max_seqs)
+    return cache, h.Scheduler(cache, h.SchedulerLimits(max_seqs, budget, chunk, positions))
+
+
+def run_to_end(cache, sch, next_token=lambda rid, k: 100 + k, max_steps=10_000):
+    """Drives the scheduler with made-up sampled tokens; returns {id: (reason, output)} and the plans."""
+    done, plans, count = {}, [], {}
+    for _ in range(max_steps):
+        if sch.idle():
+            break
+        plan = sch.schedule()
+        assert plan, "a step must run something while requests are left"
+        assert cache.check() == ""
+        plans.append([(p.request_id, p.start, list(p.tokens), p.sample) for p in plan])
+        sampled = []
+        for p in plan:
+            if p.sample:
+                k = count.get(p.request_id, 0)
+                assert p.output_index == k
+                count[p.request_id] = k + 1
+                sampled.append((p.request_id, next_token(p.request_id, k)))
+        for f in sch.update(sampled):
+            done[f.request_id] = (f.reason, list(f.output))
+    assert sch.idle()
+    return done, plans
+
+
+def test_prompt_is_cut_into_portions_beside_decoding_requests():
+    cache, sch = make(budget=16, chunk=8)
+    sch.add(0, list(range(5)), 3)
+    plan = sch.schedule()
+    assert [(p.request_id, p.start, p.tokens, p.sample) for p in plan] == [(0, 0, [0, 1, 2, 3, 4], True)]
+    sch.update([(0, 50)])
+    sch.add(1, list(range(20)), 2)
+    plan = sch.schedule()                                   # decode token first, then a portion of the new prompt
+    assert [(p.request_id, p.start, len(p.tokens), p.sample) for p in plan] == [(0, 5, 1, True), (1, 0, 8, False)]
+    assert plan[0].tokens == [50]
+    sch.update([(0, 51)])
+    plan = sch.schedule()
+    assert [(p.request_id, p.start, len(p.tokens), p.sample) for p in plan] == [(0, 6, 1, True), (1, 8, 8, False)]
+    done = sch.update([(0, 52)])
+    assert [(f.request_id, f.reason, f.output) for f in done] == [(0, "length", [50, 51, 52])]
+    plan = sch.schedule()
+    assert [(p.request_id, p.start, len(p.tokens), p.sample) for p in plan] == [(1, 16, 4, True)]
+    assert cache.free_slots() == 3
+
+
+def test_budget_bounds_every_step_and_all_finish():
+    cache, sch = make(budget=10, chunk=6, max_seqs=3)
+    lens = [1, 7, 23, 40, 13]
+    for i, n in enumerate(lens):
+        sch.add(i, [i] * n, 5)
+    done, plans = run_to_end(cache, sch)
+    assert set(done) == set(range(5)) and all(r == "length" and len(o) == 5 for r, o in done.values())
+    for plan in plans:
+        assert sum(len(t) for _, _, t, _ in plan) <= 10 and len(plan) <= 3
+        assert all(len(t) <= 6 for _, _, t, _ in plan)
+    # every request's tokens were run exactly once, in order, prompt then its outputs but the last
+    for i, n in enumerate(lens):
+        fed = [t for plan in plans for rid, _, toks, _ in plan if rid == i for t in toks]
+        assert fed == [i] * n + [100, 101, 102, 103]
+    assert cache.free_pages(0) == 64 and cache.free_slots() == 3
+
+
+def test_fifo_admission_and_slot_limit():
+    cache, sch = make(max_seqs=2, budget=64, chunk=64)
+    for i in range(4):
+        sch.add(i, [1, 2, 3], 2)
+    plan = sch.schedule()
+    assert [p.request_id for p in plan] == [0, 1] and sch.num_waiting() == 2
+    sch.update([(0, 9), (1, 9)])
+    sch.schedule()
+    sch.update([(0, 9), (1, 9)])                            # both finish
+    assert [p.request_id for p in sch.schedule()] == [2, 3]
+
+
+def test_eos_and_position_limit():
+    cache, sch = make(positions=8, budget=16, chunk=16)
+    sch.add(0, [1, 2, 3], 10, 7, False)
+    sch.add(1, [1, 2, 3], 10, 7, True)
+    sch.add(2, [1, 2, 3, 4, 5, 6], 10)
+    done, _ = run_to_end(cache, sch, next_token=lambda rid, k: 7 if k == 1 else 5)
+    assert done[0] == ("stop", [5, 7])
+    assert done[1][0] == "length" and len(done[1][1]) == 6   # 3 + 6 = 9 tokens > 8 positions: the 6th cannot be fed
+    assert done[2] == ("length", [5, 7, 5])                  # fed 6,7,8 tokens; the third output has no position left
+
+
+def test_refusals_at_add():
+    cache, sch = make(num_pages=4, page=4, positions=32)
+    with pytest.raises(ValueError, match="empty prompt"):
+        sch.add(0, [], 4)
+    with pytest.raises(ValueError, match="exceeds the model's 32 positions"):
+        sch.add(1, [0] * 33, 1)
+    with pytest.raises(ValueError, match="can never fit"):
+        sch.add(2, [0] * 10, 8)                              # 17 tokens need 5 pages of 4
+    sch.add(3, [0] * 10, 7)                                  # 16 tokens: fits exactly
+    with pytest.raises(ValueError, match="exists already"):
+        sch.add(3, [0], 1)
+
+
+def test_pages_run_out_newest_is_preempted_and_recomputed():
+    cache, sch = make(num_pages=6, page=4, max_seqs=3, budget=32, chunk=32)
+    sch.add(0, [10] * 7, 9)                                  # grows to 15 tokens: 4 pages
+    sch.add(1, [11] * 7, 9)
+    plan = sch.schedule()
+    assert [p.request_id for p in plan] == [0, 1] and cache.free_pages(0) == 2
+    sch.update([(0, 100), (1, 100)])
+    history = {0: [], 1: []}
+    preempted_seen = False
+    for step in range(200):
+        if sch.idle():
+            break
+        plan = sch.schedule()
+        assert plan and cache.check() == ""
+        sampled = []
+        for p in plan:
+            history[p.request_id].append((p.start, list(p.tokens)))
+            if p.request_id == 1 and p.start == 0 and len(p.tokens) > 7:
+                preempted_seen = True                         # recomputed: prompt and its outputs so far in one portion
+                assert p.tokens[:7] == [11] * 7 and p.tokens[7:] == [100 + k for k in range(len(p.tokens) - 7)]
+            if p.sample:
+                sampled.append((p.request_id, 100 + p.output_index))
+        sch.update(sampled)
+    assert sch.idle() and sch.preemptions() >= 1 and preempted_seen
+    # the older request was never disturbed: it ran each position exactly once
+    starts0 = [s for s, _ in history[0]]
+    assert starts0 == sorted(set(starts0))
+    assert cache.free_pages(0) == 6 and cache.free_slots() == 3
+
+
+def test_admission_by_what_fits_now_is_settled_by_preemption_later():
+    cache, sch = make(num_pages=4, page=4, max_seqs=2, budget=32, chunk=32)
+    sch.add(0, [1] * 8, 5)                                   # 12 tokens at most: 3 pages
+    sch.add(1, [2] * 8, 5)
+    done, plans = run_to_end(cache, sch)
+    assert [rid for rid, _, _, _ in plans[0]] == [0, 1]      # both prompts fit now (2 pages each) ...
+    # ... but not both at 3 pages: the newer one yields
+    assert set(done) == {0, 1} and sch.preemptions() >= 1
+    assert all(len(o) == 5 for _, o in done.values())
+    starts0 = [st for plan in plans for rid, st, _, _ in plan if rid == 0]
+    assert starts0 == sorted(set(starts0))                   # the older request never started over
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_finish_with_books_kept(seed):
+    rng = random.Random(seed)
+    window = rng.choice([0, 0, 12])
+    cache, sch = make(num_pages=rng.randint(12, 30), page=rng.choice([2, 4, 8]), max_seqs=rng.randint(1, 5),
+                      budget=rng.randint(4, 24), chunk=rng.randint(2, 16), positions=48, window=window)
+    want = {}
+    rid = 0
+    done = {}
+    fed = {}
+    for step in range(3000):
+        if rid < 25 and rng.random() < 0.3:
+            n, g = rng.randint(1, 30), rng.randint(1, 12)
+            try:
+                sch.add(rid, [rid] * n, g)
+                want[rid] = min(g, 48 - n + 1)
+            except ValueError:
+                pass
+            rid += 1
+        if sch.idle():
+            if rid >= 25:
+                break
+            continue
+        plan = sch.schedule()
+        assert plan and cache.check() == ""
+        sampled = []
+        for p in plan:
+            if p.start == 0:
+                fed[p.request_id] = []                        # (re)computed from the start
+            assert p.start == len(fed[p.request_id])
+            fed[p.request_id] += list(p.tokens)
+            if p.sample:
+                sampled.append((p.request_id, 1000 + p.output_index))
+        for f in sch.update(sampled):
+            done[f.request_id] = list(f.output)
+    assert sch.idle() and set(done) == set(want)
+    for r, out in done.items():
+        assert out == [1000 + k for k in range(want[r])]
+    assert cache.free_pages(0) == cache.num_pages(0) and cache.check() == ""
