@@ -1,0 +1,142 @@
+"""Generation through the Python entry point and the command line against the plain implementation (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt
+import tiny_configs as tc
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def prompts_for(cfg, lens, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+
+
+def check_against_plain(folder, prompts, outputs, temperature, seed, first_id, exact):
+    """exact: token for token.  Otherwise (bfloat16) every chosen token must be, by the plain
+    model's own scores for the engine's sequence, within a small margin of the best one."""
+    cfg, w = plain_gpt.read_model_folder(folder, torch.float64)
+    for i, (p, out) in enumerate(zip(prompts, outputs)):
+        if exact:
+            assert out == plain_gpt.generate(cfg, w, p, len(out), temperature, seed, first_id + i), f"request {i}"
+            continue
+        with torch.no_grad():
+            logits = plain_gpt.forward(cfg, w, p + out[:-1]).numpy()
+        for j, t in enumerate(out):
+            scores = plain_gpt.perturbed_scores(logits[len(p) - 1 + j], temperature, seed, first_id + i, j)
+            margin = 0.03 * np.abs(logits).max() / max(temperature, 1.0) if temperature else 0.03 * np.abs(logits).max()
+            assert scores[t] >= scores.max() - margin, f"request {i} output {j}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_tiny_a(folder_a, dtype):
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_A, [5, 17, 33], 1)
+    eng = cb.Engine(folder_a, dtype=dtype, page_size=tc.PAGE_A, num_pages=16, max_num_seqs=3, max_batched_tokens=64)
+    outs = eng.generate(prompts, cb.SamplingParams(max_new_tokens=16))
+    assert [len(o) for o in outs] == [16, 16, 16]
+    check_against_plain(folder_a, prompts, outs, 0.0, 0, 0, exact=dtype == "float32")
+    assert eng.pool.manager.free_pages(0) == 16 and eng.pool.manager.check() == ""
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_generation_tiny_b_in_portions(folder_b, dtype):
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_B, [1, 7, 23, 40, 61], 2)
+    eng = cb.Engine(folder_b, dtype=dtype, page_size=tc.PAGE_B, num_pages=64, max_num_seqs=5, max_batched_tokens=40,
+                    prefill_chunk=16)
+    outs = eng.generate(prompts, cb.SamplingParams(max_new_tokens=16, temperature=0.8, seed=4321))
+    assert [len(o) for o in outs] == [16] * 5
+    check_against_plain(folder_b, prompts, outs, 0.8, 4321, 0, exact=dtype == "float32")
+    # the draws do not depend on the batch: one request alone gives the same tokens
+    solo = cb.Engine(folder_b, dtype=dtype, page_size=tc.PAGE_B, num_pages=64, max_num_seqs=1, max_batched_tokens=96)
+    rid = solo.add_request(prompts[3], cb.SamplingParams(max_new_tokens=16, temperature=0.8, seed=4321), request_id=3)
+    res = {}
+    while solo.has_unfinished():
+        for o in solo.step():
+            res[o.request_id] = o.tokens
+    if dtype == "float32":
+        assert res[rid] == outs[3]
+
+
+def test_long_decoding_to_the_last_position(folder_a):
+    import cbis_b200 as cb
+    P = tc.TINY_A["n_positions"]
+    eng = cb.Engine(folder_a, dtype="float32", page_size=16, num_pages=8, max_num_seqs=1, max_batched_tokens=16)
+    prompt = [7, 3, 200]
+    out = eng.generate([prompt], cb.SamplingParams(max_new_tokens=500))[0]
+    assert len(out) == P - len(prompt) + 1                      # every position was fed; the last output has none left
+    cfg, w = plain_gpt.read_model_folder(folder_a, torch.float64)
+    assert out == plain_gpt.generate(cfg, w, prompt, len(out))
+
+
+def test_first_tokens_of_a_sequence(tiny):
+    import cbis_b200 as cb
+    folder, cfg, page = tiny
+    eng = cb.Engine(folder, dtype="float32", page_size=page, num_pages=8, max_num_seqs=2, max_batched_tokens=16)
+    pcfg, w = plain_gpt.read_model_folder(folder, torch.float64)
+    for toks in ([0], [cfg["vocab_size"] - 1], [3, 3], [5, 0, 9]):
+        got = eng.logits(toks).double().cpu().numpy()
+        with torch.no_grad():
+            ref = plain_gpt.forward(pcfg, w, toks).numpy()
+        assert np.abs(got - ref).max() < 1e-4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_gives_the_same_tokens(folder_b, dtype):
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_B, [9, 14, 20, 11], 3)
+    params = cb.SamplingParams(max_new_tokens=24, temperature=0.7, seed=99)
+    roomy = cb.Engine(folder_b, dtype=dtype, page_size=8, num_pages=40, max_num_seqs=4, max_batched_tokens=32)
+    want = roomy.generate(prompts, params)
+    tight = cb.Engine(folder_b, dtype=dtype, page_size=8, num_pages=11, max_num_seqs=4, max_batched_tokens=32)
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.preemptions() >= 1
+    if dtype == "float32":
+        assert got == want
+    else:
+        check_against_plain(folder_b, prompts, got, 0.7, 99, 0, exact=False)
+    assert tight.pool.manager.free_pages(0) == 11 and tight.pool.manager.check() == ""
+
+
+def test_eos_stops_a_request(folder_a):
+    import cbis_b200 as cb
+    eng = cb.Engine(folder_a, dtype="float32", page_size=16, num_pages=8, max_num_seqs=2, max_batched_tokens=32)
+    prompt = [1, 2, 3, 4]
+    free = eng.generate([prompt], cb.SamplingParams(max_new_tokens=12))[0]
+    stop_at = free[5]
+    k = free.index(stop_at)
+    out = eng.generate([prompt], cb.SamplingParams(max_new_tokens=12, eos_token_id=stop_at))[0]
+    assert out == free[:k + 1]
+    assert eng.generate([prompt], cb.SamplingParams(max_new_tokens=12, eos_token_id=stop_at, ignore_eos=True))[0] == free
+
+
+def test_build_model_from_a_configuration_and_a_seed():
+    import cbis_b200 as cb
+    a = cb.build_model(tc.TINY_B, seed=5, dtype="float32", page_size=8, num_pages=16, max_num_seqs=2)
+    b = cb.build_model(cb.config_from_dict(tc.TINY_B), seed=5, dtype="float32", page_size=8, num_pages=16, max_num_seqs=2)
+    c = cb.build_model(tc.TINY_B, seed=6, dtype="float32", page_size=8, num_pages=16, max_num_seqs=2)
+    toks = [4, 8, 15, 16, 23, 42]
+    la, lb, lc = a.logits(toks), b.logits(toks), c.logits(toks)
+    assert la.shape == (6, 317) and torch.equal(la, lb) and not torch.equal(la, lc)
+
+
+def test_command_line(folder_a, tmp_path):
+    prompts = prompts_for(tc.TINY_A, [4, 9], 8)
+    pf = tmp_path / "prompts.txt"
+    pf.write_text("\n".join(",".join(map(str, p)) for p in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "generate"), folder_a, "--dtype", "float32",
+                        "--prompts-file", str(pf), "--max-new-tokens", "6", "--num-pages", "8", "--json"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+    outs = [json.loads(l)["tokens"] for l in r.stdout.splitlines() if l.startswith("{")]
+    cfg, w = plain_gpt.read_model_folder(folder_a, torch.float64)
+    assert outs == [plain_gpt.generate(cfg, w, p, 6) for p in prompts]

@@ -1,0 +1,259 @@
+"""Each CUDA kernel alone against a plain torch reference, at sizes other than the engine's (GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cbis_b200.kernels import ops as o
+    return o
+
+
+def dev(t):
+    return t.cuda().contiguous()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [7, 100, 1032])
+def test_embed_pos_add(ops, dtype, d):
+    g = torch.Generator().manual_seed(d)
+    V, P, T = 53, 19, 37
+    wte, wpe = torch.randn(V, d, generator=g).to(dtype), torch.randn(P, d, generator=g).to(dtype)
+    tok, pos = torch.randint(0, V, (T,), generator=g).int(), torch.randint(0, P, (T,), generator=g).int()
+    out = torch.full((T, d), float("nan"), device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_pos_add(dev(tok), dev(pos), dev(wte), dev(wpe), out, err)
+    ref = wte.float()[tok.long()] + wpe.float()[pos.long()]
+    assert torch.equal(out.cpu(), ref) and err.item() == 0
+    ops.embed_pos_add(dev(tok), dev(pos), dev(wte), None, out, err)
+    assert torch.equal(out.cpu(), wte.float()[tok.long()])
+    tok[5] = V
+    ops.embed_pos_add(dev(tok), dev(pos), dev(wte), dev(wpe), out, err)
+    assert err.item() == 1 and torch.equal(out[5].cpu(), torch.zeros(d))
+    err.zero_(); tok[5] = 0; pos[3] = P
+    ops.embed_pos_add(dev(tok), dev(pos), dev(wte), dev(wpe), out, err)
+    assert err.item() == 2
+
+
+@pytest.mark.parametrize("d", [5, 96, 1000, 2500, 20000])
+@pytest.mark.parametrize("delta_dtype,out_dtype", [(None, torch.float32), (torch.float32, torch.float32),
+                                                    (torch.bfloat16, torch.bfloat16), (torch.float32, torch.bfloat16)])
+def test_add_layernorm(ops, d, delta_dtype, out_dtype):
+    g = torch.Generator().manual_seed(d)
+    T, eps = 9, 3e-6
+    x = torch.randn(T, d, generator=g) * 3 + 1.5
+    delta = (torch.randn(T, d, generator=g)).to(delta_dtype) if delta_dtype else None
+    bias = torch.randn(d, generator=g) if delta_dtype else None
+    gamma, beta = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    xs = x.double() + (delta.double() + bias.double() if delta is not None else 0)
+    ref = plain_gpt.layer_norm(xs, gamma.double(), beta.double(), eps)
+    xd = dev(x)
+    out = torch.empty(T, d, dtype=out_dtype, device="cuda")
+    ops.add_layernorm(xd, dev(delta) if delta is not None else None, dev(bias) if bias is not None else None,
+                      dev(gamma), dev(beta), eps, out)
+    tol = 1e-5 if out_dtype == torch.float32 else 2e-2
+    assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+    assert (xd.double().cpu() - xs).abs().max() < 1e-6 * 20          # the residual stream moved on, in 32-bit
+    # row selection: only the chosen rows, x untouched
+    rows = torch.tensor([7, 0, 7, 3], dtype=torch.int32)
+    xd2 = dev(x)
+    out2 = torch.empty(4, d, dtype=out_dtype, device="cuda")
+    ops.add_layernorm(xd2, dev(delta) if delta is not None else None, dev(bias) if bias is not None else None,
+                      dev(gamma), dev(beta), eps, out2, dev(rows))
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()]) and torch.equal(xd2.cpu(), x)
+
+
+def test_add_layernorm_refuses_a_width_it_cannot_stage(ops):
+    x = torch.zeros(1, 60000, device="cuda")
+    with pytest.raises(ops.KernelError, match="too large"):
+        ops.add_layernorm(x, None, None, x[0], x[0], 1e-5, torch.empty_like(x))
+
+
+def test_layernorm_of_large_offsets_is_centred(ops):
+    # E[x^2]-mean^2 (the reference's form, kernels/elementwise.cu:50) loses the variance here; the centred form does not
+    d = 512
+    x = (torch.randn(3, d) * 0.01 + 300.0)
+    ones, zeros = torch.ones(d), torch.zeros(d)
+    out = torch.empty(3, d, device="cuda")
+    ops.add_layernorm(dev(x), None, None, dev(ones), dev(zeros), 1e-8, out)
+    ref = plain_gpt.layer_norm(x.double(), ones.double(), zeros.double(), 1e-8)
+    assert (out.double().cpu() - ref).abs().max() < 5e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act,name", [("gelu_erf", "gelu"), ("gelu_tanh", "gelu_new"), (None, None)])
+def test_bias_act(ops, dtype, act, name):
+    g = torch.Generator().manual_seed(3)
+    M, N = 13, 301
+    x = (torch.randn(M, N, generator=g) * 2).to(dtype)
+    b = torch.randn(N, generator=g)
+    xd = dev(x)
+    ops.bias_act(xd, dev(b), act)
+    v = x.double() + b.double()
+    ref = plain_gpt.gelu(v, name) if name else v
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    assert (xd.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("M", [1, 5, 17, 70, 300])
+@pytest.mark.parametrize("N,K", [(33, 5), (100, 64), (513, 300), (64, 1030)])
+def test_linear_f32(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x, w, b = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g), torch.randn(N, generator=g)
+    ref = x.double() @ w.double() + b.double()
+    scale = ref.abs().max().item()
+    out = torch.empty(M, N, device="cuda")
+    ops.linear_f32(dev(x), dev(w), dev(b), None, out)
+    assert (out.double().cpu() - ref).abs().max() < 2e-6 * scale * math.sqrt(K)
+    ops.linear_f32(dev(x), dev(w.t()), None, "gelu_erf", out, w_is_nk=True)
+    ref2 = plain_gpt.gelu(x.double() @ w.double(), "gelu")
+    assert (out.double().cpu() - ref2).abs().max() < 2e-6 * scale * math.sqrt(K)
+    # a strided input (columns of a wider matrix) and a strided output
+    wide = torch.randn(M, K + 11, generator=g)
+    big = torch.zeros(M, N + 5, device="cuda")
+    ops.linear_f32(dev(wide)[:, 3:3 + K], dev(w), None, None, big[:, :N])
+    assert (big[:, :N].double().cpu() - wide[:, 3:3 + K].double() @ w.double()).abs().max() < 2e-6 * scale * math.sqrt(K)
+    assert torch.equal(big[:, N:].cpu(), torch.zeros(M, 5))
+
+
+def test_linear_f32_is_true_32_bit(ops):
+    # a product that TF32 (10-bit mantissa) would get wrong by ~1e-3 relative
+    g = torch.Generator().manual_seed(1)
+    x, w = 1.0 + torch.rand(64, 256, generator=g) * 1e-3, 1.0 + torch.rand(256, 64, generator=g) * 1e-3
+    out = torch.empty(64, 64, device="cuda")
+    ops.linear_f32(dev(x), dev(w), None, None, out)
+    ref = x.double() @ w.double()
+    assert ((out.double().cpu() - ref).abs() / ref).max() < 1e-6
+
+
+def naive_paged_attention(q, k_all, v_all, positions, row_seq, n_head, n_kv_head, hd, scale, window):
+    """q [T, H*hd]; k_all/v_all: per segment the full key/value rows [ctx, Hkv*hd] (float64)."""
+    out = torch.zeros_like(q)
+    for r in range(q.shape[0]):
+        s, p = int(row_seq[r]), int(positions[r])
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(n_head):
+            hk = h // (n_head // n_kv_head)
+            kk = k_all[s][lo:p + 1, hk * hd:(hk + 1) * hd]
+            vv = v_all[s][lo:p + 1, hk * hd:(hk + 1) * hd]
+            sc = (kk @ q[r, h * hd:(h + 1) * hd]) * scale
+            out[r, h * hd:(h + 1) * hd] = torch.softmax(sc, 0) @ vv
+    return out
+
+
+def paged_case(ops, dtype, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed):
+    """Random keys/values scattered over random pages by kv_write; queries for the last seg_rows of each segment."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(seg_ctx)
+    max_blocks = max(-(-c // ps) for c in seg_ctx) + 2
+    num_pages = sum(-(-c // ps) for c in seg_ctx) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    bt = torch.full((S, max_blocks), -1, dtype=torch.int32)
+    k_all, v_all = [], []
+    kc = torch.full((num_pages, n_kv_head, ps, hd), float("nan")).to(dtype).cuda()
+    vc = torch.full((num_pages, n_kv_head, ps, hd), float("nan")).to(dtype).cuda()
+    dkv = n_kv_head * hd
+    for s, c in enumerate(seg_ctx):
+        nb = -(-c // ps)
+        pages = [perm.pop() for _ in range(nb)]
+        bt[s, :nb] = torch.tensor(pages, dtype=torch.int32)
+        kv = torch.randn(c, 2 * dkv, generator=g).to(dtype)
+        k_all.append(kv[:, :dkv].double()); v_all.append(kv[:, dkv:].double())
+        slots = torch.tensor([pages[p // ps] * ps + p % ps for p in range(c)], dtype=torch.int32)
+        ops.kv_write(dev(kv), 0, dkv, kc, vc, dev(slots), n_kv_head, hd, ps)
+    positions = torch.tensor([p for c, n in zip(seg_ctx, seg_rows) for p in range(c - n, c)], dtype=torch.int32)
+    row_seq = torch.tensor([s for s, n in enumerate(seg_rows) for _ in range(n)], dtype=torch.int32)
+    q = torch.randn(len(positions), n_head * hd, generator=g).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    ref = naive_paged_attention(q.double(), k_all, v_all, positions, row_seq, n_head, n_kv_head, hd, scale, window)
+    return dict(q=q, kc=kc, vc=vc, bt=bt, positions=positions, row_seq=row_seq, ref=ref, scale=scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [
+    (3, 3, 24, 8, 0), (2, 2, 32, 16, 0), (6, 2, 80, 4, 0), (5, 5, 128, 16, 0), (2, 1, 256, 32, 0),
+    (4, 4, 48, 8, 11), (1, 1, 16, 3, 5)])
+def test_kv_write_and_generic_attention(ops, dtype, n_head, n_kv_head, hd, ps, window):
+    seg_ctx, seg_rows = [1, 37, 70, 16, 129], [1, 1, 33, 16, 2]
+    c = paged_case(ops, dtype, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed=hd + ps)
+    out = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_attention_generic(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(c["row_seq"]), dev(c["positions"]),
+                                out, n_head, n_kv_head, hd, ps, c["scale"], window)
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - c["ref"]).abs().max() < tol * max(1.0, c["ref"].abs().max().item())
+
+
+def test_attention_refuses_sizes_it_does_not_take(ops):
+    z = torch.zeros(1, 600, device="cuda")
+    i = torch.zeros(1, 1, dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.KernelError, match="head_dim=300"):
+        ops.paged_attention_generic(z, z, z, i, i[0], i[0], z, 2, 2, 300, 16, 1.0)
+    with pytest.raises(ops.KernelError, match="not a multiple"):
+        ops.paged_attention_generic(z, z, z, i, i[0], i[0], z, 3, 2, 32, 16, 1.0)
+
+
+def test_a_far_key_among_hundreds_is_found(ops):
+    # one key, far back and at the edge of a page, matches the query; every other score is small
+    hd, ps, ctx = 64, 16, 700
+    for far in (0, 15, 16, 463, 464, 699):
+        g = torch.Generator().manual_seed(far)
+        k = torch.randn(ctx, hd, generator=g) * 0.05
+        v = torch.randn(ctx, hd, generator=g)
+        q = torch.randn(1, hd, generator=g)
+        k[far] = q[0] * 4.0
+        pages = torch.randperm(44, generator=g)[:44].int()
+        kc = torch.zeros(44, 1, ps, hd, device="cuda"); vc = torch.zeros_like(kc)
+        slots = torch.tensor([int(pages[p // ps]) * ps + p % ps for p in range(ctx)], dtype=torch.int32)
+        ops.kv_write(dev(torch.cat([k, v], 1)), 0, hd, kc, vc, dev(slots), 1, hd, ps)
+        out = torch.empty(1, hd, device="cuda")
+        ops.paged_attention_generic(dev(q), kc, vc, dev(pages[None, :]), dev(torch.zeros(1, dtype=torch.int32)),
+                                    dev(torch.tensor([ctx - 1], dtype=torch.int32)), out, 1, 1, hd, ps, 1 / 8.0)
+        p = torch.softmax((k.double() @ q[0].double()) / 8.0, 0)
+        assert p[far] > 0.99
+        assert (out.double().cpu()[0] - p @ v.double()).abs().max() < 1e-5
+
+
+def test_sampling(ops):
+    g = torch.Generator().manual_seed(0)
+    R, V = 7, 50257
+    logits = torch.randn(R, V, generator=g)
+    logits[2, 400] = logits[2, 9000] = 50.0                   # a tie: the first wins
+    logits[3, 0] = 60.0
+    logits[4, V - 1] = 60.0
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits), None, None, out)
+    exp = logits.argmax(-1)
+    exp[2] = 400
+    assert out.cpu().tolist() == exp.tolist()
+    from cbis_b200.sampling import request_key
+    temps = torch.tensor([0.8, 0.0, 1.3, 0.5, 2.0, 0.05, 1.0])
+    keys = torch.tensor([request_key(77, r, 5 + r) for r in range(R)], dtype=torch.int64)
+    ops.sample(dev(logits), dev(temps), dev(keys), out)
+    for r in range(R):
+        scores = plain_gpt.perturbed_scores(logits[r].numpy(), float(temps[r]), 77, r, 5 + r)
+        assert scores[out[r].item()] >= scores.max() - 1e-4   # 32-bit logs against the plain 64-bit ones
+    # a padded row stride
+    wide = torch.randn(3, 40, generator=g)
+    ops.sample(dev(wide)[:, :33], None, None, out[:3])
+    assert out[:3].cpu().tolist() == wide[:, :33].argmax(-1).tolist()
+
+
+def test_sampling_follows_the_softmax(ops):
+    from cbis_b200.sampling import request_key
+    logits = torch.tensor([1.0, 0.0, -1.0, 0.5, -30.0])
+    n = 6000
+    keys = torch.tensor([request_key(1, 2, i) for i in range(n)], dtype=torch.int64)
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    ops.sample(dev(logits.repeat(n, 1)), dev(torch.full((n,), 0.7)), dev(keys), out)
+    counts = np.bincount(out.cpu().numpy(), minlength=5) / n
+    p = torch.softmax(logits / 0.7, 0).numpy()
+    assert np.abs(counts - p).max() < 0.025
+    exp = [plain_gpt.sample(logits.numpy(), 0.7, 1, 2, i) for i in range(200)]
+    assert out[:200].cpu().tolist() == exp
