@@ -1,0 +1,271 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Cerebras-GPT-1.3B shapes (random weights).
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+One "step" is one decode step of the whole batch.  The default run has the layer sizes of
+the 1.3B configuration, bfloat16, a batch of 8 requests with 1,024-token prompts decoded
+towards the context length 2,048.  It prints ONE JSON line:
+
+* ``value``: decoded tokens per second, timed on the device with CUDA events around K replays
+  of the captured decode step (model, argmax and the move to the next position all on the
+  device);
+* ``e2e``: the same through the Python entry point (``Engine.step``: scheduler, packed inputs
+  copied from pinned host memory, sampled tokens read back every step);
+* ``prefill``: one 2,048-token prompt in one step, tokens per second and the fraction of the
+  bf16 matrix peak its flops reach;
+* ``roofline``: bytes a decode step has to read (every weight once and the cache of the live
+  requests) over its time, against the measured copy bandwidth;
+* ``points``: decode at batch 1 and 64.
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists.  This engine runs on one
+GPU: with --gpus N > 1 it says so and exits with status 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Cerebras-GPT-1.3B layer sizes (GPT2LMHeadModel)
+CONFIG_1_3B = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=24, n_embd=2048, n_head=16,
+                   n_inner=8192, vocab_size=50257, n_positions=2048, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in d:
+                out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+            return out
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64, prefill and e2e")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a CMake C++/CUDA project without setup.py or pyproject.toml: pip cannot "
+                          "install it offline; its sizes are compile-time constants (d=256, L=4) built for sm_89"}))
+        return 0
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (single-GPU tier)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+
+    torch.cuda.set_device(0)
+    cfgd = dict(CONFIG_1_3B)
+    n_layer_config = cfgd["n_layer"]
+    if args.layers:
+        cfgd["n_layer"] = args.layers
+    P = cfgd["n_positions"]
+    K, W, B, PL = args.steps, args.warmup, args.batch, args.prompt_len
+    K = max(1, min(K, P - PL - W - 20))
+    pk = peaks()
+    max_b = B if args.skip_points else max(B, 64)
+    eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size,
+                                max_tokens=max_b * P, max_num_seqs=max_b, max_batched_tokens=2048,
+                                prefill_chunk=2048)
+    model, runner, mgr = eng.model, eng.runner, eng.pool.manager
+    V = cfgd["vocab_size"]
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(n, length):
+        return torch.randint(0, V, (n, length), generator=gen).tolist()
+
+    def prefill_slots(ps):
+        """Prefills prompts through the step function (two per step); returns their slots."""
+        slots = [eng.open_request(i) for i in range(len(ps))]
+        per = max(1, 2048 // len(ps[0]))
+        for i in range(0, len(ps), per):
+            eng.forward_step([StepEntry(slots[j], 0, ps[j], []) for j in range(i, min(i + per, len(ps)))])
+        return slots
+
+    def decode_device(batch, steps, warm):
+        """tokens/s of `steps` captured decode steps after `warm` untimed ones; also ms/step, launches/step."""
+        ps = prompts(batch, PL)
+        slots = prefill_slots(ps)
+        for s in slots:
+            assert mgr.append(s, warm + steps + 2)
+        ops.reset_launch_count()
+        loop = runner.decode_loop([StepEntry(s, PL, [1], [0]) for s in slots])
+        per_step = ops.launch_count() // 2          # the loop ran its step twice: warm-up and capture
+        loop.run(warm)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loop.run(steps)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        for s in slots:
+            eng.close_request(s)
+        del loop
+        return batch * steps / (ms / 1e3), ms / steps, per_step
+
+    # ---- main measurement: decode at the default batch, clocks sampled meanwhile -------------
+    sampler = ClockSampler()
+    sampler.start()
+    value, ms_per_step, launches_per_step = decode_device(B, K, W)
+    clocks = sampler.stop()
+    ctx_mean = PL + 1 + W + K / 2.0
+    step_bytes = model.weight_bytes() + B * ctx_mean * eng.pool.bytes_per_token()
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    result = {
+        "metric": "decode tokens/s (Cerebras-GPT-1.3B shapes, batch 8, context 1024->2048)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
+        "impl": "b200",
+        "config": {"model": "Cerebras-GPT-1.3B shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"],
+                   "n_layer_config": n_layer_config, "n_embd": cfgd["n_embd"], "n_head": cfgd["n_head"],
+                   "n_inner": cfgd["n_inner"], "vocab_size": V, "n_positions": P, "activation": "gelu",
+                   "tied_head": True, "global_batch": B, "prompt_len": PL, "seq_len": P,
+                   "page_size": args.page_size, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2: every step reads all weights (2.6 GB) and the live cache"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"],
+                     "bytes_per_step": int(step_bytes)},
+        "clocks": clocks,
+        "gpu_launches": int(launches_per_step * K),
+    }
+
+    if not args.skip_points:
+        # ---- prefill of 2,048 tokens in one step ------------------------------------------------
+        T = 2048
+        toks = prompts(1, T)[0]
+        times = []
+        for it in range(3 + 5):
+            slot = eng.open_request(1000 + it)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.forward_step([StepEntry(slot, 0, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+            eng.close_request(slot)
+        ms = statistics.median(times)
+        d, F, L = cfgd["n_embd"], cfgd["n_inner"], cfgd["n_layer"]
+        flops = L * (2 * T * (3 * d * d + d * d + 2 * d * F) + 2 * T * T * d) + 2 * d * V
+        result["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
+                             "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                             "flops": int(flops), "peak_tflops": pk["bf16_tflops"], "of": pk["source"]}
+        # ---- decode at batch 1 and 64 -----------------------------------------------------------
+        pts = {}
+        for b in (1, 64):
+            v, _, _ = decode_device(b, min(K, 256), W)
+            pts[f"decode_b{b}"] = round(v, 1)
+        result["points"] = pts
+        # ---- end to end through the Python entry point -------------------------------------------
+        ps = prompts(B, PL)
+        n_new = W + K + 16                      # no request ends inside the timed region
+        for p in ps:
+            eng.add_request(p, cb.SamplingParams(max_new_tokens=n_new))
+        while not all_decoding(eng, B):
+            eng.step()
+        for _ in range(W):
+            eng.step()
+        torch.cuda.synchronize()
+        tokens_before = eng.tokens_run
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(K):
+            eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        steps_e2e, tokens_e2e = K, eng.tokens_run - tokens_before
+        while eng.has_unfinished():
+            eng.step()
+        result["e2e"] = {"value": round(tokens_e2e / wall, 1), "unit": "tokens/s", "steps": steps_e2e,
+                         "ms_per_step": round(wall * 1e3 / steps_e2e, 4),
+                         "h2d_bytes_per_step": int(runner.bytes_per_step_h2d()), "d2h_bytes_per_step": 4 * B,
+                         "device_ms_per_step": round(e0.elapsed_time(e1) / steps_e2e, 4)}
+    print(json.dumps(result))
+    return 0
+
+
+def all_decoding(eng, batch):
+    """True once every request of the batch has had its prompt run (each step then feeds one token each)."""
+    return eng.scheduler.num_running() == batch and eng.last_step_tokens == batch
+
+
+if __name__ == "__main__":
+    sys.exit(main())

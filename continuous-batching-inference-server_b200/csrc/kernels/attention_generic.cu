@@ -48,7 +48,12 @@ __global__ void paged_attention_generic_kernel(
   const int row = w / n_head, h = w % n_head;
   const int hk = h / (n_head / n_kv_head);
   const int pos = positions[row];
-  const int* bt = block_table + (size_t)row_seq[row] * max_blocks;
+  const int seq = row_seq[row];
+  if (seq < 0) {  // a padding row of a fixed-size batch
+    for (int dim = lane; dim < hd; dim += 32) from_f32(out[(size_t)row * out_ld + h * hd + dim], 0.f);
+    return;
+  }
+  const int* bt = block_table + (size_t)seq * max_blocks;
   const int kend = pos + 1;
   const int kstart = window > 0 ? max(0, kend - window) : 0;
 

@@ -57,6 +57,7 @@ class Engine:
         self._next_id = 0
         self.steps = 0
         self.tokens_run = 0
+        self.last_step_tokens = 0
 
     # ---- construction from random weights --------------------------------------
     @classmethod
@@ -105,9 +106,10 @@ class Engine:
         for slot in self.scheduler.take_new_slots():
             self.pool.clear_state(slot)
         entries = [StepEntry(p.slot, p.start, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, borrow=True)
         self.steps += 1
-        self.tokens_run += sum(len(p.tokens) for p in plan)
+        self.last_step_tokens = sum(len(p.tokens) for p in plan)
+        self.tokens_run += self.last_step_tokens
         sampling = [p for p in plan if p.sample]
         if not sampling:
             return []

@@ -1,16 +1,39 @@
-"""Chooses the attention kernel for the rows of a step.
+"""Chooses the attention kernels for the rows of a step, and stores the step's keys and values.
 
 Rows of one-token segments (decoding) come first, the rows of longer segments (portions of
 prompts) after them, so each kind is one run of rows.  All kernels read the same pages and
-keep the same contract: the query at position p sees the keys of its own request up to p.
+keep the same contract: the query at position p sees the keys of its own request up to p
+(inside the window, if the mixer has one).
+
+* bfloat16, head size a multiple of 8, decoding rows: the split-KV decode kernel, which also
+  stores the current token's key and value;
+* everything else: the general kernel, after the cache-write kernel.
 """
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 
 
 def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
-    q = qkv[:, :mixer.d_q]
-    ops.paged_attention_generic(q, cache.k, cache.v, view.block_table, ctx.row_seq, ctx.positions, out,
-                                mixer.n_head, mixer.n_kv_head, mixer.head_dim, cache.page_size, mixer.scale,
-                                mixer.window)
+    nd = ctx.n_decode
+    T = ctx.n_rows
+    hd, ps = mixer.head_dim, cache.page_size
+    k_off, v_off = mixer.d_q, mixer.d_q + mixer.d_kv
+    fast_decode = qkv.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nd > 0
+    first_general = nd if fast_decode else 0
+    if fast_decode:
+        limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+        nsplit = ops.decode_splits(nd, mixer.n_head, limit)
+        scratch = ctx.decode_scratch(nd * mixer.n_head * nsplit * (hd + 2)) if nsplit > 1 else None
+        ops.paged_decode_bf16(qkv[:nd], k_off if mixer.own_kv else -1, v_off if mixer.own_kv else -1, cache.k, cache.v,
+                              view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, out[:nd], scratch,
+                              mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale, mixer.window, nsplit)
+    if first_general < T:
+        r = slice(first_general, T)
+        if mixer.own_kv:
+            ops.kv_write(qkv[r], k_off, v_off, cache.k, cache.v, view.slot_mapping[r], mixer.n_kv_head, hd, ps)
+        ops.paged_attention_generic(qkv[r, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[r],
+                                    ctx.positions[r], out[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                                    mixer.window)

@@ -64,7 +64,9 @@ class StepContext:
         self.max_seg_rows = 0
         self.max_ctx = 0
         self.pool: Optional[CachePool] = None
-        self.scratch: Dict[str, torch.Tensor] = {}
+        self.runner = None
+        self.fixed_shapes = False              # the step is being captured for replay: no size may depend on this batch
+        self.max_positions = 0
 
     def layer_cache(self, li: int):
         return self.pool.layer_cache.get(li)
@@ -73,7 +75,11 @@ class StepContext:
         return self.pool.state.get(li)
 
     def attention(self, mixer, qkv, cache, view, out):
+        """Stores this step's keys/values of ``mixer`` (if it keeps its own) and attends over the pages."""
         run_attention(self, mixer, qkv, cache, view, out)
+
+    def decode_scratch(self, n_floats: int) -> torch.Tensor:
+        return self.runner.scratch(n_floats)
 
 
 class ModelRunner:
@@ -105,6 +111,17 @@ class ModelRunner:
         self._dev = torch.zeros(off, dtype=torch.int32, device=self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = None    # event after the last host->device copy of the packed buffer
+        # decode-only steps replay a captured CUDA graph unless a part reads device values on the host
+        self.use_graphs = all(getattr(part, "capturable", True)
+                              for layer in model.layers for _, part in layer.parts())
+        self._graphs: Dict[int, tuple] = {}      # rows of a decode-only step -> (graph, context, logits)
+        worst = 0
+        for layer in model.layers:
+            m = layer.mixer
+            if hasattr(m, "n_head") and hasattr(m, "head_dim"):
+                worst = max(worst, S * m.n_head * 32 * (m.head_dim + 2))
+        self._scratch = torch.empty(max(worst, 1), dtype=torch.float32, device=self.device)
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------
     def _dev_view(self, name, n=None):
@@ -115,7 +132,19 @@ class ModelRunner:
         o, full = self._layout[name]
         return self._host_np[o:o + (full if n is None else n)]
 
-    def validate(self, entries: Sequence[StepEntry]) -> None:
+    def bytes_per_step_h2d(self) -> int:
+        """Bytes of the packed step description copied from pinned host memory every step."""
+        return self._host.numel() * 4
+
+    def scratch(self, n_floats: int) -> torch.Tensor:
+        """Float32 scratch shared by the kernels of a step (split-KV partial results)."""
+        if n_floats > self._scratch.numel():
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("kernel scratch would have to grow during graph capture")
+            self._scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
+        return self._scratch
+
+    def validate(self, entries: Sequence[StepEntry], reserved_ahead: bool = False) -> None:
         spec, mgr = self.model.spec, self.pool.manager
         if not entries:
             raise StepError("a step needs at least one entry")
@@ -137,7 +166,9 @@ class ModelRunner:
             if e.start < 0 or e.start + n > spec.max_positions:
                 raise StepError(f"slot {e.slot}: positions {e.start}..{e.start + n - 1} exceed the model's "
                                 f"{spec.max_positions} positions")
-            if mgr.length(e.slot) != e.start + n:
+            if reserved_ahead and mgr.length(e.slot) >= e.start + n:
+                pass
+            elif mgr.length(e.slot) != e.start + n:
                 raise StepError(f"slot {e.slot}: the cache holds room for {mgr.length(e.slot)} tokens, the step "
                                 f"brings tokens {e.start}..{e.start + n - 1}")
             lo, hi = min(e.tokens), max(e.tokens)
@@ -148,9 +179,14 @@ class ModelRunner:
                 if not 0 <= w < n:
                     raise StepError(f"slot {e.slot}: wanted place {w} outside its {n} tokens")
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Packs the step into the host buffer, copies it over, returns the views."""
-        self.validate(entries)
+    def build_context(self, entries: Sequence[StepEntry], pad_rows: int = 0, all_logits: bool = False,
+                      reserved_ahead: bool = False) -> StepContext:
+        """Packs the step into the host buffer, copies it over, returns the views.
+
+        ``pad_rows`` > 0 (decode-only steps): the step is laid out for exactly that many rows and
+        segments; rows beyond the entries are padding (segment -1: no cache write, zero attention
+        output).  ``all_logits``: every row's logits, whatever the entries want."""
+        self.validate(entries, reserved_ahead)
         if self._copied is not None:
             self._copied.synchronize()   # the last step's copy must have left the pinned buffer
         mgr, pool = self.pool.manager, self.pool
@@ -173,7 +209,17 @@ class ModelRunner:
             seg_slot[s], seg_start[s], seg_ctx[s] = e.slot, e.start, e.start + n
             r += n
             cu[s + 1] = r
-        want_rows = [row0_of_entry[ei] + w for ei, e in enumerate(entries) for w in e.want]
+        n_real_rows, n_real_segs = T, S
+        if pad_rows:
+            assert all(len(e.tokens) == 1 for e in entries) and pad_rows >= S
+            for name, fill in (("tokens", 0), ("positions", 0), ("row_seq", -1)):
+                self._host_view(name, pad_rows)[T:] = fill
+            for name in ("seg_slot", "seg_start", "seg_ctx"):
+                self._host_view(name, pad_rows)[S:] = 0
+            self._host_view("cu_rows", pad_rows + 1)[:] = np.minimum(np.arange(pad_rows + 1), T)
+            T = S = pad_rows
+        want_rows = (list(range(T)) if all_logits
+                     else [row0_of_entry[ei] + w for ei, e in enumerate(entries) for w in e.want])
         R = len(want_rows)
         if R:
             self._host_view("logit_rows", R)[:] = np.asarray(want_rows, dtype=np.int32)
@@ -181,6 +227,9 @@ class ModelRunner:
             ps, mb = pool.page_size, pool.max_blocks(g)
             sm = self._host_view(f"slot_mapping{g}", T)
             bt = self._host_view(f"block_table{g}", S * mb).reshape(S, mb)
+            if pad_rows:
+                sm[n_real_rows:] = -1
+                bt[n_real_segs:] = -1
             for s, ei in enumerate(order):
                 e = entries[ei]
                 table = np.asarray(mgr.block_table(e.slot, g), dtype=np.int32)
@@ -195,14 +244,15 @@ class ModelRunner:
 
         ctx = StepContext()
         ctx.dtype, ctx.pool, ctx.error_flag = self.model.dtype, pool, self.error_flag
+        ctx.runner, ctx.max_positions, ctx.fixed_shapes = self, self.model.spec.max_positions, bool(pad_rows)
         ctx.n_rows, ctx.n_segments, ctx.n_logit_rows = T, S, R
-        ctx.n_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        ctx.n_decode = T if pad_rows else sum(1 for e in entries if len(e.tokens) == 1)
         ctx.tokens, ctx.positions, ctx.row_seq = (self._dev_view(n, T) for n in ("tokens", "positions", "row_seq"))
         ctx.seg_slot, ctx.seg_start, ctx.seg_ctx = (self._dev_view(n, S) for n in ("seg_slot", "seg_start", "seg_ctx"))
         ctx.cu_rows = self._dev_view("cu_rows", S + 1)
         ctx.logit_rows = self._dev_view("logit_rows", R)
-        ctx.host_seg_rows = [len(entries[ei].tokens) for ei in order]
-        ctx.host_seg_ctx = [entries[ei].start + len(entries[ei].tokens) for ei in order]
+        ctx.host_seg_rows = [len(entries[ei].tokens) for ei in order] + [1] * (S - n_real_segs)
+        ctx.host_seg_ctx = [entries[ei].start + len(entries[ei].tokens) for ei in order] + [0] * (S - n_real_segs)
         ctx.max_seg_rows, ctx.max_ctx = max(ctx.host_seg_rows), max(ctx.host_seg_ctx)
         for g in range(self._n_groups):
             mb = pool.max_blocks(g)
@@ -210,10 +260,86 @@ class ModelRunner:
                                         self._dev_view(f"slot_mapping{g}", T), mb))
         return ctx
 
+    def _bucket(self, n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return min(b, self.max_seqs)
+
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
         """Runs one step; returns float32 logits ``[wanted, vocab]`` on the device, in the order
         of the entries and of each entry's ``want``.  The cache manager must already hold room
-        for the step's tokens (``manager.append``)."""
+        for the step's tokens (``manager.append``).  With ``borrow`` the result may be a buffer
+        that the next step overwrites (no copy).
+
+        A step of single tokens only (decoding) is captured once per batch-size bucket as a CUDA
+        graph and replayed, so its few hundred launches cost one; any other step runs launch by
+        launch."""
+        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
+            out = self._decode_step_graph(entries)
+            return out if borrow else out.clone()
         ctx = self.build_context(entries)
         return self.model.forward(ctx)
+
+    def _decode_step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        rows = self._bucket(len(entries))
+        ctx = self.build_context(entries, pad_rows=rows, all_logits=True)
+        if rows not in self._graphs:
+            self.model.forward(ctx)                       # warm-up outside the capture (writes the same cache values)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            self._graphs[rows] = (graph, logits)
+        graph, logits = self._graphs[rows]
+        graph.replay()
+        self.graph_replays += 1
+        want = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(want) == rows:
+            return logits
+        return logits[torch.tensor(want, dtype=torch.long, device=logits.device)] if want else logits[:0]
+
+    @torch.no_grad()
+    def decode_loop(self, entries: Sequence[StepEntry]) -> "DecodeLoop":
+        """A run of greedy decode steps that never leaves the device: see ``DecodeLoop``."""
+        return DecodeLoop(self, entries)
+
+
+class DecodeLoop:
+    """Greedy decoding of a fixed batch for many steps without the host in the loop.
+
+    One CUDA graph holds a whole step: the model, the argmax over each row's logits, and the
+    kernels that move every row on (the chosen token becomes the input, position + 1, the token
+    slot from the request's block table).  The caller reserves the pages of all steps beforehand
+    (``manager.append(slot, n_steps)``), so the block tables do not change while it runs."""
+
+    def __init__(self, runner: ModelRunner, entries: Sequence[StepEntry]):
+        self.runner = runner
+        n = len(entries)
+        ctx = runner.build_context(entries, pad_rows=n, all_logits=True, reserved_ahead=True)
+        self.ctx = ctx
+        self.sampled = torch.zeros(n, dtype=torch.int32, device=runner.device)
+        self._one_step()                                  # warm-up, also moves the rows on by one
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._one_step()
+        self.steps_done = 1
+
+    def _one_step(self):
+        ctx, r = self.ctx, self.runner
+        logits = r.model.forward(ctx)
+        ops.sample(logits, None, None, self.sampled)
+        ops.decode_advance(ctx.tokens, ctx.positions, ctx.seg_start, ctx.seg_ctx, self.sampled, ctx.n_rows)
+        for g, view in enumerate(ctx.groups):
+            ops.slots_from_table(ctx.positions, ctx.row_seq, view.block_table, r.pool.page_size, view.slot_mapping,
+                                 ctx.n_rows)
+
+    def run(self, steps: int) -> None:
+        for _ in range(steps):
+            self.graph.replay()
+        self.steps_done += steps
+
+    def last_tokens(self) -> List[int]:
+        return self.sampled.cpu().tolist()

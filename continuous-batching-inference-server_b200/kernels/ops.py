@@ -26,8 +26,23 @@ class KernelError(RuntimeError):
     pass
 
 
-def _check(status: int, what: str, detail: str = "") -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches of this package since the last reset (captured launches count once, at capture)."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def _check(status: int, what: str, detail: str = "", launches: int = 1) -> None:
+    global _launches
     if status == 0:
+        _launches += launches
         return
     if status < 0:
         raise KernelError(f"{what}: {_STATUS.get(status, 'error %d' % status)}{(' (' + detail + ')') if detail else ''}")
@@ -161,6 +176,48 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
         _ptr(row_seq), _ptr(positions), _ptr(out), c_int(out.stride(0)), c_int(T), c_int(n_head), c_int(n_kv_head),
         c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(dtype_code(q.dtype)), _stream())
     _check(st, "paged_attention_generic", f"T={T} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+
+
+def decode_splits(rows: int, n_head: int, max_context: int) -> int:
+    """How many ways the decode kernel splits a request's keys: enough blocks for about four per SM,
+    never pieces under 64 keys."""
+    want = -(-4 * 148 // max(1, rows * n_head))
+    return max(1, min(want, 32, max(1, max_context // 64)))
+
+
+def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out,
+                      scratch, n_head, n_kv_head, head_dim, page_size, scale, window, nsplit):
+    """Decode attention (one query per row) with the keys split ``nsplit`` ways; with ``k_off >= 0`` the
+    current token's key/value are taken from ``qkv`` and stored into the cache by the same kernel."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out, scratch)
+    rows = qkv.shape[0]
+    if head_dim % 8 or head_dim > 256:
+        raise KernelError(f"decode attention: head_dim={head_dim} must be a multiple of 8, at most 256")
+    assert qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    need = rows * n_head * nsplit * (head_dim + 2) if nsplit > 1 else 0
+    assert need == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need)
+    st = kernels().cbis_paged_decode_bf16(
+        _ptr(qkv), c_int(qkv.stride(0)), c_int(k_off), c_int(v_off), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+        c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions), _ptr(slot_mapping), _ptr(out),
+        c_int(out.stride(0)), _ptr(scratch), c_int(rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim),
+        c_int(page_size), c_float(scale), c_int(window), c_int(nsplit), _stream())
+    _check(st, "paged_decode_bf16", f"rows={rows} heads={n_head}/{n_kv_head} head_dim={head_dim} splits={nsplit}",
+           launches=2 if nsplit > 1 else 1)
+
+
+def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):
+    """tokens <- sampled, positions/seg_start/seg_ctx += 1 for the first n rows (all on the device)."""
+    st = kernels().cbis_decode_advance(_ptr(tokens), _ptr(positions), _ptr(seg_start), _ptr(seg_ctx), _ptr(sampled),
+                                       c_int(n), _stream())
+    _check(st, "decode_advance")
+
+
+def slots_from_table(positions, row_seq, block_table, page_size, slot_mapping, n):
+    """slot_mapping[r] = token slot of positions[r] by the request's block table (-1 for padding rows)."""
+    st = kernels().cbis_slots_from_table(_ptr(positions), _ptr(row_seq), _ptr(block_table),
+                                         c_int(block_table.shape[1]), c_int(page_size), _ptr(slot_mapping), c_int(n),
+                                         _stream())
+    _check(st, "slots_from_table")
 
 
 def sample(logits, temperature, keys, out):

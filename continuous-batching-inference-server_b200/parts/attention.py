@@ -52,11 +52,8 @@ class PagedAttention(Mixer):
             raise RuntimeError("attention needs a cache: its own or the layer's it reads")
         qkv = ops.linear(h, self.w_qkv, self.b_qkv)
         view = ctx.groups[cache.group]
-        if self.own_kv:
-            ops.kv_write(qkv, self.d_q, self.d_q + self.d_kv, cache.k, cache.v, view.slot_mapping,
-                         self.n_kv_head, self.head_dim, cache.page_size)
         out = torch.empty((ctx.n_rows, self.d_q), dtype=qkv.dtype, device=qkv.device)
-        ctx.attention(self, qkv, cache, view, out)
+        ctx.attention(self, qkv, cache, view, out)      # stores this step's k, v (if own_kv), then attends
         return Delta(ops.linear(out, self.w_o, None, None, out_dtype=torch.float32), self.b_o)
 
 

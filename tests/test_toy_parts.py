@@ -16,6 +16,7 @@ def register_toy():
 
     class DecayingSum(Mixer):
         """state <- decay * state + h_t ; out_t = state @ W.  The state lives in the request's slot."""
+        capturable = False        # forward() reads the slots on the host
 
         def __init__(self, width, decay):
             self.width, self.decay = width, decay
