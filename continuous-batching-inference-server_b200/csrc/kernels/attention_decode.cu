@@ -1,5 +1,6 @@
 // Decode attention over the paged cache for bfloat16: one query token per request, keys split
-// over several blocks (split-KV), partial softmax states merged by a second kernel.
+// over several blocks (split-KV); the block of a (row, head) that finishes last merges the
+// partial softmax states.
 //
 // The reference runs one warp per (row, head) that walks the keys one after the other
 // (kernels/attention.cu:57-98): at decode that is n_head warps per request and a chain of
@@ -33,16 +34,20 @@ constexpr int DEC_U = 4;  // keys in flight per lane group
 // part: [rows][n_head][nsplit][hd + 2] floats: acc[hd] (not normalised), max, sum.
 template <int LPK>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-paged_decode_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int k_off, int v_off,
-                         __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
-                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq,
-                         const int* __restrict__ positions, const int* __restrict__ slot_mapping,
-                         __nv_bfloat16* __restrict__ out, int out_ld, float* __restrict__ part, int n_head,
-                         int n_kv_head, int hd, int ps, float scale, int window, int nsplit) {
+paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
+                         __nv_bfloat16* kc, __nv_bfloat16* vc,
+                         const int* block_table, int max_blocks, const int* row_seq,
+                         const int* positions, const int* slot_mapping,
+                         __nv_bfloat16* __restrict__ out, int out_ld, float* part,
+                         unsigned int* counters, int n_head, int n_kv_head, int hd, int ps, float scale,
+                         int window, int nsplit) {
   constexpr int G = 32 / LPK;             // key groups per warp
   constexpr int NW = DEC_WARPS * G;       // key workers per block
   __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
   __shared__ float sm_acc[DEC_WARPS][256];
+  __shared__ bool is_last;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int seq = row_seq[row];
@@ -76,33 +81,44 @@ paged_decode_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int k_of
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
   const int wkr = warp * G + group;
+  uint4 knext[DEC_U], vnext[DEC_U];
+  // Loads of the keys/values base + u*NW + wkr (u < DEC_U); the current token's pair comes from qkv and is stored.
+  auto fetch = [&](int base, uint4* kk, uint4* vv) {
+#pragma unroll
+    for (int u = 0; u < DEC_U; ++u) {
+      const int j = base + u * NW + wkr;
+      kk[u] = make_uint4(0, 0, 0, 0);
+      vv[u] = make_uint4(0, 0, 0, 0);
+      if (j < ke && active) {
+        if (fused && j == pos) {
+          kk[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + k_off + hk * hd + sub * 8);
+          vv[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + v_off + hk * hd + sub * 8);
+          const int slot = slot_mapping[row];
+          if (slot >= 0) {
+            const size_t dst = (((size_t)(slot / ps) * n_kv_head + hk) * ps + (slot % ps)) * hd + sub * 8;
+            *reinterpret_cast<uint4*>(kc + dst) = kk[u];
+            *reinterpret_cast<uint4*>(vc + dst) = vv[u];
+          }
+        } else {
+          const int page = bt[j / ps];
+          const size_t src = (((size_t)page * n_kv_head + hk) * ps + (j % ps)) * hd + sub * 8;
+          kk[u] = *reinterpret_cast<const uint4*>(kc + src);
+          vv[u] = *reinterpret_cast<const uint4*>(vc + src);
+        }
+      }
+    }
+  };
+  if (ks < ke) fetch(ks, knext, vnext);
   for (int base = ks; base < ke; base += NW * DEC_U) {
     uint4 kraw[DEC_U], vraw[DEC_U];
     bool valid[DEC_U];
 #pragma unroll
     for (int u = 0; u < DEC_U; ++u) {
-      const int j = base + u * NW + wkr;
-      valid[u] = j < ke;
-      kraw[u] = make_uint4(0, 0, 0, 0);
-      vraw[u] = make_uint4(0, 0, 0, 0);
-      if (valid[u] && active) {
-        if (fused && j == pos) {
-          kraw[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + k_off + hk * hd + sub * 8);
-          vraw[u] = *reinterpret_cast<const uint4*>(qkv + (size_t)row * ld + v_off + hk * hd + sub * 8);
-          const int slot = slot_mapping[row];
-          if (slot >= 0) {
-            const size_t dst = (((size_t)(slot / ps) * n_kv_head + hk) * ps + (slot % ps)) * hd + sub * 8;
-            *reinterpret_cast<uint4*>(kc + dst) = kraw[u];
-            *reinterpret_cast<uint4*>(vc + dst) = vraw[u];
-          }
-        } else {
-          const int page = bt[j / ps];
-          const size_t src = (((size_t)page * n_kv_head + hk) * ps + (j % ps)) * hd + sub * 8;
-          kraw[u] = *reinterpret_cast<const uint4*>(kc + src);
-          vraw[u] = *reinterpret_cast<const uint4*>(vc + src);
-        }
-      }
+      kraw[u] = knext[u];
+      vraw[u] = vnext[u];
+      valid[u] = base + u * NW + wkr < ke;
     }
+    if (base + NW * DEC_U < ke) fetch(base + NW * DEC_U, knext, vnext);  // the next batch is in flight during the math
     float s[DEC_U];
 #pragma unroll
     for (int u = 0; u < DEC_U; ++u) {
@@ -188,32 +204,37 @@ paged_decode_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, int k_of
       }
     }
   }
-}
-
-__global__ void decode_combine_kernel(const float* __restrict__ part, const int* __restrict__ row_seq,
-                                      __nv_bfloat16* __restrict__ out, int out_ld, int n_head, int hd, int nsplit) {
-  const int row = blockIdx.x, h = blockIdx.y;
-  if (row_seq[row] < 0) return;  // the decode kernel wrote zeros
+  if (nsplit == 1) return;
+  // The block of this (row, head) that finishes last merges the splits (and sets the counter back to zero).
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&counters[row * n_head + h], 1u) == (unsigned)nsplit - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   const float* p = part + ((size_t)row * n_head + h) * nsplit * (hd + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p[(size_t)s * (hd + 2) + hd]);
+  float Mx = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) Mx = fmaxf(Mx, __ldcg(p + (size_t)s * (hd + 2) + hd));
   for (int t = threadIdx.x; t < hd; t += blockDim.x) {
-    float L = 0.f, v = 0.f;
+    float Ls = 0.f, v = 0.f;
     for (int s = 0; s < nsplit; ++s) {
       const float* ps_ = p + (size_t)s * (hd + 2);
-      const float ms = ps_[hd];
-      const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
-      L += ps_[hd + 1] * w;
-      v += ps_[t] * w;
+      const float ms = __ldcg(ps_ + hd);
+      const float w = ms > -INFINITY ? expf(ms - Mx) : 0.f;
+      Ls += __ldcg(ps_ + hd + 1) * w;
+      v += __ldcg(ps_ + t) * w;
     }
-    out[(size_t)row * out_ld + h * hd + t] = __float2bfloat16_rn(v / L);
+    out[(size_t)row * out_ld + h * hd + t] = __float2bfloat16_rn(v / Ls);
   }
+  if (threadIdx.x == 0) counters[row * n_head + h] = 0;
 }
 
 // After a decode step whose next tokens were chosen on the device: the chosen token becomes the
 // row's input, its position moves on by one, and so do the segment's first position and length.
 __global__ void decode_advance_kernel(int* tokens, int* positions, int* seg_start, int* seg_ctx,
-                                      const int* __restrict__ sampled, int n) {
+                                      const int* sampled, int n) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
   tokens[r] = sampled[r];
@@ -224,9 +245,11 @@ __global__ void decode_advance_kernel(int* tokens, int* positions, int* seg_star
 
 // slot_mapping[r] = page(position) * page_size + offset, from the request's block table; -1 for padding rows
 // and for positions whose page is not there.
-__global__ void slots_from_table_kernel(const int* __restrict__ positions, const int* __restrict__ row_seq,
-                                        const int* __restrict__ block_table, int max_blocks, int ps,
-                                        int* __restrict__ slot_mapping, int n) {
+__global__ void slots_from_table_kernel(const int* positions, const int* row_seq,
+                                        const int* block_table, int max_blocks, int ps,
+                                        int* slot_mapping, int n) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
   const int seq = row_seq[r], pos = positions[r];
@@ -242,7 +265,10 @@ __global__ void slots_from_table_kernel(const int* __restrict__ positions, const
 
 using namespace cbis;
 
-// Floats of scratch the decode kernel needs for `rows` rows when it splits the keys `nsplit` ways.
+// Scratch of the decode kernel for `rows` rows split `nsplit` ways: `part` holds
+// cbis_paged_decode_scratch_floats() floats of partial results; `counters` holds rows*n_head
+// unsigned ints that are zero before the first launch (every launch leaves them zero).  The two
+// are separate so that a region once used for partial results is never read as a counter.
 CBIS_EXPORT long long cbis_paged_decode_scratch_floats(int rows, int n_head, int hd, int nsplit) {
   return nsplit <= 1 ? 0 : (long long)rows * n_head * nsplit * (hd + 2);
 }
@@ -252,52 +278,44 @@ CBIS_EXPORT long long cbis_paged_decode_scratch_floats(int rows, int n_head, int
 CBIS_EXPORT int cbis_paged_decode_bf16(const void* qkv, int ld, int k_off, int v_off, void* kc, void* vc,
                                        const int* block_table, int max_blocks, const int* row_seq,
                                        const int* positions, const int* slot_mapping, void* out, int out_ld,
-                                       float* part, int rows, int n_head, int n_kv_head, int hd, int ps, float scale,
-                                       int window, int nsplit, void* stream) {
+                                       float* part, unsigned int* counters, int rows, int n_head, int n_kv_head,
+                                       int hd, int ps, float scale, int window, int nsplit, void* stream) {
   if (rows <= 0) return CBIS_OK;
   if (hd <= 0 || hd > 256 || hd % 8 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head || nsplit < 1)
     return CBIS_ERR_BAD_SIZE;
   if (ld % 8 || out_ld % 8 || (k_off >= 0 && (k_off % 8 || v_off % 8)) || ((uintptr_t)qkv & 15) || ((uintptr_t)kc & 15) ||
       ((uintptr_t)vc & 15))
     return CBIS_ERR_ALIGNMENT;
-  if (nsplit > 1 && part == nullptr) return CBIS_ERR_BAD_SIZE;
+  if (nsplit > 1 && (part == nullptr || counters == nullptr)) return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(rows, n_head, nsplit);
   const int chunks = hd / 8;
-#define CBIS_DEC(LPK)                                                                                               \
-  paged_decode_bf16_kernel<LPK><<<grid, DEC_WARPS * 32, 0, st>>>(                                                   \
-      (const __nv_bfloat16*)qkv, ld, k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, \
-      row_seq, positions, slot_mapping, (__nv_bfloat16*)out, out_ld, part, n_head, n_kv_head, hd, ps, scale, window, \
-      nsplit)
+  cudaError_t e;
+#define CBIS_DEC(LPK)                                                                                             \
+  e = launch_pdl(paged_decode_bf16_kernel<LPK>, grid, dim3(DEC_WARPS * 32), 0, st, (const __nv_bfloat16*)qkv, ld, \
+                 k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, block_table, max_blocks, row_seq, positions, \
+                 slot_mapping, (__nv_bfloat16*)out, out_ld, part, counters, n_head, n_kv_head, hd, ps, scale, window, \
+                 nsplit)
   if (chunks <= 2) CBIS_DEC(2);
   else if (chunks <= 4) CBIS_DEC(4);
   else if (chunks <= 8) CBIS_DEC(8);
   else if (chunks <= 16) CBIS_DEC(16);
   else CBIS_DEC(32);
 #undef CBIS_DEC
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  if (nsplit > 1) {
-    dim3 g2(rows, n_head);
-    decode_combine_kernel<<<g2, hd <= 64 ? 64 : 128, 0, st>>>(part, row_seq, (__nv_bfloat16*)out, out_ld, n_head, hd, nsplit);
-    e = cudaGetLastError();
-  }
   return (int)e;
 }
 
 CBIS_EXPORT int cbis_decode_advance(int* tokens, int* positions, int* seg_start, int* seg_ctx, const int* sampled,
                                     int n, void* stream) {
   if (n <= 0) return CBIS_OK;
-  decode_advance_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, positions, seg_start, seg_ctx,
-                                                                            sampled, n);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tokens,
+                         positions, seg_start, seg_ctx, sampled, n);
 }
 
 CBIS_EXPORT int cbis_slots_from_table(const int* positions, const int* row_seq, const int* block_table, int max_blocks,
                                       int ps, int* slot_mapping, int n, void* stream) {
   if (n <= 0) return CBIS_OK;
   if (ps <= 0) return CBIS_ERR_BAD_SIZE;
-  slots_from_table_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>(positions, row_seq, block_table,
-                                                                              max_blocks, ps, slot_mapping, n);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(slots_from_table_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, positions,
+                         row_seq, block_table, max_blocks, ps, slot_mapping, n);
 }

@@ -14,9 +14,11 @@ namespace cbis {
 // Row r of the step's projections goes to token slot slot_mapping[r] = page*page_size + offset
 // (reference: scatter_kv_kernel, kernels/attention.cu:7-19).  A negative slot writes nothing.
 template <typename TT>
-__global__ void kv_write_kernel(const TT* __restrict__ qkv, int ld, int k_off, int v_off, TT* __restrict__ kc,
-                                TT* __restrict__ vc, const int* __restrict__ slot_mapping, int n_kv_head,
+__global__ void kv_write_kernel(const TT* qkv, int ld, int k_off, int v_off, TT* kc,
+                                TT* vc, const int* slot_mapping, int n_kv_head,
                                 int hd, int ps) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int slot = slot_mapping[r];
   if (slot < 0) return;
@@ -38,10 +40,12 @@ __global__ void kv_write_kernel(const TT* __restrict__ qkv, int ld, int k_off, i
 // kernels/attention.cu:74-95, four keys at a time.  Lane i owns head dims i, i+32, ...
 template <typename TT, int NPER>
 __global__ void paged_attention_generic_kernel(
-    const TT* __restrict__ q, int q_ld, const TT* __restrict__ kc, const TT* __restrict__ vc,
-    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seq,
-    const int* __restrict__ positions, TT* __restrict__ out, int out_ld, int n_rows, int n_head, int n_kv_head,
+    const TT* q, int q_ld, const TT* kc, const TT* vc,
+    const int* block_table, int max_blocks, const int* row_seq,
+    const int* positions, TT* __restrict__ out, int out_ld, int n_rows, int n_head, int n_kv_head,
     int hd, int ps, float scale, int window) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= n_rows * n_head) return;
@@ -133,15 +137,12 @@ CBIS_EXPORT int cbis_kv_write(const void* qkv, int ld, int k_off, int v_off, voi
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
-    kv_write_kernel<float><<<T, threads, 0, st>>>((const float*)qkv, ld, k_off, v_off, (float*)kc, (float*)vc,
-                                                  slot_mapping, n_kv_head, hd, ps);
-  else if (dtype == CBIS_BF16)
-    kv_write_kernel<__nv_bfloat16><<<T, threads, 0, st>>>((const __nv_bfloat16*)qkv, ld, k_off, v_off,
-                                                          (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping,
-                                                          n_kv_head, hd, ps);
-  else
-    return CBIS_ERR_BAD_DTYPE;
-  return (int)cudaGetLastError();
+    return (int)launch_pdl(kv_write_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)qkv, ld, k_off, v_off,
+                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, ps);
+  if (dtype == CBIS_BF16)
+    return (int)launch_pdl(kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st, (const __nv_bfloat16*)qkv, ld,
+                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, ps);
+  return CBIS_ERR_BAD_DTYPE;
 }
 
 template <typename TT>
@@ -152,16 +153,17 @@ static int launch_generic(const void* q, int q_ld, const void* kc, const void* v
   const int warps = 4;
   const long long total = (long long)n_rows * n_head;
   const int blocks = (int)((total + warps - 1) / warps);
-#define CBIS_LAUNCH(NPER)                                                                                      \
-  paged_attention_generic_kernel<TT, NPER><<<blocks, warps * 32, 0, st>>>(                                     \
-      (const TT*)q, q_ld, (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, \
-      out_ld, n_rows, n_head, n_kv_head, hd, ps, scale, window)
+  cudaError_t e;
+#define CBIS_LAUNCH(NPER)                                                                                            \
+  e = launch_pdl(paged_attention_generic_kernel<TT, NPER>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
+                 (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, out_ld, n_rows, \
+                 n_head, n_kv_head, hd, ps, scale, window)
   if (hd <= 32) CBIS_LAUNCH(1);
   else if (hd <= 64) CBIS_LAUNCH(2);
   else if (hd <= 128) CBIS_LAUNCH(4);
   else CBIS_LAUNCH(8);
 #undef CBIS_LAUNCH
-  return (int)cudaGetLastError();
+  return (int)e;
 }
 
 CBIS_EXPORT int cbis_paged_attention_generic(const void* q, int q_ld, const void* kc, const void* vc,

@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 // Status codes returned by every launcher (0 = launched; CUDA errors are returned as they are, > 0).
 #define CBIS_OK 0
@@ -23,6 +24,54 @@
 #define CBIS_EXPORT extern "C" __attribute__((visibility("default")))
 
 namespace cbis {
+
+// Programmatic dependent launch: a kernel launched with launch_pdl may start while the kernel
+// before it in the stream still runs.  It first lets ITS successor start (pdl_trigger), may
+// fetch what no earlier kernel writes (weights), and calls pdl_wait before it touches anything
+// an earlier kernel produces: pdl_wait returns when the preceding kernels have finished and
+// their writes are visible.  Without the launch attribute both calls do nothing.
+// Pointers to anything an earlier kernel of the step may have written are NOT declared
+// `const __restrict__`: that lets the compiler read them through the non-coherent path
+// (ld.global.nc), whose cached lines may predate the writes when kernels overlap, and lets it
+// move the loads above the wait.  Only weights, biases and norm parameters are read that way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// 0 switches the launch attribute off (environment CBIS_PDL=0): kernels then run strictly one after the other.
+inline int pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("CBIS_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on;
+}
+
+// `after_kernel`: the operation before this launch in the stream is a kernel.  A kernel that
+// follows a copy or a graph launch (the first kernel of a step, the sampling kernel after a
+// replayed step) is launched without the attribute: it then starts only when everything before
+// it has finished.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after(bool after_kernel, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = after_kernel ? pdl_enabled() : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+  return launch_after(true, kernel, grid, block, smem, st, args...);
+}
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

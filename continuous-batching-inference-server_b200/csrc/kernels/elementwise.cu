@@ -7,9 +7,11 @@ namespace cbis {
 // x[r,:] = wte[tok[r],:] + wpe[pos[r],:]   (reference: kernels/elementwise.cu:7-17)
 // A token or position outside its table sets *err (1 = token, 2 = position) and gives a zero row.
 template <typename TT>
-__global__ void embed_pos_add_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+__global__ void embed_pos_add_kernel(const int* tokens, const int* positions,
                                      const TT* __restrict__ wte, const TT* __restrict__ wpe,
                                      float* __restrict__ out, int d, int vocab, int n_pos, int* err) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int tok = tokens[r];
   const int pos = positions[r];
@@ -39,13 +41,15 @@ __global__ void embed_pos_add_kernel(const int* __restrict__ tokens, const int* 
 // var is the centred, biased variance (the reference uses E[x^2]-mean^2, kernels/elementwise.cu:50).
 // The row is staged in shared memory (d floats), so x is read once.
 template <typename TD, typename TO>
-__global__ void add_layernorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+__global__ void add_layernorm_kernel(float* __restrict__ x, const TD* delta,
                                      const float* __restrict__ delta_bias, const float* __restrict__ gamma,
                                      const float* __restrict__ beta, float eps, TO* __restrict__ out,
-                                     const int* __restrict__ rows, int d) {
+                                     const int* rows, int d) {
   extern __shared__ float smem[];
   float* row = smem;          // d floats
   float* red = smem + d;      // 33 floats
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
   float* xrow = x + (size_t)s * d;
@@ -78,10 +82,26 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const TD* __restrict
 // x[m,n] = act(x[m,n] + bias[n]) in place (reference: add_bias_rowmajor kernels/linear.cu:6-12 + gelu_kernel).
 template <typename TT>
 __global__ void bias_act_kernel(TT* __restrict__ x, const float* __restrict__ bias, int act, size_t total, int n) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     float v = to_f32(x[i]);
     if (bias) v += bias[i % n];
     from_f32(x[i], activate(v, act));
+  }
+}
+
+// dst[m,n] = act(src[m,n] + bias[n]): the 32-bit sums of a matrix product become the stored
+// activations with one rounding.
+template <typename TO>
+__global__ void bias_act_out_kernel(const float* src, const float* __restrict__ bias, int act, TO* __restrict__ dst,
+                                    size_t total, int n) {
+  pdl_trigger();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = src[i];
+    if (bias) v += bias[i % n];
+    from_f32(dst[i], activate(v, act));
   }
 }
 
@@ -97,14 +117,12 @@ CBIS_EXPORT int cbis_embed_pos_add(const int* tokens, const int* positions, cons
   const int threads = d >= 1024 ? 256 : (d >= 256 ? 128 : 64);
   cudaStream_t st = (cudaStream_t)stream;
   if (table_dtype == CBIS_F32)
-    embed_pos_add_kernel<float><<<T, threads, 0, st>>>(tokens, positions, (const float*)wte, (const float*)wpe, out,
-                                                        d, vocab, n_pos, err);
-  else if (table_dtype == CBIS_BF16)
-    embed_pos_add_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(tokens, positions, (const __nv_bfloat16*)wte,
-                                                                (const __nv_bfloat16*)wpe, out, d, vocab, n_pos, err);
-  else
-    return CBIS_ERR_BAD_DTYPE;
-  return (int)cudaGetLastError();
+    return (int)launch_after(false, embed_pos_add_kernel<float>, dim3(T), dim3(threads), 0, st, tokens, positions,
+                           (const float*)wte, (const float*)wpe, out, d, vocab, n_pos, err);
+  if (table_dtype == CBIS_BF16)
+    return (int)launch_after(false, embed_pos_add_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st, tokens, positions,
+                           (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d, vocab, n_pos, err);
+  return CBIS_ERR_BAD_DTYPE;
 }
 
 template <typename TD, typename TO>
@@ -119,8 +137,8 @@ static int launch_add_layernorm(float* x, const void* delta, const float* delta_
     if (e != cudaSuccess) return (int)e;
   }
   const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-  kern<<<R, threads, smem, st>>>(x, (const TD*)delta, delta_bias, gamma, beta, eps, (TO*)out, rows, d);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, dim3(R), dim3(threads), smem, st, x, (const TD*)delta, delta_bias, gamma, beta, eps,
+                         (TO*)out, rows, d);
 }
 
 // delta_dtype / out_dtype: CBIS_F32 or CBIS_BF16.  delta, delta_bias and rows may be null.
@@ -149,10 +167,26 @@ CBIS_EXPORT int cbis_bias_act(void* x, const float* bias, int act, int M, int N,
   if (blocks > 148 * 16) blocks = 148 * 16;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
-    bias_act_kernel<float><<<(int)blocks, threads, 0, st>>>((float*)x, bias, act, total, N);
-  else if (dtype == CBIS_BF16)
-    bias_act_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, st>>>((__nv_bfloat16*)x, bias, act, total, N);
-  else
-    return CBIS_ERR_BAD_DTYPE;
-  return (int)cudaGetLastError();
+    return (int)launch_pdl(bias_act_kernel<float>, dim3((int)blocks), dim3(threads), 0, st, (float*)x, bias, act, total, N);
+  if (dtype == CBIS_BF16)
+    return (int)launch_pdl(bias_act_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, st, (__nv_bfloat16*)x,
+                           bias, act, total, N);
+  return CBIS_ERR_BAD_DTYPE;
+}
+
+CBIS_EXPORT int cbis_bias_act_out(const float* src, const float* bias, int act, void* dst, int M, int N, int dst_dtype,
+                                  void* stream) {
+  if (M <= 0 || N <= 0) return CBIS_OK;
+  const size_t total = (size_t)M * N;
+  const int threads = 256;
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dst_dtype == CBIS_F32)
+    return (int)launch_pdl(bias_act_out_kernel<float>, dim3((int)blocks), dim3(threads), 0, st, src, bias, act,
+                           (float*)dst, total, N);
+  if (dst_dtype == CBIS_BF16)
+    return (int)launch_pdl(bias_act_out_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, st, src, bias, act,
+                           (__nv_bfloat16*)dst, total, N);
+  return CBIS_ERR_BAD_DTYPE;
 }

@@ -1,0 +1,184 @@
+// Matrix product for few rows (decoding: M <= 64) in bfloat16 with 32-bit accumulation:
+//   C[M,N] = act(A[M,K] * W^T + bias),   W stored [N,K] (K contiguous), A [M,K]
+// At these sizes the product is bound by reading W once from HBM, so the kernel is built
+// around the weight stream: a block owns 8*NT output columns over the whole of K; its 8 warps
+// take the 32-wide K blocks in turn (warp w: blocks w, w+8, ...), so together they read each
+// weight row in long contiguous runs; every lane fetches 16 bytes of a weight row per block and
+// feeds them to the tensor cores as they come (mma.sync m16n8k16, the K order permuted alike
+// for both operands so that one 16-byte load is two fragments); the few rows of A come from
+// L1/L2.  The warps' partial sums are added in shared memory and bias and activation are
+// applied to the 32-bit sum before the one store.  The reference calls cublasSgemm and adds
+// the bias in a second kernel and the GELU in a third (kernels/linear.cu:15-34,
+// kernels/elementwise.cu:59-66).
+#include "common.cuh"
+
+namespace cbis {
+
+constexpr int SM_WARPS = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// MT: 16-row tiles of A (M <= 16*MT); NT: 8-column tiles of W per block; UNROLL: K blocks in flight per warp.
+template <int MT, int NT, int UNROLL, typename TO>
+__global__ void __launch_bounds__(SM_WARPS * 32)
+gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
+                    const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act) {
+  extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1]
+  constexpr int RS = NT * 8 + 1;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * (NT * 8);
+  const int nkb = (K + 31) / 32;
+
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+  const __nv_bfloat16* wrow[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int n = min(n0 + j * 8 + g, N - 1);  // rows past N are clamped; their columns are never stored
+    wrow[j] = W + (size_t)n * K + t * 8;
+  }
+  const __nv_bfloat16* arow[MT][2];
+  bool avalid[MT][2];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+      const int m = i * 16 + hlf * 8 + g;
+      avalid[i][hlf] = m < M;
+      arow[i][hlf] = A + (size_t)min(m, M - 1) * lda + t * 8;
+    }
+
+  pdl_trigger();
+  bool waited = false;
+  for (int kb0 = warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
+    uint4 wv[UNROLL][NT], av[UNROLL][MT][2];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int kb = kb0 + u * SM_WARPS;
+      const bool kin = kb < nkb && kb * 32 + t * 8 < K;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) wv[u][j] = kin ? ldg_stream(wrow[j] + kb * 32) : make_uint4(0, 0, 0, 0);
+    }
+    if (!waited) {  // the first batch of weights is on its way before the kernels ahead have finished
+      pdl_wait();
+      waited = true;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int kb = kb0 + u * SM_WARPS;
+      const bool kin = kb < nkb && kb * 32 + t * 8 < K;
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf)
+          av[u][i][hlf] = (kin && avalid[i][hlf]) ? __ldcg(reinterpret_cast<const uint4*>(arow[i][hlf] + kb * 32))
+                                                   : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        // physical k = t*8 + s*4 + {0,1} plays the fragment's k = 2t + {0,1}; + {2,3} plays 2t + 8 + {0,1}
+        const uint32_t a_s0[4] = {av[u][i][0].x, av[u][i][1].x, av[u][i][0].y, av[u][i][1].y};
+        const uint32_t a_s1[4] = {av[u][i][0].z, av[u][i][1].z, av[u][i][0].w, av[u][i][1].w};
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          mma_bf16_16816(acc[i][j], a_s0, wv[u][j].x, wv[u][j].y);
+          mma_bf16_16816(acc[i][j], a_s1, wv[u][j].z, wv[u][j].w);
+        }
+      }
+    }
+  }
+
+  if (!waited) pdl_wait();
+  // partial sums of the warps -> shared memory; c0,c1: row g, cols 2t,2t+1; c2,c3: row g+8
+  float* mine = red + (size_t)warp * (MT * 16) * RS;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      mine[(i * 16 + g) * RS + j * 8 + 2 * t] = acc[i][j][0];
+      mine[(i * 16 + g) * RS + j * 8 + 2 * t + 1] = acc[i][j][1];
+      mine[(i * 16 + g + 8) * RS + j * 8 + 2 * t] = acc[i][j][2];
+      mine[(i * 16 + g + 8) * RS + j * 8 + 2 * t + 1] = acc[i][j][3];
+    }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < M * (NT * 8); idx += blockDim.x) {
+    const int m = idx / (NT * 8), c = idx % (NT * 8);
+    const int n = n0 + c;
+    if (n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < SM_WARPS; ++w) v += red[((size_t)w * (MT * 16) + m) * RS + c];
+    if (bias) v += bias[n];
+    from_f32(C[(size_t)m * ldc + n], activate(v, act));
+  }
+}
+
+template <int MT, int NT, int UNROLL, typename TO>
+static int launch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
+                          int K, int act, cudaStream_t st) {
+  const size_t smem = (size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) * sizeof(float);
+  auto kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int blocks = (N + NT * 8 - 1) / (NT * 8);
+  return (int)launch_pdl(kern, dim3(blocks), dim3(SM_WARPS * 32), smem, st, (const __nv_bfloat16*)A, lda,
+                         (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act);
+}
+
+template <typename TO>
+static int dispatch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
+                            int K, int act, cudaStream_t st) {
+  // Columns per block: 16 when that still gives the 148 SMs about two blocks each, else 8.
+  const bool wide = N >= 148 * 2 * 16;
+  if (M <= 16) {
+    if (wide) return launch_small_m<1, 2, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+    return launch_small_m<1, 1, 8, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  }
+  if (M <= 32) {
+    if (wide) return launch_small_m<2, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+    return launch_small_m<2, 1, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  }
+  if (wide) return launch_small_m<4, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  return launch_small_m<4, 1, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+}
+
+}  // namespace cbis
+
+using namespace cbis;
+
+// A [M, lda>=K] bfloat16, W [N, K] bfloat16, bias [N] float or null, C [M, ldc>=N] bfloat16 or float.
+// Takes M <= 64 and K a multiple of 8 with 16-byte aligned operands; refuses anything else.
+CBIS_EXPORT int cbis_gemm_small_m_bf16(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
+                                       int M, int N, int K, int act, int out_dtype, void* stream) {
+  if (M <= 0 || N <= 0) return CBIS_OK;
+  if (M > 64 || K <= 0 || K % 8 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
+  if (lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return CBIS_ERR_ALIGNMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (out_dtype == CBIS_BF16) return dispatch_small_m<__nv_bfloat16>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  if (out_dtype == CBIS_F32) return dispatch_small_m<float>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  return CBIS_ERR_BAD_DTYPE;
+}

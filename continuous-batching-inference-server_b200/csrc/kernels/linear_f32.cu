@@ -8,11 +8,13 @@ namespace cbis {
 
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
-linear_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, const float* __restrict__ bias,
+linear_f32_kernel(const float* A, const float* __restrict__ W, const float* __restrict__ bias,
                   float* __restrict__ C, int M, int N, int K, int w_is_nk, int act, int lda, int ldc) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -84,13 +86,15 @@ CBIS_EXPORT int cbis_linear_f32(const float* A, const float* W, const float* bia
   cudaStream_t st = (cudaStream_t)stream;
   if (M > 256) {
     dim3 grid((N + 127) / 128, (M + 127) / 128);
-    linear_f32_kernel<128, 128, 8, 8, 8><<<grid, 256, 0, st>>>(A, W, bias, C, M, N, K, w_is_nk, act, lda, ldc);
-  } else if (M > 16) {
-    dim3 grid((N + 63) / 64, (M + 63) / 64);
-    linear_f32_kernel<64, 64, 16, 4, 4><<<grid, 256, 0, st>>>(A, W, bias, C, M, N, K, w_is_nk, act, lda, ldc);
-  } else {
-    dim3 grid((N + 63) / 64, (M + 15) / 16);
-    linear_f32_kernel<16, 64, 16, 1, 4><<<grid, 256, 0, st>>>(A, W, bias, C, M, N, K, w_is_nk, act, lda, ldc);
+    return (int)launch_pdl(linear_f32_kernel<128, 128, 8, 8, 8>, grid, dim3(256), 0, st, A, W, bias, C, M, N, K, w_is_nk,
+                           act, lda, ldc);
   }
-  return (int)cudaGetLastError();
+  if (M > 16) {
+    dim3 grid((N + 63) / 64, (M + 63) / 64);
+    return (int)launch_pdl(linear_f32_kernel<64, 64, 16, 4, 4>, grid, dim3(256), 0, st, A, W, bias, C, M, N, K, w_is_nk,
+                           act, lda, ldc);
+  }
+  dim3 grid((N + 63) / 64, (M + 15) / 16);
+  return (int)launch_pdl(linear_f32_kernel<16, 64, 16, 1, 4>, grid, dim3(256), 0, st, A, W, bias, C, M, N, K, w_is_nk,
+                         act, lda, ldc);
 }

@@ -14,26 +14,8 @@ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
   return z ^ (z >> 31);
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ temperature,
-                              const unsigned long long* __restrict__ keys, int* __restrict__ out, int V) {
-  __shared__ float sval[32];
-  __shared__ int sidx[32];
-  const int r = blockIdx.x;
-  const float* row = logits + (size_t)r * ld;
-  const float temp = temperature ? temperature[r] : 0.f;
-  const unsigned long long key = keys ? keys[r] : 0ull;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = row[i];
-    if (temp > 0.f) {
-      const unsigned long long z = mix64(key + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull);
-      const float u = ((float)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);  // (0,1), exact in 24 bits
-      v = v / temp - logf(-logf(u));
-    }
-    if (v != v) v = -INFINITY;  // NaN never wins over a number
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
+// Best (score, index) of a thread's candidates, reduced over the block; valid in thread 0.
+__device__ __forceinline__ void block_best(float& best, int& bi, float* sval, int* sidx) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -52,7 +34,62 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, const fl
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (lane == 0) out[r] = bi < V ? bi : 0;
+  }
+}
+
+// grid (chunks, R): block (c, r) scans its part of row r; the block of a row that finishes last
+// (a counter per row, which it sets back to zero) reduces the chunks' results.  part_val/part_idx:
+// [R][chunks]; counters: [R], zero before the first launch.
+__global__ void sample_kernel(const float* logits, int ld, const float* temperature,
+                              const unsigned long long* keys, int* __restrict__ out, int V,
+                              float* part_val, int* part_idx, unsigned int* counters) {
+  __shared__ float sval[32];
+  __shared__ int sidx[32];
+  __shared__ bool last;
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y, chunks = gridDim.x;
+  const float* row = logits + (size_t)r * ld;
+  const float temp = temperature ? temperature[r] : 0.f;
+  const unsigned long long key = keys ? keys[r] : 0ull;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += chunks * blockDim.x) {
+    float v = row[i];
+    if (temp > 0.f) {
+      const unsigned long long z = mix64(key + (unsigned long long)(i + 1) * 0x9E3779B97F4A7C15ull);
+      const float u = ((float)(z >> 41) + 0.5f) * (1.0f / 8388608.0f);  // (0,1), exact in 24 bits
+      v = v / temp - logf(-logf(u));
+    }
+    if (v != v) v = -INFINITY;  // NaN never wins over a number
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  block_best(best, bi, sval, sidx);
+  if (chunks == 1) {
+    if (threadIdx.x == 0) out[r] = bi < V ? bi : 0;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    part_val[(size_t)r * chunks + blockIdx.x] = best;
+    part_idx[(size_t)r * chunks + blockIdx.x] = bi;
+    __threadfence();
+    last = atomicAdd(&counters[r], 1u) == (unsigned)chunks - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const float v = part_val[(size_t)r * chunks + c];
+    const int i = part_idx[(size_t)r * chunks + c];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  __syncthreads();
+  block_best(best, bi, sval, sidx);
+  if (threadIdx.x == 0) {
+    out[r] = bi < V ? bi : 0;
+    counters[r] = 0;
   }
 }
 
@@ -60,12 +97,23 @@ __global__ void sample_kernel(const float* __restrict__ logits, int ld, const fl
 
 using namespace cbis;
 
+// Chunks a row of V entries is cut into, and the scratch this needs: chunks*R floats, chunks*R ints, R counters.
+CBIS_EXPORT int cbis_sample_chunks(int V) {
+  int c = (V + 4095) / 4096;
+  return c < 1 ? 1 : (c > 64 ? 64 : c);
+}
+
 // logits [R, ld >= V] 32-bit; temperature[R] (<= 0: greedy) and keys[R] may be null (greedy).
+// part_val/part_idx [R * chunks], counters [R] (zeroed once by the caller; the kernel leaves them zero).
 CBIS_EXPORT int cbis_sample(const float* logits, int ld, const float* temperature, const unsigned long long* keys,
-                            int* out, int R, int V, void* stream) {
+                            int* out, int R, int V, float* part_val, int* part_idx, unsigned int* counters,
+                            void* stream) {
   if (R <= 0) return CBIS_OK;
   if (V <= 0 || ld < V) return CBIS_ERR_BAD_SIZE;
-  const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-  sample_kernel<<<R, threads, 0, (cudaStream_t)stream>>>(logits, ld, temperature, keys, out, V);
-  return (int)cudaGetLastError();
+  const int chunks = cbis_sample_chunks(V);
+  if (chunks > 1 && (!part_val || !part_idx || !counters)) return CBIS_ERR_BAD_SIZE;
+  const int threads = V >= 1024 ? 256 : 64;
+  dim3 grid(chunks, R);
+  return (int)launch_after(false, sample_kernel, grid, dim3(threads), 0, (cudaStream_t)stream, logits, ld, temperature, keys, out,
+                         V, part_val, part_idx, counters);
 }

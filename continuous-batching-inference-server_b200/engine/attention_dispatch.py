@@ -26,9 +26,12 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
     if fast_decode:
         limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
         nsplit = ops.decode_splits(nd, mixer.n_head, limit)
-        scratch = ctx.decode_scratch(nd * mixer.n_head * nsplit * (hd + 2)) if nsplit > 1 else None
+        scratch = counters = None
+        if nsplit > 1:
+            scratch, counters = ctx.decode_scratch(ops.decode_scratch_floats(nd, mixer.n_head, hd, nsplit),
+                                                   nd * mixer.n_head)
         ops.paged_decode_bf16(qkv[:nd], k_off if mixer.own_kv else -1, v_off if mixer.own_kv else -1, cache.k, cache.v,
-                              view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, out[:nd], scratch,
+                              view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, out[:nd], scratch, counters,
                               mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale, mixer.window, nsplit)
     if first_general < T:
         r = slice(first_general, T)

@@ -78,8 +78,9 @@ class StepContext:
         """Stores this step's keys/values of ``mixer`` (if it keeps its own) and attends over the pages."""
         run_attention(self, mixer, qkv, cache, view, out)
 
-    def decode_scratch(self, n_floats: int) -> torch.Tensor:
-        return self.runner.scratch(n_floats)
+    def decode_scratch(self, n_floats: int, n_counters: int):
+        """(float scratch, zeroed int32 counters) for kernels that split work and merge it in the last block."""
+        return self.runner.scratch(n_floats, n_counters)
 
 
 class ModelRunner:
@@ -115,12 +116,14 @@ class ModelRunner:
         self.use_graphs = all(getattr(part, "capturable", True)
                               for layer in model.layers for _, part in layer.parts())
         self._graphs: Dict[int, tuple] = {}      # rows of a decode-only step -> (graph, context, logits)
-        worst = 0
+        worst = heads = 0
         for layer in model.layers:
             m = layer.mixer
             if hasattr(m, "n_head") and hasattr(m, "head_dim"):
-                worst = max(worst, S * m.n_head * 32 * (m.head_dim + 2))
+                worst = max(worst, ops.decode_scratch_floats(S, m.n_head, m.head_dim, 32))
+                heads = max(heads, m.n_head)
         self._scratch = torch.empty(max(worst, 1), dtype=torch.float32, device=self.device)
+        self._counters = torch.zeros(max(S * heads, 1), dtype=torch.int32, device=self.device)
         self.graph_replays = 0
 
     # ------------------------------------------------------------------
@@ -136,13 +139,17 @@ class ModelRunner:
         """Bytes of the packed step description copied from pinned host memory every step."""
         return self._host.numel() * 4
 
-    def scratch(self, n_floats: int) -> torch.Tensor:
-        """Float32 scratch shared by the kernels of a step (split-KV partial results)."""
-        if n_floats > self._scratch.numel():
+    def scratch(self, n_floats: int, n_counters: int):
+        """Float scratch for partial results and int32 counters (zero between launches) shared by the
+        kernels of a step; both grow if a part asks for more than the built-in attention needs."""
+        if n_floats > self._scratch.numel() or n_counters > self._counters.numel():
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("kernel scratch would have to grow during graph capture")
-            self._scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
-        return self._scratch
+            if n_floats > self._scratch.numel():
+                self._scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
+            if n_counters > self._counters.numel():
+                self._counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
+        return self._scratch, self._counters
 
     def validate(self, entries: Sequence[StepEntry], reserved_ahead: bool = False) -> None:
         spec, mgr = self.model.spec, self.pool.manager

@@ -112,6 +112,16 @@ def bias_act(x, bias, act):
     _check(st, "bias_act", f"M={M} N={N}")
 
 
+def bias_act_out(src, bias, act, dst):
+    """dst = act(src + bias): 32-bit sums in, activations out with one rounding."""
+    _need_cuda(src, bias, dst)
+    M, N = src.shape
+    assert src.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous() and dst.shape == src.shape
+    st = kernels().cbis_bias_act_out(_ptr(src), _ptr(bias), c_int(ACT[act]), _ptr(dst), c_int(M), c_int(N),
+                                     c_int(dtype_code(dst.dtype)), _stream())
+    _check(st, "bias_act_out", f"M={M} N={N}")
+
+
 def linear_f32(x, w, bias, act, out, w_is_nk=False):
     """out = act(x @ W + bias) on the FP32 units; W is [K,N], or [N,K] with ``w_is_nk``."""
     _need_cuda(x, w, bias, out)
@@ -126,25 +136,51 @@ def linear_f32(x, w, bias, act, out, w_is_nk=False):
     _check(st, "linear_f32", f"M={M} N={N} K={K}")
 
 
-def linear(x, w, bias, act=None, out_dtype=None, w_is_nk=False):
-    """act(x @ W + bias).  32-bit inputs: this package's FFMA kernel (no reduced-precision
-    matrix mode).  bfloat16 inputs: the library GEMM with 32-bit accumulation, then the
-    bias/activation kernel."""
-    M = x.shape[0]
-    N = w.shape[0] if w_is_nk else w.shape[1]
+SMALL_M = 16      # rows up to which the weight-streaming kernel takes a bfloat16 product (it can take 64)
+
+
+def gemm_small_m(x, w_nk, bias, act, out):
+    """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16, 32-bit accumulation (weight streaming)."""
+    _need_cuda(x, w_nk, bias, out)
+    M, K = x.shape
+    N = w_nk.shape[0]
+    assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
+    st = kernels().cbis_gemm_small_m_bf16(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
+                                          c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
+                                          c_int(dtype_code(out.dtype)), _stream())
+    _check(st, "gemm_small_m", f"M={M} N={N} K={K}")
+
+
+def linear(x, w_nk, bias, act=None, out_dtype=None):
+    """act(x @ W^T + bias) with W stored [N, K] (K contiguous).
+
+    32-bit inputs: this package's FFMA kernel (no reduced-precision matrix mode).  bfloat16
+    inputs: up to 64 rows go to the weight-streaming tensor-core kernel with the bias and the
+    activation applied to the 32-bit sum; more rows go to the library GEMM with a 32-bit
+    result, then the bias/activation kernel, so both ways round once."""
+    M, K = x.shape
+    N = w_nk.shape[0]
     if x.dtype == torch.float32:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
-        linear_f32(x, w, bias, act, out, w_is_nk)
+        linear_f32(x, w_nk, bias, act, out, w_is_nk=True)
         return out
-    _need_cuda(x, w)
+    _need_cuda(x, w_nk)
     out_dtype = out_dtype or x.dtype
-    wm = w.t() if w_is_nk else w
+    if M <= SMALL_M and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        gemm_small_m(x, w_nk, bias, act, out)
+        return out
+    plain = bias is None and not ACT[act]
+    if out_dtype != torch.float32 and plain:
+        return torch.mm(x, w_nk.t())
+    acc = torch.mm(x, w_nk.t(), out_dtype=torch.float32)
     if out_dtype == torch.float32:
-        out = torch.mm(x, wm, out_dtype=torch.float32)
-    else:
-        out = torch.mm(x, wm)
-    if bias is not None or ACT[act]:
-        bias_act(out, bias, act)
+        if not plain:
+            bias_act(acc, bias, act)
+        return acc
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    bias_act_out(acc, bias, act, out)     # one rounding, as in the few-rows kernel
     return out
 
 
@@ -185,24 +221,31 @@ def decode_splits(rows: int, n_head: int, max_context: int) -> int:
     return max(1, min(want, 32, max(1, max_context // 64)))
 
 
+def decode_scratch_floats(rows: int, n_head: int, head_dim: int, nsplit: int) -> int:
+    """Floats of scratch for the decode kernel's partial results."""
+    return rows * n_head * nsplit * (head_dim + 2) if nsplit > 1 else 0
+
+
 def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out,
-                      scratch, n_head, n_kv_head, head_dim, page_size, scale, window, nsplit):
+                      scratch, counters, n_head, n_kv_head, head_dim, page_size, scale, window, nsplit):
     """Decode attention (one query per row) with the keys split ``nsplit`` ways; with ``k_off >= 0`` the
-    current token's key/value are taken from ``qkv`` and stored into the cache by the same kernel."""
-    _need_cuda(qkv, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out, scratch)
+    current token's key/value are taken from ``qkv`` and stored into the cache by the same kernel.
+    ``scratch``: ``decode_scratch_floats`` floats; ``counters``: rows*n_head int32, zero before the
+    first launch (every launch leaves them zero)."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, row_seq, positions, slot_mapping, out, scratch, counters)
     rows = qkv.shape[0]
     if head_dim % 8 or head_dim > 256:
         raise KernelError(f"decode attention: head_dim={head_dim} must be a multiple of 8, at most 256")
     assert qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-    need = rows * n_head * nsplit * (head_dim + 2) if nsplit > 1 else 0
-    assert need == 0 or (scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need)
+    if nsplit > 1:
+        assert scratch.dtype == torch.float32 and scratch.numel() >= decode_scratch_floats(rows, n_head, head_dim, nsplit)
+        assert counters.dtype == torch.int32 and counters.numel() >= rows * n_head
     st = kernels().cbis_paged_decode_bf16(
         _ptr(qkv), c_int(qkv.stride(0)), c_int(k_off), c_int(v_off), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
         c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions), _ptr(slot_mapping), _ptr(out),
-        c_int(out.stride(0)), _ptr(scratch), c_int(rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim),
-        c_int(page_size), c_float(scale), c_int(window), c_int(nsplit), _stream())
-    _check(st, "paged_decode_bf16", f"rows={rows} heads={n_head}/{n_kv_head} head_dim={head_dim} splits={nsplit}",
-           launches=2 if nsplit > 1 else 1)
+        c_int(out.stride(0)), _ptr(scratch), _ptr(counters), c_int(rows), c_int(n_head), c_int(n_kv_head),
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(nsplit), _stream())
+    _check(st, "paged_decode_bf16", f"rows={rows} heads={n_head}/{n_kv_head} head_dim={head_dim} splits={nsplit}")
 
 
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):
@@ -220,6 +263,24 @@ def slots_from_table(positions, row_seq, block_table, page_size, slot_mapping, n
     _check(st, "slots_from_table")
 
 
+_sample_scratch = {}
+
+
+def _sample_buffers(device, R: int, chunks: int):
+    """Scratch of the sampling kernel, kept per device and grown as needed; counters start at zero
+    and every launch leaves them zero."""
+    key = device.index     # one scratch per device: launches on different streams must not overlap
+    have = _sample_scratch.get(key)
+    if have is None or have[0].numel() < R * chunks or have[2].numel() < R:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("sampling scratch would have to grow during graph capture")
+        n = max(R * chunks, 64 * 64)
+        have = (torch.empty(n, dtype=torch.float32, device=device), torch.empty(n, dtype=torch.int32, device=device),
+                torch.zeros(max(R, 1024), dtype=torch.int32, device=device))
+        _sample_scratch[key] = have
+    return have
+
+
 def sample(logits, temperature, keys, out):
     """out[r] = argmax_i(logits[r,i]) (temperature[r] <= 0 or None) or the Gumbel-max draw keyed by keys[r]."""
     _need_cuda(logits, temperature, keys, out)
@@ -227,6 +288,8 @@ def sample(logits, temperature, keys, out):
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     assert temperature is None or temperature.dtype == torch.float32
     assert keys is None or keys.dtype == torch.int64
+    chunks = kernels().cbis_sample_chunks(c_int(V))
+    pv, pi, cnt = _sample_buffers(logits.device, R, chunks)
     st = kernels().cbis_sample(_ptr(logits), c_int(logits.stride(0)), _ptr(temperature), _ptr(keys), _ptr(out),
-                               c_int(R), c_int(V), _stream())
+                               c_int(R), c_int(V), _ptr(pv), _ptr(pi), _ptr(cnt), _stream())
     _check(st, "sample", f"R={R} V={V}")

@@ -120,7 +120,7 @@ class Model:
         if ctx.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
         h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
-        return ops.linear(h, self.head, None, None, out_dtype=torch.float32, w_is_nk=True)
+        return ops.linear(h, self.head, None, None, out_dtype=torch.float32)
 
 
 def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:

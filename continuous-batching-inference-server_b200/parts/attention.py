@@ -42,9 +42,9 @@ class PagedAttention(Mixer):
                 TensorDecl(f"{prefix}{self.proj_name}.bias", (self.width,), "vector")]
 
     def load(self, prefix, tensors, dtype, device):
-        self.w_qkv = self._matrix(tensors[f"{prefix}{self.qkv_name}.weight"], dtype, device)
+        self.w_qkv = self._matrix_nk(tensors[f"{prefix}{self.qkv_name}.weight"], dtype, device)
         self.b_qkv = self._vector(tensors[f"{prefix}{self.qkv_name}.bias"], device)
-        self.w_o = self._matrix(tensors[f"{prefix}{self.proj_name}.weight"], dtype, device)
+        self.w_o = self._matrix_nk(tensors[f"{prefix}{self.proj_name}.weight"], dtype, device)
         self.b_o = self._vector(tensors[f"{prefix}{self.proj_name}.bias"], device)
 
     def forward(self, ctx, h, cache, state):

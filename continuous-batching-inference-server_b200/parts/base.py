@@ -67,6 +67,11 @@ class Part:
         return t.to(device=device, dtype=dtype).contiguous()
 
     @staticmethod
+    def _matrix_nk(t: torch.Tensor, dtype, device) -> torch.Tensor:
+        """A Conv1D weight [in, out] as the kernels want it: [out, in], the contraction dim contiguous."""
+        return t.to(device=device, dtype=dtype).t().contiguous()
+
+    @staticmethod
     def _vector(t: torch.Tensor, device) -> torch.Tensor:
         return t.to(device=device, dtype=torch.float32).contiguous()
 

@@ -10,8 +10,8 @@ from .base import Delta, FeedForward, register_feed_forward
 
 class DenseFeedForward(FeedForward):
     """act(h @ W1 + b1) @ W2 + b2 with the activation taken on the 32-bit sum
-    (reference: python/model.py:50, src/transformer.cpp:86-88).  Weights in GPT-2's
-    Conv1D layout [in, out]."""
+    (reference: python/model.py:50, src/transformer.cpp:86-88).  Weights come in GPT-2's
+    Conv1D layout [in, out] and are kept transposed, [out, in]."""
 
     def __init__(self, width: int, inner: int, activation: str,
                  names=("mlp.c_fc", "mlp.c_proj")):
@@ -28,9 +28,9 @@ class DenseFeedForward(FeedForward):
                 TensorDecl(f"{prefix}{self.proj}.bias", (self.width,), "vector")]
 
     def load(self, prefix, tensors, dtype, device):
-        self.w1 = self._matrix(tensors[f"{prefix}{self.fc}.weight"], dtype, device)
+        self.w1 = self._matrix_nk(tensors[f"{prefix}{self.fc}.weight"], dtype, device)
         self.b1 = self._vector(tensors[f"{prefix}{self.fc}.bias"], device)
-        self.w2 = self._matrix(tensors[f"{prefix}{self.proj}.weight"], dtype, device)
+        self.w2 = self._matrix_nk(tensors[f"{prefix}{self.proj}.weight"], dtype, device)
         self.b2 = self._vector(tensors[f"{prefix}{self.proj}.bias"], device)
 
     def forward(self, ctx, h):

@@ -285,14 +285,15 @@ def test_decode_attention_split_kv(ops, n_head, n_kv_head, hd, ps, window, nspli
     row_seq = torch.cat([c["row_seq"], torch.tensor([-1], dtype=torch.int32)])      # a padding row at the end
     positions = torch.cat([c["positions"], torch.tensor([0], dtype=torch.int32)])
     out = torch.full((S + 1, dq), float("nan"), dtype=torch.bfloat16, device="cuda")
-    scratch = torch.empty((S + 1) * n_head * nsplit * (hd + 2), device="cuda")
+    scratch = torch.full((max(1, ops.decode_scratch_floats(S + 1, n_head, hd, nsplit)),), float("nan"), device="cuda")
+    counters = torch.zeros((S + 1) * n_head, dtype=torch.int32, device="cuda")
     if hd % 8:
         with pytest.raises(ops.KernelError, match="multiple of 8"):
             ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
-                                  scratch, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
+                                  scratch, counters, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
         return
     ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
-                          scratch, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
+                          scratch, counters, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
     assert (out[:S].double().cpu() - c["ref"]).abs().max() < 1e-2 * max(1.0, c["ref"].abs().max().item())
     assert torch.equal(out[S].cpu(), torch.zeros(dq, dtype=torch.bfloat16))
     assert not torch.isnan(kc.float()).any() or True
@@ -302,9 +303,10 @@ def test_decode_attention_split_kv(ops, n_head, n_kv_head, hd, ps, window, nspli
         assert torch.equal(vc[page, :, off, :].reshape(-1), qkv[s, dq + dkv:])
     # the same from the cache alone (k_off < 0) gives the same result
     out2 = torch.empty_like(out)
-    ops.paged_decode_bf16(qkv, -1, -1, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out2, scratch,
+    ops.paged_decode_bf16(qkv, -1, -1, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out2, scratch, counters,
                           n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
     assert torch.equal(out2[:S], out[:S])
+    assert int(counters.abs().sum()) == 0                                             # left zero for the next launch
 
 
 def test_decode_advance_and_slots(ops):
@@ -316,3 +318,53 @@ def test_decode_advance_and_slots(ops):
     slots = dev(torch.zeros(3, dtype=torch.int32))
     ops.slots_from_table(pos, dev(torch.tensor([0, 1, -1], dtype=torch.int32)), bt, 4, slots, 3)
     assert slots.tolist() == [2 * 4 + 0, 3 * 4 + 0, -1]
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(40, 64), (2048, 2048), (50257, 96), (6144, 2048), (1000, 8200), (7, 8)])
+def test_gemm_small_m(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * 7 + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    ref = x.double() @ w.double().t() + b.double()
+    scale = max(1.0, ref.abs().max().item())
+    out = torch.full((M, N), float("nan"), device="cuda")
+    ops.gemm_small_m(dev(x), dev(w), dev(b), None, out)
+    assert (out.double().cpu() - ref).abs().max() < 1e-5 * scale * math.sqrt(K)      # 32-bit sums of exact products
+    out16 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_small_m(dev(x), dev(w), None, "gelu_erf", out16)
+    ref2 = plain_gpt.gelu(x.double() @ w.double().t(), "gelu")
+    assert (out16.double().cpu() - ref2).abs().max() < 1e-2 * max(1.0, ref2.abs().max().item())
+    # rows of a wider matrix as input, columns of a wider matrix as output
+    wide = torch.randn(M, K + 16, generator=g).to(torch.bfloat16)
+    big = torch.zeros(M, N + 3, device="cuda")
+    ops.gemm_small_m(dev(wide)[:, 8:8 + K], dev(w), None, None, big[:, :N])
+    ref3 = wide[:, 8:8 + K].double() @ w.double().t()
+    assert (big[:, :N].double().cpu() - ref3).abs().max() < 1e-5 * scale * math.sqrt(K)
+    assert torch.equal(big[:, N:].cpu(), torch.zeros(M, 3))
+
+
+def test_gemm_small_m_refuses_what_it_does_not_take(ops):
+    x = torch.zeros(65, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.gemm_small_m(x, w, None, None, torch.empty(65, 16, device="cuda"))
+    x = torch.zeros(4, 60, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(16, 60, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.gemm_small_m(x, w, None, None, torch.empty(4, 16, device="cuda"))
+    # the dispatcher sends such sizes to the library product instead
+    out = ops.linear(x, w, None, None, out_dtype=torch.float32)
+    assert out.shape == (4, 16)
+
+
+def test_bias_act_out_rounds_once(ops):
+    g = torch.Generator().manual_seed(5)
+    src, b = torch.randn(9, 130, generator=g) * 3, torch.randn(130, generator=g)
+    dst = torch.empty(9, 130, dtype=torch.bfloat16, device="cuda")
+    ops.bias_act_out(dev(src), dev(b), "gelu_tanh", dst)
+    ref = plain_gpt.gelu(src.double() + b.double(), "gelu_new")
+    # one bfloat16 rounding (2^-8 relative) of a 32-bit GELU (absolute error of tanhf times |x| in the tails)
+    close = (dst.double().cpu() - ref).abs() <= (ref.abs() * 2 ** -8 + 4e-6)
+    assert close.all()
