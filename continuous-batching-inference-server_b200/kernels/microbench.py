@@ -1,0 +1,124 @@
+"""Times single kernels at given sizes, inside a CUDA graph over distinct buffers (so that every
+launch streams from HBM, as in a real step) or launch by launch for profilers.
+
+    python -m cbis_b200.kernels.microbench --op decode_attn --rows 8 --ctx 1536 --layers 24
+    python -m cbis_b200.kernels.microbench --op gemm --rows 8 --n 6144 --k 2048
+    python -m cbis_b200.kernels.microbench --op layernorm --rows 8 --k 2048
+    python -m cbis_b200.kernels.microbench --op sample --rows 8 --n 50257
+
+``--no-graph`` launches the kernels directly (a profiler then sees ordinary launches).
+"""
+import argparse
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def timed(fn, use_graph=True, reps=20):
+    """Microseconds per call of fn()."""
+    fn()
+    torch.cuda.synchronize()
+    if use_graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        run = g.replay
+    else:
+        run = fn
+    run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def main():
+    from cbis_b200.kernels import ops
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", required=True, choices=["decode_attn", "gemm", "layernorm", "sample"])
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--ctx", type=int, default=1536)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--splits", type=int, default=0, help="0: the engine's own choice")
+    ap.add_argument("--layers", type=int, default=24, help="distinct weight/cache buffers per timed call")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--reps", type=int, default=20)
+    a = ap.parse_args()
+    dev, M, L = "cuda", a.rows, a.layers
+    torch.manual_seed(0)
+    if a.op == "gemm":
+        W = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(L)]
+        x = torch.randn(M, a.k, device=dev, dtype=torch.bfloat16)
+        bias = torch.randn(a.n, device=dev)
+        out = torch.empty(M, a.n, device=dev, dtype=torch.bfloat16)
+
+        def fn():
+            for l in range(L):
+                ops.gemm_small_m(x, W[l], bias, None, out)
+
+        def lib():
+            for l in range(L):
+                torch.mm(x, W[l].t(), out=out)
+        mb = a.n * a.k * 2 / 1e6
+        t = timed(fn, not a.no_graph, a.reps) / L
+        tl = timed(lib, not a.no_graph, a.reps) / L
+        print(f"gemm M={M} N={a.n} K={a.k}: {mb:.1f} MB  own {t:.2f} us ({mb / t:.2f} TB/s)  library {tl:.2f} us ({mb / tl:.2f} TB/s)")
+    elif a.op == "layernorm":
+        x = torch.randn(M, a.k, device=dev)
+        delta = torch.randn(M, a.k, device=dev)
+        gm, bt = torch.ones(a.k, device=dev), torch.zeros(a.k, device=dev)
+        out = torch.empty(M, a.k, device=dev, dtype=torch.bfloat16)
+
+        def fn():
+            for l in range(L):
+                ops.add_layernorm(x, delta, bt, gm, bt, 1e-5, out)
+        print(f"add_layernorm rows={M} width={a.k}: {timed(fn, not a.no_graph, a.reps) / L:.2f} us")
+    elif a.op == "sample":
+        lg = torch.randn(M, a.n, device=dev)
+        out = torch.empty(M, dtype=torch.int32, device=dev)
+
+        def fn():
+            for l in range(L):
+                ops.sample(lg, None, None, out)
+        print(f"sample rows={M} vocab={a.n}: {timed(fn, not a.no_graph, a.reps) / L:.2f} us")
+    else:
+        H, hd, ps, ctx = a.heads, a.head_dim, a.page_size, a.ctx
+        nblk = -(-ctx // ps)
+        npages = M * nblk
+        kc = torch.randn(L, npages, H, ps, hd, device=dev, dtype=torch.bfloat16)
+        vc = torch.randn_like(kc)
+        mb_ = max(nblk, 128)
+        bt_ = (torch.arange(M * mb_, dtype=torch.int32, device=dev).view(M, mb_) % nblk
+               + (torch.arange(M, dtype=torch.int32, device=dev) * nblk)[:, None]).int().contiguous()
+        d = H * hd
+        qkv = torch.randn(M, 3 * d, device=dev, dtype=torch.bfloat16)
+        rs = torch.arange(M, dtype=torch.int32, device=dev)
+        pos = torch.full((M,), ctx - 1, dtype=torch.int32, device=dev)
+        sm = (bt_[:, (ctx - 1) // ps] * ps + (ctx - 1) % ps).int().contiguous()
+        out = torch.empty(M, d, device=dev, dtype=torch.bfloat16)
+        ns = a.splits or ops.decode_splits(M, H, ctx)
+        scratch = torch.empty(max(1, ops.decode_scratch_floats(M, H, hd, ns)), device=dev)
+        cnt = torch.zeros(M * H, dtype=torch.int32, device=dev)
+
+        def fn():
+            for l in range(L):
+                ops.paged_decode_bf16(qkv, d, 2 * d, kc[l], vc[l], bt_, rs, pos, sm, out, scratch, cnt, H, H, hd, ps,
+                                      hd ** -0.5, 0, ns)
+        mb = M * ctx * d * 2 * 2 / 1e6
+        t = timed(fn, not a.no_graph, a.reps) / L
+        print(f"decode_attn rows={M} ctx={ctx} heads={H} head_dim={hd} splits={ns}: {mb:.1f} MB  {t:.2f} us ({mb / t:.2f} TB/s)")
+
+
+if __name__ == "__main__":
+    main()

@@ -215,10 +215,12 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
 
 
 def decode_splits(rows: int, n_head: int, max_context: int) -> int:
-    """How many ways the decode kernel splits a request's keys: enough blocks for about four per SM,
-    never pieces under 64 keys."""
-    want = -(-4 * 148 // max(1, rows * n_head))
-    return max(1, min(want, 32, max(1, max_context // 64)))
+    """How many ways the decode kernel splits a request's keys.  A block takes (row, head, split) and
+    4 blocks fit on each of the 148 SMs: split as far as one round of blocks allows, in pieces of at
+    least 32 keys, at most 32 ways; with a round or more of (row, head) pairs there is no split."""
+    slots = 4 * 148
+    pairs = max(1, rows * n_head)
+    return max(1, min(slots // pairs, 32, max(1, max_context // 32)))
 
 
 def decode_scratch_floats(rows: int, n_head: int, head_dim: int, nsplit: int) -> int:
