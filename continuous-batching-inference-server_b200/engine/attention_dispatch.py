@@ -7,6 +7,8 @@ keep the same contract: the query at position p sees the keys of its own request
 
 * bfloat16, head size a multiple of 8, decoding rows: the split-KV decode kernel, which also
   stores the current token's key and value;
+* bfloat16, head size 64 or 128, page size a power of two, longer segments: the tiled
+  tensor-core kernel, after the cache-write kernel;
 * everything else: the general kernel, after the cache-write kernel.
 """
 from __future__ import annotations
@@ -37,6 +39,12 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
         r = slice(first_general, T)
         if mixer.own_kv:
             ops.kv_write(qkv[r], k_off, v_off, cache.k, cache.v, view.slot_mapping[r], mixer.n_kv_head, hd, ps)
+        if qkv.dtype == torch.bfloat16 and hd in (64, 128) and ps & (ps - 1) == 0 and first_general == nd:
+            # q and out keep their full row numbering: the kernel finds its rows through cu_rows
+            ops.paged_prefill_bf16(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
+                                   ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
+                                   mixer.scale, mixer.window)
+            return
         ops.paged_attention_generic(qkv[r, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[r],
                                     ctx.positions[r], out[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
                                     mixer.window)

@@ -250,6 +250,25 @@ def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq,
     _check(st, "paged_decode_bf16", f"rows={rows} heads={n_head}/{n_kv_head} head_dim={head_dim} splits={nsplit}")
 
 
+def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
+                       n_head, n_kv_head, head_dim, page_size, scale, window=0):
+    """Attention of the segments seg0..seg0+n_seg-1 (runs of rows given by ``cu_rows``, first positions
+    ``seg_start``) over their pages, on the tensor cores.  Head sizes 64 and 128, page sizes 2^k."""
+    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
+    if head_dim not in (64, 128):
+        raise KernelError(f"prefill attention: head_dim={head_dim} is not 64 or 128 (the general kernel takes it)")
+    if page_size & (page_size - 1):
+        raise KernelError(f"prefill attention: page_size={page_size} is not a power of two (the general kernel takes it)")
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous()
+    st = kernels().cbis_paged_prefill_bf16(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(cu_rows), _ptr(seg_start), _ptr(out), c_int(out.stride(0)), c_int(seg0), c_int(n_seg),
+        c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim), c_int(page_size), c_float(scale),
+        c_int(window), _stream())
+    _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+
+
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):
     """tokens <- sampled, positions/seg_start/seg_ctx += 1 for the first n rows (all on the device)."""
     st = kernels().cbis_decode_advance(_ptr(tokens), _ptr(positions), _ptr(seg_start), _ptr(seg_ctx), _ptr(sampled),

@@ -368,3 +368,51 @@ def test_bias_act_out_rounds_once(ops):
     # one bfloat16 rounding (2^-8 relative) of a 32-bit GELU (absolute error of tanhf times |x| in the tails)
     close = (dst.double().cpu() - ref).abs() <= (ref.abs() * 2 ** -8 + 4e-6)
     assert close.all()
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [(2, 2, 128, 16, 0), (4, 2, 64, 16, 0), (3, 1, 128, 64, 0),
+                                                           (2, 2, 64, 8, 0), (2, 2, 128, 16, 100), (1, 1, 64, 32, 37)])
+def test_prefill_attention_tensor_cores(ops, n_head, n_kv_head, hd, ps, window):
+    """Segments of 1..200 rows at the end of contexts of up to 333 keys: first portions, later portions,
+    rows that are not a multiple of the 64-row tile, contexts that end inside a page and inside a key tile."""
+    seg_ctx, seg_rows = [200, 333, 64, 70, 1, 130], [200, 77, 64, 3, 1, 65]
+    c = paged_case(ops, torch.bfloat16, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed=hd + ps + window)
+    S = len(seg_ctx)
+    cu = torch.tensor([0] + list(np.cumsum(seg_rows)), dtype=torch.int32)
+    start = torch.tensor([cx - n for cx, n in zip(seg_ctx, seg_rows)], dtype=torch.int32)
+    out = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out, 0, S, max(seg_rows),
+                           n_head, n_kv_head, hd, ps, c["scale"], window)
+    err = (out.double().cpu() - c["ref"]).abs().max().item()
+    assert err < 1.5e-2 * max(1.0, c["ref"].abs().max().item()), err
+    # only some of the segments (the first two count as decoded elsewhere): their rows stay untouched
+    out2 = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 2, S - 2, max(seg_rows[2:]),
+                           n_head, n_kv_head, hd, ps, c["scale"], window)
+    r2 = int(cu[2])
+    assert torch.isnan(out2[:r2].float()).all() and torch.equal(out2[r2:], out[r2:])
+
+
+def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal(ops):
+    hd, ps, T = 128, 16, 300
+    g = torch.Generator().manual_seed(4)
+    k = (torch.randn(T, hd, generator=g) * 0.05).to(torch.bfloat16)
+    v = torch.randn(T, hd, generator=g).to(torch.bfloat16)
+    q = (torch.randn(T, hd, generator=g) * 0.05).to(torch.bfloat16)
+    # row 250 matches key 3 strongly; row 100 would match key 101 (the future) strongly, which it must not see
+    q[250] = torch.randn(hd, generator=g).to(torch.bfloat16)
+    q[100] = torch.randn(hd, generator=g).to(torch.bfloat16)
+    k[3] = q[250]
+    k[101] = q[100]
+    pages = torch.randperm(19, generator=g).int()
+    kc = torch.zeros(19, 1, ps, hd, dtype=torch.bfloat16, device="cuda"); vc = torch.zeros_like(kc)
+    slots = torch.tensor([int(pages[p // ps]) * ps + p % ps for p in range(T)], dtype=torch.int32)
+    ops.kv_write(dev(torch.cat([k, v], 1)), 0, hd, kc, vc, dev(slots), 1, hd, ps)
+    out = torch.empty(T, hd, dtype=torch.bfloat16, device="cuda")
+    ops.paged_prefill_bf16(dev(q), kc, vc, dev(pages[None, :]), dev(torch.tensor([0, T], dtype=torch.int32)),
+                           dev(torch.tensor([0], dtype=torch.int32)), out, 0, 1, T, 1, 1, hd, ps, hd ** -0.5)
+    sc = (q.double() @ k.double().t()) * hd ** -0.5
+    sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+    p = torch.softmax(sc, -1)
+    assert p[250, 3] > 0.9 and p[100, 101] == 0
+    assert (out.double().cpu() - p @ v.double()).abs().max() < 2e-2
