@@ -117,3 +117,62 @@ CBIS_EXPORT int cbis_sample(const float* logits, int ld, const float* temperatur
   return (int)launch_after(false, sample_kernel, grid, dim3(threads), 0, (cudaStream_t)stream, logits, ld, temperature, keys, out,
                          V, part_val, part_idx, counters);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same sampling with the library's own scratch: see sample_no_alloc.h.
+// ---------------------------------------------------------------------------------------------
+#include "sample_no_alloc.h"
+#include <mutex>
+
+namespace {
+
+constexpr int NA_MAX_CHUNKS = 64;  // cbis_sample_chunks() never returns more
+constexpr int NA_WORDS = CBIS_SAMPLE_NO_ALLOC_MAX_ROWS * NA_MAX_CHUNKS * 2 + CBIS_SAMPLE_NO_ALLOC_MAX_ROWS;
+
+// chunk maxima (floats), their indices (ints), one counter per row: 33,024 words = 132,096 bytes.
+// In host code this name is only a handle for the runtime, never a device address.
+static __device__ __align__(256) unsigned int na_scratch[NA_WORDS];
+
+constexpr int NA_MAX_DEVICES = 64;
+static unsigned int* na_device_ptr[NA_MAX_DEVICES];
+static std::mutex na_mutex;
+
+// Device address of na_scratch on the current device; looked up once per device.
+static int na_scratch_address(unsigned int** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NA_MAX_DEVICES) return CBIS_ERR_BAD_SIZE;
+  std::lock_guard<std::mutex> lock(na_mutex);
+  if (na_device_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, na_scratch);
+    if (e != cudaSuccess) return (int)e;
+    na_device_ptr[dev] = static_cast<unsigned int*>(p);
+  }
+  *ptr = na_device_ptr[dev];
+  return CBIS_OK;
+}
+
+}  // namespace
+
+CBIS_EXPORT int cbis_sample_no_alloc(const float* logits, int ld, const float* temperature,
+                                     const unsigned long long* keys, int* out, int R, int V, void* stream) {
+  if (R <= 0) return CBIS_OK;
+  if (V <= 0 || ld < V) return CBIS_ERR_BAD_SIZE;
+  if (R > CBIS_SAMPLE_NO_ALLOC_MAX_ROWS) return CBIS_ERR_TOO_LARGE;
+  unsigned int* base = nullptr;
+  const int st = na_scratch_address(&base);
+  if (st != CBIS_OK) return st;
+  float* part_val = reinterpret_cast<float*>(base);
+  int* part_idx = reinterpret_cast<int*>(base + CBIS_SAMPLE_NO_ALLOC_MAX_ROWS * NA_MAX_CHUNKS);
+  unsigned int* counters = base + CBIS_SAMPLE_NO_ALLOC_MAX_ROWS * NA_MAX_CHUNKS * 2;
+  // The counters must be zero when the kernel starts; whatever an earlier call left (it may have been cut short) goes.
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)R * sizeof(unsigned int), (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  const int chunks = cbis_sample_chunks(V);
+  const int threads = V >= 1024 ? 256 : 64;
+  dim3 grid(chunks, R);
+  return (int)launch_after(false, sample_kernel, grid, dim3(threads), 0, (cudaStream_t)stream, logits, ld, temperature,
+                           keys, out, V, part_val, part_idx, counters);
+}
