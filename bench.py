@@ -109,6 +109,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64, prefill and e2e")
+    ap.add_argument("--prefill-only", action="store_true", help="time only the 2,048-token prefill (for profilers)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -137,6 +138,8 @@ def main() -> int:
     K = max(1, min(K, P - PL - W - 20))
     pk = peaks()
     max_b = B if args.skip_points else max(B, 64)
+    if args.prefill_only:
+        max_b = 1
     eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size,
                                 max_tokens=max_b * P, max_num_seqs=max_b, max_batched_tokens=2048,
                                 prefill_chunk=2048)
@@ -177,6 +180,28 @@ def main() -> int:
         del loop
         return batch * steps / (ms / 1e3), ms / steps, per_step
 
+    def prefill_once(T):
+        """Median milliseconds of one T-token prompt run as ONE step (3 warm-ups, 5 timed)."""
+        toks = prompts(1, T)[0]
+        times = []
+        for it in range(3 + 5):
+            slot = eng.open_request(1000 + it)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.forward_step([StepEntry(slot, 0, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+            eng.close_request(slot)
+        return statistics.median(times)
+
+    if args.prefill_only:
+        ms = prefill_once(2048)
+        print(json.dumps({"prefill_ms": round(ms, 3), "tokens": 2048, "n_layer": cfgd["n_layer"]}))
+        return 0
+
     # ---- main measurement: decode at the default batch, clocks sampled meanwhile -------------
     sampler = ClockSampler()
     sampler.start()
@@ -207,20 +232,7 @@ def main() -> int:
     if not args.skip_points:
         # ---- prefill of 2,048 tokens in one step ------------------------------------------------
         T = 2048
-        toks = prompts(1, T)[0]
-        times = []
-        for it in range(3 + 5):
-            slot = eng.open_request(1000 + it)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.forward_step([StepEntry(slot, 0, toks, [T - 1])])
-            e1.record()
-            torch.cuda.synchronize()
-            if it >= 3:
-                times.append(e0.elapsed_time(e1))
-            eng.close_request(slot)
-        ms = statistics.median(times)
+        ms = prefill_once(T)
         d, F, L = cfgd["n_embd"], cfgd["n_inner"], cfgd["n_layer"]
         flops = L * (2 * T * (3 * d * d + d * d + 2 * d * F) + 2 * T * T * d) + 2 * d * V
         result["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),

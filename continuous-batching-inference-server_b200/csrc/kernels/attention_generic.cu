@@ -34,6 +34,28 @@ __global__ void kv_write_kernel(const TT* qkv, int ld, int k_off, int v_off, TT*
   }
 }
 
+// The same with 16-byte moves, for head sizes that are a multiple of 8 (bfloat16) or 4 (float).
+template <typename TT>
+__global__ void kv_write_vec_kernel(const TT* qkv, int ld, int k_off, int v_off, TT* kc, TT* vc,
+                                    const int* slot_mapping, int n_kv_head, int hd, int ps) {
+  constexpr int E = 16 / sizeof(TT);  // elements per 16 bytes
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int slot = slot_mapping[r];
+  if (slot < 0) return;
+  const int page = slot / ps, off = slot % ps;
+  const TT* krow = qkv + (size_t)r * ld + k_off;
+  const TT* vrow = qkv + (size_t)r * ld + v_off;
+  const int chunks = n_kv_head * hd / E, per_head = hd / E;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const int h = c / per_head, i = (c % per_head) * E;
+    const size_t dst = (((size_t)page * n_kv_head + h) * ps + off) * hd + i;
+    *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(krow + c * E);
+    *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(vrow + c * E);
+  }
+}
+
 // One warp per (row, query head).  The query at position p sees keys max(0, p-window+1)..p
 // (window 0: all keys 0..p; the loop bound is the causal mask, kernels/attention.cu:67-68,78).
 // Online softmax with running max m, normaliser l and accumulator acc as in
@@ -136,6 +158,15 @@ CBIS_EXPORT int cbis_kv_write(const void* qkv, int ld, int k_off, int v_off, voi
   const int width = n_kv_head * hd;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   cudaStream_t st = (cudaStream_t)stream;
+  const int esz = dtype == CBIS_F32 ? 4 : 2, per16 = 16 / esz;
+  const bool vec = hd % per16 == 0 && ld % per16 == 0 && k_off % per16 == 0 && v_off % per16 == 0 &&
+                   !(((uintptr_t)qkv | (uintptr_t)kc | (uintptr_t)vc) & 15);
+  if (vec && dtype == CBIS_F32)
+    return (int)launch_pdl(kv_write_vec_kernel<float>, dim3(T), dim3(128), 0, st, (const float*)qkv, ld, k_off, v_off,
+                           (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, ps);
+  if (vec && dtype == CBIS_BF16)
+    return (int)launch_pdl(kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, st, (const __nv_bfloat16*)qkv, ld,
+                           k_off, v_off, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, slot_mapping, n_kv_head, hd, ps);
   if (dtype == CBIS_F32)
     return (int)launch_pdl(kv_write_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)qkv, ld, k_off, v_off,
                            (float*)kc, (float*)vc, slot_mapping, n_kv_head, hd, ps);

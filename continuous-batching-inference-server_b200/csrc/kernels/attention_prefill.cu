@@ -52,7 +52,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // step's segment tables: rows cu_rows[s]..cu_rows[s+1] of q/out belong to segment s and start at
 // position seg_start[s].
 template <int HD>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, 3)
 paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                           const int* block_table, int max_blocks, const int* cu_rows, const int* seg_start,
                           __nv_bfloat16* out, int out_ld, int seg0, int n_head, int n_kv_head, int ps_shift,

@@ -79,6 +79,91 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const TD* delta,
   }
 }
 
+// The same for widths that are a multiple of 4 and at most 128*4*NV: the row stays in registers
+// (NV float4 per thread, 128 threads per row), every access is 16 bytes wide, no staging in shared
+// memory.  TD/TO: float or bfloat16.
+template <typename TT>
+__device__ __forceinline__ float4 load4(const TT* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *reinterpret_cast<uint32_t*>(&a);
+  r.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename TD, typename TO, int NV>
+__global__ void __launch_bounds__(128)
+add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ delta_bias,
+                         const float* __restrict__ gamma, const float* __restrict__ beta, float eps, TO* __restrict__ out,
+                         const int* rows, int d) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int s = rows ? rows[r] : r;
+  float* xrow = x + (size_t)s * d;
+  const TD* drow = delta ? delta + (size_t)s * d : nullptr;
+  const int nvec = d >> 2;
+  float4 v[NV];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * 128;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < nvec) {
+      v[i] = *reinterpret_cast<const float4*>(xrow + 4 * c);
+      if (drow) {
+        const float4 t = load4<TD>(drow + 4 * c);
+        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+      }
+      if (delta_bias) {
+        const float4 t = *reinterpret_cast<const float4*>(delta_bias + 4 * c);
+        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+      }
+      sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+  }
+  const float mean = block_sum(sum, red) / (float)d;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (threadIdx.x + i * 128 < nvec) {
+      const float a = v[i].x - mean, b = v[i].y - mean, c2 = v[i].z - mean, e = v[i].w - mean;
+      sq += (a * a + b * b) + (c2 * c2 + e * e);
+    }
+  }
+  const float var = block_sum(sq, red) / (float)d;
+  const float inv = rsqrtf(var + eps);
+  const bool write_x = rows == nullptr && (drow != nullptr || delta_bias != nullptr);
+  TO* orow = out + (size_t)r * d;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * 128;
+    if (c < nvec) {
+      if (write_x) *reinterpret_cast<float4*>(xrow + 4 * c) = v[i];
+      const float4 gm = *reinterpret_cast<const float4*>(gamma + 4 * c);
+      const float4 bt = *reinterpret_cast<const float4*>(beta + 4 * c);
+      float4 y;
+      y.x = (v[i].x - mean) * inv * gm.x + bt.x;
+      y.y = (v[i].y - mean) * inv * gm.y + bt.y;
+      y.z = (v[i].z - mean) * inv * gm.z + bt.z;
+      y.w = (v[i].w - mean) * inv * gm.w + bt.w;
+      store4(orow + 4 * c, y);
+    }
+  }
+}
+
 // x[m,n] = act(x[m,n] + bias[n]) in place (reference: add_bias_rowmajor kernels/linear.cu:6-12 + gelu_kernel).
 template <typename TT>
 __global__ void bias_act_kernel(TT* __restrict__ x, const float* __restrict__ bias, int act, size_t total, int n) {
@@ -129,6 +214,19 @@ template <typename TD, typename TO>
 static int launch_add_layernorm(float* x, const void* delta, const float* delta_bias, const float* gamma,
                                 const float* beta, float eps, void* out, const int* rows, int R, int d,
                                 cudaStream_t st) {
+  const bool aligned = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta_bias | (uintptr_t)gamma | (uintptr_t)beta |
+                          (uintptr_t)out) & 15);
+  if (d % 4 == 0 && d <= 128 * 4 * 16 && aligned) {  // the row fits into the registers of 128 threads
+#define CBIS_LN(NV)                                                                                              \
+  return (int)launch_pdl(add_layernorm_reg_kernel<TD, TO, NV>, dim3(R), dim3(128), 0, st, x, (const TD*)delta, \
+                         delta_bias, gamma, beta, eps, (TO*)out, rows, d)
+    if (d <= 128 * 4 * 1) CBIS_LN(1);
+    if (d <= 128 * 4 * 2) CBIS_LN(2);
+    if (d <= 128 * 4 * 4) CBIS_LN(4);
+    if (d <= 128 * 4 * 8) CBIS_LN(8);
+    CBIS_LN(16);
+#undef CBIS_LN
+  }
   const size_t smem = (size_t)(d + 33) * sizeof(float);
   if (smem > 200 * 1024) return CBIS_ERR_TOO_LARGE;
   auto kern = add_layernorm_kernel<TD, TO>;
