@@ -244,6 +244,20 @@ __device__ __forceinline__ uint4 ldcg16(const void* p) {
   asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
+// Keys and values are read once per step: they are marked to leave L2 first, so that they do not push
+// out the weights that the products have prefetched.
+__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint4 ldcg16_stream(const void* p, unsigned long long pol) {
+  uint4 v;
+  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(pol));
+  return v;
+}
 
 __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                           uint32_t b1) {
@@ -312,6 +326,7 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
   const int vsub = lane % LPK, vgrp = lane / LPK;
+  const unsigned long long pol = l2_evict_first_policy();
 
   for (int tile = (ks >> 4) + warp; (tile << 4) < ke; tile += DEC_WARPS) {
     const int j0 = tile << 4;
@@ -321,9 +336,9 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8);
+      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) vb[i] = ldcg16(vc + base + (size_t)i * 256 + lane * 8);
+    for (int i = 0; i < NV; ++i) vb[i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
     // scores of the 16 keys: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1)
     float sc[2][4];
 #pragma unroll

@@ -73,6 +73,26 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   return launch_after(true, kernel, grid, block, smem, st, args...);
 }
 
+// Asks the memory system to bring [p, p + bytes) into L2 (bytes a multiple of 16, p 16-byte aligned);
+// nothing waits for it.  Used to have the NEXT kernel's weights on their way while this one runs.
+__device__ __forceinline__ void prefetch_l2(const void* p, unsigned int bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// This block's share of a prefetch of `bytes` bytes at `p`, spread evenly over the grid, in pieces of 16 KB.
+__device__ __forceinline__ void prefetch_share(const void* p, unsigned long long bytes, unsigned int block,
+                                               unsigned int n_blocks) {
+  if (p == nullptr || bytes == 0) return;
+  unsigned long long chunk = ((bytes + n_blocks - 1) / n_blocks + 15ull) & ~15ull;
+  unsigned long long off = (unsigned long long)block * chunk;
+  if (off >= bytes) return;
+  unsigned long long end = off + chunk < bytes ? off + chunk : (bytes & ~15ull);
+  for (; off < end; off += 16384ull) {
+    const unsigned long long n = end - off < 16384ull ? end - off : 16384ull;
+    prefetch_l2(static_cast<const char*>(p) + off, (unsigned int)n);
+  }
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void from_f32(float& dst, float v) { dst = v; }

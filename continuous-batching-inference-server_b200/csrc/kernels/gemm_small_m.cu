@@ -35,7 +35,8 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
-                    const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act) {
+                    const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
+                    const void* next_w, unsigned long long next_bytes) {
   extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -69,6 +70,9 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
     }
 
   pdl_trigger();
+  // The weights of the product that runs after this one start towards L2 now: by the time that kernel
+  // starts it reads them from L2, and HBM keeps streaming while the short kernels in between run.
+  if (threadIdx.x == 0) prefetch_share(next_w, next_bytes, blockIdx.x, gridDim.x);
   bool waited = false;
   for (int kb0 = warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
     uint4 wv[UNROLL][NT], av[UNROLL][MT][2];
@@ -137,7 +141,7 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
 
 template <int MT, int NT, int UNROLL, typename TO>
 static int launch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
-                          int K, int act, cudaStream_t st) {
+                          int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
   const size_t smem = (size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) * sizeof(float);
   auto kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
   if (smem > 48 * 1024) {
@@ -146,24 +150,24 @@ static int launch_small_m(const void* A, int lda, const void* W, const float* bi
   }
   const int blocks = (N + NT * 8 - 1) / (NT * 8);
   return (int)launch_pdl(kern, dim3(blocks), dim3(SM_WARPS * 32), smem, st, (const __nv_bfloat16*)A, lda,
-                         (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act);
+                         (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act, next_w, next_bytes);
 }
 
 template <typename TO>
 static int dispatch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
-                            int K, int act, cudaStream_t st) {
+                            int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
   // Columns per block: 16 when that still gives the 148 SMs about two blocks each, else 8.
   const bool wide = N >= 148 * 2 * 16;
   if (M <= 16) {
-    if (wide) return launch_small_m<1, 2, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
-    return launch_small_m<1, 1, 8, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+    if (wide) return launch_small_m<1, 2, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    return launch_small_m<1, 1, 8, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   }
   if (M <= 32) {
-    if (wide) return launch_small_m<2, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
-    return launch_small_m<2, 1, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+    if (wide) return launch_small_m<2, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    return launch_small_m<2, 1, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   }
-  if (wide) return launch_small_m<4, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
-  return launch_small_m<4, 1, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  if (wide) return launch_small_m<4, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  return launch_small_m<4, 1, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
 }
 
 }  // namespace cbis
@@ -172,13 +176,16 @@ using namespace cbis;
 
 // A [M, lda>=K] bfloat16, W [N, K] bfloat16, bias [N] float or null, C [M, ldc>=N] bfloat16 or float.
 // Takes M <= 64 and K a multiple of 8 with 16-byte aligned operands; refuses anything else.
+// next_w / next_bytes: weights of the product that will run after this one (16-byte aligned), or null:
+// they are prefetched into L2 while this kernel runs.
 CBIS_EXPORT int cbis_gemm_small_m_bf16(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
-                                       int M, int N, int K, int act, int out_dtype, void* stream) {
+                                       int M, int N, int K, int act, int out_dtype, const void* next_w,
+                                       unsigned long long next_bytes, void* stream) {
   if (M <= 0 || N <= 0) return CBIS_OK;
   if (M > 64 || K <= 0 || K % 8 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
-  if (lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return CBIS_ERR_ALIGNMENT;
+  if (lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)next_w & 15)) return CBIS_ERR_ALIGNMENT;
   cudaStream_t st = (cudaStream_t)stream;
-  if (out_dtype == CBIS_BF16) return dispatch_small_m<__nv_bfloat16>(A, lda, W, bias, C, ldc, M, N, K, act, st);
-  if (out_dtype == CBIS_F32) return dispatch_small_m<float>(A, lda, W, bias, C, ldc, M, N, K, act, st);
+  if (out_dtype == CBIS_BF16) return dispatch_small_m<__nv_bfloat16>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  if (out_dtype == CBIS_F32) return dispatch_small_m<float>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   return CBIS_ERR_BAD_DTYPE;
 }

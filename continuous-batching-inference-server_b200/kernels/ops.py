@@ -139,6 +139,23 @@ def linear_f32(x, w, bias, act, out, w_is_nk=False):
 SMALL_M = 16      # rows up to which the weight-streaming kernel takes a bfloat16 product (it can take 64)
 
 
+_next_weight = {}      # data_ptr of a weight -> weak reference to the weight used after it
+PREFETCH_CAP = 64 << 20   # bytes of a successor's weights brought into L2 ahead of time (L2 holds 126 MB)
+
+
+def add_weight_order(weights) -> None:
+    """Tells the few-rows product in which order a decode step uses its weights (a cycle: after the
+    last comes the first of the next step), so that each product can prefetch its successor's weights
+    into L2 while it runs.  Only weak references are kept: a freed model's entries die with it."""
+    import weakref
+    ws = [w for w in weights if w is not None and w.is_cuda and w.dtype == torch.bfloat16]
+    for a, b in zip(ws, ws[1:] + ws[:1]):
+        if a.data_ptr() != b.data_ptr():
+            _next_weight[a.data_ptr()] = weakref.ref(b)
+    for k in [k for k, r in _next_weight.items() if r() is None]:
+        del _next_weight[k]
+
+
 def gemm_small_m(x, w_nk, bias, act, out):
     """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16, 32-bit accumulation (weight streaming)."""
     _need_cuda(x, w_nk, bias, out)
@@ -146,9 +163,12 @@ def gemm_small_m(x, w_nk, bias, act, out):
     N = w_nk.shape[0]
     assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
+    ref = _next_weight.get(w_nk.data_ptr())
+    nxt = ref() if ref is not None else None
     st = kernels().cbis_gemm_small_m_bf16(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
                                           c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
-                                          c_int(dtype_code(out.dtype)), _stream())
+                                          c_int(dtype_code(out.dtype)), _ptr(nxt),
+                                          ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0), _stream())
     _check(st, "gemm_small_m", f"M={M} N={N} K={K}")
 
 

@@ -90,7 +90,18 @@ class Model:
         self.final_norm.load(s.final_norm_prefix, tensors, dtype, device)
         self.head = (self.token_table if s.head is None
                      else tensors[s.head].to(device=device, dtype=dtype).contiguous())
+        self.register_weight_order()
         return self
+
+    def register_weight_order(self) -> None:
+        """The order in which a step reads the big matrices, for prefetching one ahead (bfloat16 on a GPU)."""
+        if self.dtype != torch.bfloat16 or self.device.type != "cuda":
+            return
+        order = []
+        for li in self.spec.schedule:
+            layer = self.layers[li]
+            order += layer.mixer.streamed_weights() + layer.feed_forward.streamed_weights()
+        ops.add_weight_order(order + [self.head])
 
     def weight_bytes(self) -> int:
         """Bytes of all weights a step reads (each once; a tied head counts once)."""

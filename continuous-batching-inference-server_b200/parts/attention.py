@@ -47,6 +47,9 @@ class PagedAttention(Mixer):
         self.w_o = self._matrix_nk(tensors[f"{prefix}{self.proj_name}.weight"], dtype, device)
         self.b_o = self._vector(tensors[f"{prefix}{self.proj_name}.bias"], device)
 
+    def streamed_weights(self):
+        return [self.w_qkv, self.w_o]
+
     def forward(self, ctx, h, cache, state):
         if cache is None:
             raise RuntimeError("attention needs a cache: its own or the layer's it reads")

@@ -62,6 +62,11 @@ class Part:
         """Takes its tensors (stored dtype, CPU or device) and keeps them on ``device``:
         matrices and tables in ``dtype``, vectors in float32."""
 
+    def streamed_weights(self) -> List[torch.Tensor]:
+        """The matrices a decode step reads through this part, in the order it uses them (so that the
+        product before can prefetch them)."""
+        return []
+
     @staticmethod
     def _matrix(t: torch.Tensor, dtype, device) -> torch.Tensor:
         return t.to(device=device, dtype=dtype).contiguous()

@@ -33,6 +33,9 @@ class DenseFeedForward(FeedForward):
         self.w2 = self._matrix_nk(tensors[f"{prefix}{self.proj}.weight"], dtype, device)
         self.b2 = self._vector(tensors[f"{prefix}{self.proj}.bias"], device)
 
+    def streamed_weights(self):
+        return [self.w1, self.w2]
+
     def forward(self, ctx, h):
         a = ops.linear(h, self.w1, self.b1, self.activation)
         return Delta(ops.linear(a, self.w2, None, None, out_dtype=torch.float32), self.b2)
