@@ -283,11 +283,14 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
   __shared__ float sm_p[DEC_WARPS][16];
   __shared__ bool is_last;
   pdl_trigger();
-  pdl_wait();
+  // The step's tables (rows, positions, block tables) were written before the step's first kernel and the
+  // cached keys and values of earlier positions by earlier steps: they are read, and this warp's first
+  // tile is fetched, while the kernels ahead (the projection of this step's q, k, v) still run.
   const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int seq = row_seq[row];
   if (seq < 0) {  // a padding row of a fixed-size batch
+    pdl_wait();
     if (split == 0)
       for (int t = threadIdx.x; t < HD; t += blockDim.x) out[(size_t)row * out_ld + h * HD + t] = __float2bfloat16_rn(0.f);
     return;
@@ -302,6 +305,26 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
   const int ke = min(kend, ks + per);
   const int* bt = block_table + (size_t)seq * max_blocks;
   const int g = lane >> 2, t = lane & 3;
+
+  const int vsub = lane % LPK, vgrp = lane / LPK;
+  const unsigned long long pol = l2_evict_first_policy();
+  uint4 kb[2][NC], vb[NV];
+  auto load_tile = [&](int tile) {
+    const int j0 = tile << 4;
+    const int page = bt[j0 / ps];
+    const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j0 % ps)) * HD;   // 16 keys from here are one run
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) vb[i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
+  };
+  int tile = (ks >> 4) + warp;
+  // not the tile that holds the current token: its key and value are stored below, after the wait
+  bool preloaded = (tile << 4) < ke && tile != (pos >> 4);
+  if (preloaded) load_tile(tile);
+  pdl_wait();
 
   // The current token's key and value go into their page first; the loop below then reads them
   // like any other key.  (Blocks of query heads that share this key/value head store the same values.)
@@ -325,20 +348,11 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  const int vsub = lane % LPK, vgrp = lane / LPK;
-  const unsigned long long pol = l2_evict_first_policy();
 
-  for (int tile = (ks >> 4) + warp; (tile << 4) < ke; tile += DEC_WARPS) {
+  for (; (tile << 4) < ke; tile += DEC_WARPS) {
     const int j0 = tile << 4;
-    const int page = bt[j0 / ps];
-    const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j0 % ps)) * HD;   // 16 keys from here are one run
-    uint4 kb[2][NC], vb[NV];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
-#pragma unroll
-    for (int i = 0; i < NV; ++i) vb[i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
+    if (!preloaded) load_tile(tile);
+    preloaded = false;
     // scores of the 16 keys: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1)
     float sc[2][4];
 #pragma unroll

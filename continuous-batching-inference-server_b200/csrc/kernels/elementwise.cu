@@ -109,12 +109,24 @@ add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ de
                          const int* rows, int d) {
   __shared__ float red[33];
   pdl_trigger();
+  const int nvec = d >> 2;
+  // parameters first: no earlier kernel writes them, so they are fetched while the kernels ahead still run
+  float4 gm[NV], bt[NV], db[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = threadIdx.x + i * 128;
+    gm[i] = bt[i] = db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < nvec) {
+      gm[i] = *reinterpret_cast<const float4*>(gamma + 4 * c);
+      bt[i] = *reinterpret_cast<const float4*>(beta + 4 * c);
+      if (delta_bias) db[i] = *reinterpret_cast<const float4*>(delta_bias + 4 * c);
+    }
+  }
   pdl_wait();
   const int r = blockIdx.x;
   const int s = rows ? rows[r] : r;
   float* xrow = x + (size_t)s * d;
   const TD* drow = delta ? delta + (size_t)s * d : nullptr;
-  const int nvec = d >> 2;
   float4 v[NV];
   float sum = 0.f;
 #pragma unroll
@@ -127,10 +139,7 @@ add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ de
         const float4 t = load4<TD>(drow + 4 * c);
         v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
       }
-      if (delta_bias) {
-        const float4 t = *reinterpret_cast<const float4*>(delta_bias + 4 * c);
-        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
-      }
+      v[i].x += db[i].x; v[i].y += db[i].y; v[i].z += db[i].z; v[i].w += db[i].w;
       sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     }
   }
@@ -152,13 +161,11 @@ add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ de
     const int c = threadIdx.x + i * 128;
     if (c < nvec) {
       if (write_x) *reinterpret_cast<float4*>(xrow + 4 * c) = v[i];
-      const float4 gm = *reinterpret_cast<const float4*>(gamma + 4 * c);
-      const float4 bt = *reinterpret_cast<const float4*>(beta + 4 * c);
       float4 y;
-      y.x = (v[i].x - mean) * inv * gm.x + bt.x;
-      y.y = (v[i].y - mean) * inv * gm.y + bt.y;
-      y.z = (v[i].z - mean) * inv * gm.z + bt.z;
-      y.w = (v[i].w - mean) * inv * gm.w + bt.w;
+      y.x = (v[i].x - mean) * inv * gm[i].x + bt[i].x;
+      y.y = (v[i].y - mean) * inv * gm[i].y + bt[i].y;
+      y.z = (v[i].z - mean) * inv * gm[i].z + bt[i].z;
+      y.w = (v[i].w - mean) * inv * gm[i].w + bt[i].w;
       store4(orow + 4 * c, y);
     }
   }

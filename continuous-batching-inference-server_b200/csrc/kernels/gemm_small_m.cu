@@ -73,6 +73,12 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
   // The weights of the product that runs after this one start towards L2 now: by the time that kernel
   // starts it reads them from L2, and HBM keeps streaming while the short kernels in between run.
   if (threadIdx.x == 0) prefetch_share(next_w, next_bytes, blockIdx.x, gridDim.x);
+  // the bias of this thread's first output column is fetched now (the epilogue maps idx -> column idx % (NT*8))
+  float bias0 = 0.f;
+  {
+    const int n = n0 + (int)(threadIdx.x % (NT * 8));
+    if (bias && n < N) bias0 = bias[n];
+  }
   bool waited = false;
   for (int kb0 = warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
     uint4 wv[UNROLL][NT], av[UNROLL][MT][2];
@@ -127,6 +133,7 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
       mine[(i * 16 + g + 8) * RS + j * 8 + 2 * t + 1] = acc[i][j][3];
     }
   __syncthreads();
+  // blockDim (256) is a multiple of NT*8, so a thread meets the same column at every idx it takes
   for (int idx = threadIdx.x; idx < M * (NT * 8); idx += blockDim.x) {
     const int m = idx / (NT * 8), c = idx % (NT * 8);
     const int n = n0 + c;
@@ -134,7 +141,7 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < SM_WARPS; ++w) v += red[((size_t)w * (MT * 16) + m) * RS + c];
-    if (bias) v += bias[n];
+    v += bias0;
     from_f32(C[(size_t)m * ldc + n], activate(v, act));
   }
 }
