@@ -66,7 +66,8 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   __nv_bfloat16* sV = sK + 2 * PF_BN * PITCH;                                // [2][PF_BN][PITCH]
   pdl_trigger();
   pdl_wait();
-  const int seg = seg0 + blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+  // late row tiles have the most keys to walk: they are given out first, the short ones fill the end
+  const int seg = seg0 + blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * PF_BM >= n_rows) return;
   const int hk = h / (n_head / n_kv_head);

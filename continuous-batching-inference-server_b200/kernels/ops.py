@@ -140,6 +140,7 @@ SMALL_M = 16      # rows up to which the weight-streaming kernel takes a bfloat1
 
 
 _next_weight = {}      # data_ptr of a weight -> weak reference to the weight used after it
+PREFETCH_AHEAD = int(__import__("os").environ.get("CBIS_PREFETCH_AHEAD", "2"))   # products ahead
 PREFETCH_CAP = 64 << 20   # bytes of a successor's weights brought into L2 ahead of time (L2 holds 126 MB)
 
 
@@ -149,7 +150,8 @@ def add_weight_order(weights) -> None:
     into L2 while it runs.  Only weak references are kept: a freed model's entries die with it."""
     import weakref
     ws = [w for w in weights if w is not None and w.is_cuda and w.dtype == torch.bfloat16]
-    for a, b in zip(ws, ws[1:] + ws[:1]):
+    ahead = PREFETCH_AHEAD % max(1, len(ws))
+    for a, b in zip(ws, ws[ahead:] + ws[:ahead]):
         if a.data_ptr() != b.data_ptr():
             _next_weight[a.data_ptr()] = weakref.ref(b)
     for k in [k for k, r in _next_weight.items() if r() is None]:
@@ -170,6 +172,31 @@ def gemm_small_m(x, w_nk, bias, act, out):
                                           c_int(dtype_code(out.dtype)), _ptr(nxt),
                                           ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0), _stream())
     _check(st, "gemm_small_m", f"M={M} N={N} K={K}")
+
+
+_tc_error = {}
+
+
+def tcgen05_error_flag(device) -> torch.Tensor:
+    """int32[1] on the device that the tcgen05 product sets when one of its bounded waits runs out."""
+    key = torch.device(device).index or 0
+    if key not in _tc_error:
+        _tc_error[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_error[key]
+
+
+def gemm_tcgen05(x, w_nk, bias, act, out):
+    """out = act(x @ w_nk^T + bias) on the tcgen05 tensor cores (TMA operands, accumulator in tensor
+    memory, bias and activation on the 32-bit sums).  bfloat16, K a multiple of 8."""
+    _need_cuda(x, w_nk, bias, out)
+    M, K = x.shape
+    N = w_nk.shape[0]
+    assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
+    st = kernels().cbis_gemm_tcgen05_bf16(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
+                                          c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
+                                          c_int(dtype_code(out.dtype)), _ptr(tcgen05_error_flag(x.device)), _stream())
+    _check(st, "gemm_tcgen05", f"M={M} N={N} K={K}")
 
 
 def linear(x, w_nk, bias, act=None, out_dtype=None):
