@@ -416,3 +416,19 @@ def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal(ops):
     p = torch.softmax(sc, -1)
     assert p[250, 3] > 0.9 and p[100, 101] == 0
     assert (out.double().cpu() - p @ v.double()).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 136), (1000, 512, 2048), (77, 5001, 96), (2048, 768, 320)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_tcgen05(ops, M, N, K, out_dtype):
+    """The TMA + tcgen05 product with its fused epilogue: sizes that are no multiple of its 128x256x64 tiles."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+    ops.gemm_tcgen05(dev(x), dev(w), dev(b), "gelu_tanh", out)
+    ref = plain_gpt.gelu(x.double() @ w.double().t() + b.double(), "gelu_new")
+    tol = 1e-5 * math.sqrt(K) if out_dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+    assert ops.tcgen05_error_flag("cuda").item() == 0            # no bounded wait ran out
