@@ -4,7 +4,7 @@
 // into shared memory with TMA (cp.async.bulk.tensor, 128-byte swizzle, four stages, mbarriers with
 // transaction counts); one thread issues tcgen05.mma (M=128, N=256, K=16, bf16 in, 32-bit
 // accumulate) with the accumulator in tensor memory (two of 256 columns, taking turns); four warps read
-// the accumulator of the tile before back with tcgen05.ld, add the bias and apply the activation on the 32-bit sums, round ONCE and
+// the accumulator of the tile before back with tcgen05.ld (sixteen warps: the GELU of a tile costs more instructions than its products take cycles), add the bias and apply the activation on the 32-bit sums, round ONCE and
 // store.  The reference does cublasSgemm, then a bias kernel, then a GELU kernel
 // (kernels/linear.cu:15-34, kernels/elementwise.cu:59-66).
 //
@@ -21,7 +21,8 @@ namespace cbis {
 constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2, TC_B_BYTES = TC_BN * TC_BK * 2;
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr int TC_THREADS = 192;  // warp 0: TMA, warp 1: MMA + tensor-memory allocation, warps 2..5: epilogue
+constexpr int TC_EPI_WARPS = 16;  // four per quarter of tensor memory, 64 columns each
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;  // warp 0: TMA, warp 1: MMA + tensor-memory allocation, then the epilogue
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -168,7 +169,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int b2 = 0; b2 < 2; ++b2) {
       mbar_init(&acc_full[b2], 1);
-      mbar_init(&acc_empty[b2], 4);   // one arrival per epilogue warp
+      mbar_init(&acc_empty[b2], TC_EPI_WARPS);   // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -241,8 +242,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // epilogue: warp w reads the 32 lanes of its quarter of tensor memory (quarter = w % 4)
+    // epilogue: a warp can read the 32 lanes of the quarter of tensor memory given by its index % 4; the
+    // warps of a quarter split the 256 columns among them
     const int quarter = warp & 3;
+    constexpr int COLS = TC_BN / (TC_EPI_WARPS / 4);
+    const int col_first = ((warp - 2) >> 2) * COLS;
     const bool vec_ok = (ldc * sizeof(TO)) % 16 == 0 && ((uintptr_t)C & 15) == 0;
     unsigned local = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
@@ -255,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       if (*abort_flag) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+      for (int c0 = col_first; c0 < col_first + COLS; c0 += 32) {
         if (n0 + c0 >= N) break;
         float v[32];
         tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + buf * TC_BN + (unsigned)c0, v);

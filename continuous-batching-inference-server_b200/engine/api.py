@@ -132,7 +132,9 @@ class Engine:
             keys = torch.tensor([request_key(q.seed, p.request_id, p.output_index) for p, q in zip(sampling, params)],
                                 dtype=torch.int64).to(logits.device)
             ops.sample(logits, temps, keys, out)
-        return out.cpu().tolist()
+        tokens = out.cpu().tolist()
+        ops.raise_if_kernel_errors(logits.device)        # the host has just waited for the step anyway
+        return tokens
 
     def generate(self, prompts: Sequence[Sequence[int]],
                  params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[List[int]]:

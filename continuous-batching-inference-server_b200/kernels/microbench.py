@@ -3,6 +3,7 @@ launch streams from HBM, as in a real step) or launch by launch for profilers.
 
     python -m cbis_b200.kernels.microbench --op decode_attn --rows 8 --ctx 1536 --layers 24
     python -m cbis_b200.kernels.microbench --op gemm --rows 8 --n 6144 --k 2048
+    python -m cbis_b200.kernels.microbench --op gemm_tc --rows 2048 --n 8192 --k 2048
     python -m cbis_b200.kernels.microbench --op layernorm --rows 8 --k 2048
     python -m cbis_b200.kernels.microbench --op sample --rows 8 --n 50257
 
@@ -42,7 +43,7 @@ def timed(fn, use_graph=True, reps=20):
 def main():
     from cbis_b200.kernels import ops
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["decode_attn", "gemm", "layernorm", "sample"])
+    ap.add_argument("--op", required=True, choices=["decode_attn", "gemm", "gemm_tc", "layernorm", "sample"])
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
@@ -74,6 +75,24 @@ def main():
         t = timed(fn, not a.no_graph, a.reps) / L
         tl = timed(lib, not a.no_graph, a.reps) / L
         print(f"gemm M={M} N={a.n} K={a.k}: {mb:.1f} MB  own {t:.2f} us ({mb / t:.2f} TB/s)  library {tl:.2f} us ({mb / tl:.2f} TB/s)")
+    elif a.op == "gemm_tc":
+        x = torch.randn(M, a.k, device=dev, dtype=torch.bfloat16)
+        W = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(min(L, 4))]
+        bias = torch.randn(a.n, device=dev)
+        out = torch.empty(M, a.n, device=dev, dtype=torch.bfloat16)
+
+        def fn():
+            for w in W:
+                ops.gemm_tcgen05(x, w, bias, "gelu_erf", out)
+
+        def lib():
+            for w in W:
+                torch.mm(x, w.t(), out=out)
+        fl = 2.0 * M * a.n * a.k
+        t = timed(fn, not a.no_graph, a.reps) / len(W)
+        tl = timed(lib, not a.no_graph, a.reps) / len(W)
+        print(f"gemm_tc M={M} N={a.n} K={a.k}: tcgen05 with bias+GELU {t:.1f} us ({fl / t / 1e6:.0f} TFLOP/s)  "
+              f"library, no epilogue {tl:.1f} us ({fl / tl / 1e6:.0f} TFLOP/s)  error flag {ops.tcgen05_error_flag(dev).item()}")
     elif a.op == "layernorm":
         x = torch.randn(M, a.k, device=dev)
         delta = torch.randn(M, a.k, device=dev)

@@ -175,6 +175,19 @@ def gemm_small_m(x, w_nk, bias, act, out):
 
 
 _tc_error = {}
+USE_TCGEN05 = __import__("os").environ.get("CBIS_TCGEN05", "1") != "0"
+
+
+def raise_if_kernel_errors(device="cuda") -> None:
+    """Reads the error flag of the tcgen05 product (a 4-byte copy: call it where the host waits anyway)."""
+    key = torch.device(device).index or 0
+    flag = _tc_error.get(key)
+    if flag is not None:
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise KernelError(f"gemm_tcgen05: a bounded wait inside the kernel ran out (code {code}); its results are invalid")
+
 
 
 def tcgen05_error_flag(device) -> torch.Tensor:
@@ -203,9 +216,9 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
     """act(x @ W^T + bias) with W stored [N, K] (K contiguous).
 
     32-bit inputs: this package's FFMA kernel (no reduced-precision matrix mode).  bfloat16
-    inputs: up to 64 rows go to the weight-streaming tensor-core kernel with the bias and the
-    activation applied to the 32-bit sum; more rows go to the library GEMM with a 32-bit
-    result, then the bias/activation kernel, so both ways round once."""
+    inputs: up to 16 rows go to the weight-streaming tensor-core kernel; more rows with a bias or an
+    activation go to the TMA + tcgen05 kernel; both apply bias and activation to the 32-bit sums
+    and round once.  More rows without an epilogue go to the library GEMM."""
     M, K = x.shape
     N = w_nk.shape[0]
     if x.dtype == torch.float32:
@@ -221,6 +234,11 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
     plain = bias is None and not ACT[act]
     if out_dtype != torch.float32 and plain:
         return torch.mm(x, w_nk.t())
+    if USE_TCGEN05 and out_dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+        # a product with an epilogue: TMA + tcgen05 with bias and activation applied to the sums in tensor memory
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        gemm_tcgen05(x, w_nk, bias, act, out)
+        return out
     acc = torch.mm(x, w_nk.t(), out_dtype=torch.float32)
     if out_dtype == torch.float32:
         if not plain:
