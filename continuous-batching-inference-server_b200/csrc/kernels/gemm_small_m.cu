@@ -32,11 +32,13 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 }
 
 // MT: 16-row tiles of A (M <= 16*MT); NT: 8-column tiles of W per block; UNROLL: K blocks in flight per warp.
-template <int MT, int NT, int UNROLL, typename TO>
-__global__ void __launch_bounds__(SM_WARPS * 32)
-gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
-                    const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                    const void* next_w, unsigned long long next_bytes) {
+// LOW8: M <= 8, so rows 8..15 of the one row tile do not exist: their fragments are zeros and are never loaded
+// (fewer registers: four blocks fit on an SM instead of three).
+template <int MT, int NT, int UNROLL, bool LOW8, typename TO>
+__device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
+                                                  const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M,
+                                                  int N, int K, int act, const void* next_w,
+                                                  unsigned long long next_bytes) {
   extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1]
   constexpr int RS = NT * 8 + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -81,7 +83,7 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
   }
   bool waited = false;
   for (int kb0 = warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
-    uint4 wv[UNROLL][NT], av[UNROLL][MT][2];
+    uint4 wv[UNROLL][NT], av[UNROLL][MT][LOW8 ? 1 : 2];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int kb = kb0 + u * SM_WARPS;
@@ -100,7 +102,7 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
 #pragma unroll
       for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf)
+        for (int hlf = 0; hlf < (LOW8 ? 1 : 2); ++hlf)
           av[u][i][hlf] = (kin && avalid[i][hlf]) ? __ldcg(reinterpret_cast<const uint4*>(arow[i][hlf] + kb * 32))
                                                    : make_uint4(0, 0, 0, 0);
     }
@@ -109,8 +111,10 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         // physical k = t*8 + s*4 + {0,1} plays the fragment's k = 2t + {0,1}; + {2,3} plays 2t + 8 + {0,1}
-        const uint32_t a_s0[4] = {av[u][i][0].x, av[u][i][1].x, av[u][i][0].y, av[u][i][1].y};
-        const uint32_t a_s1[4] = {av[u][i][0].z, av[u][i][1].z, av[u][i][0].w, av[u][i][1].w};
+        const uint4 lo = av[u][i][0];
+        const uint4 hi = LOW8 ? make_uint4(0, 0, 0, 0) : av[u][i][LOW8 ? 0 : 1];
+        const uint32_t a_s0[4] = {lo.x, hi.x, lo.y, hi.y};
+        const uint32_t a_s1[4] = {lo.z, hi.z, lo.w, hi.w};
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
           mma_bf16_16816(acc[i][j], a_s0, wv[u][j].x, wv[u][j].y);
@@ -146,11 +150,31 @@ gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __rest
   }
 }
 
+// Two entry points over the same body: the compiler's own register choice for the general form (80 registers,
+// three blocks per SM), and a cap of 64 registers for the M <= 8 form so that four blocks fit.
 template <int MT, int NT, int UNROLL, typename TO>
+__global__ void __launch_bounds__(SM_WARPS * 32)
+gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
+                    const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
+                    const void* next_w, unsigned long long next_bytes) {
+  gemm_small_m_body<MT, NT, UNROLL, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes);
+}
+template <int MT, int NT, int UNROLL, typename TO>
+__global__ void __launch_bounds__(SM_WARPS * 32, 4)
+gemm_small_m_low8_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
+                         const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
+                         const void* next_w, unsigned long long next_bytes) {
+  gemm_small_m_body<MT, NT, UNROLL, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes);
+}
+
+template <int MT, int NT, int UNROLL, bool LOW8, typename TO>
 static int launch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
                           int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
   const size_t smem = (size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) * sizeof(float);
-  auto kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
+  void (*kern)(const __nv_bfloat16*, int, const __nv_bfloat16*, const float*, TO*, int, int, int, int, int, const void*,
+               unsigned long long);
+  if constexpr (LOW8) kern = gemm_small_m_low8_kernel<MT, NT, UNROLL, TO>;
+  else kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -165,16 +189,19 @@ static int dispatch_small_m(const void* A, int lda, const void* W, const float* 
                             int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
   // Columns per block: 16 when that still gives the 148 SMs about two blocks each, else 8.
   const bool wide = N >= 148 * 2 * 16;
+  // M <= 8 and more 16-column blocks than fit at three per SM (444): the 64-register form runs them in one round
+  if (M <= 8 && wide && (N + 15) / 16 > 3 * 148 && (N + 15) / 16 <= 4 * 148)
+    return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   if (M <= 16) {
-    if (wide) return launch_small_m<1, 2, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-    return launch_small_m<1, 1, 8, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    if (wide) return launch_small_m<1, 2, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    return launch_small_m<1, 1, 8, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   }
   if (M <= 32) {
-    if (wide) return launch_small_m<2, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-    return launch_small_m<2, 1, 4, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    if (wide) return launch_small_m<2, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    return launch_small_m<2, 1, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
   }
-  if (wide) return launch_small_m<4, 2, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-  return launch_small_m<4, 1, 2, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  if (wide) return launch_small_m<4, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  return launch_small_m<4, 1, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
 }
 
 }  // namespace cbis

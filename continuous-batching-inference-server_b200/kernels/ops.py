@@ -234,7 +234,9 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
     plain = bias is None and not ACT[act]
     if out_dtype != torch.float32 and plain:
         return torch.mm(x, w_nk.t())
-    if USE_TCGEN05 and out_dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+    enough_tiles = -(-M // 128) * -(-N // 256) >= 96       # its 128x256 tiles must cover most of the 148 SMs
+    if (USE_TCGEN05 and enough_tiles and out_dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0):
         # a product with an epilogue: TMA + tcgen05 with bias and activation applied to the sums in tensor memory
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_tcgen05(x, w_nk, bias, act, out)
