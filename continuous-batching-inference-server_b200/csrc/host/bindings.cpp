@@ -46,6 +46,7 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def("release_out_of_window", &CacheManager::release_out_of_window)
       .def("release", &CacheManager::release)
       .def("block_table", &CacheManager::block_table)
+      .def("table_len", &CacheManager::table_len)
       .def("token_slot", &CacheManager::token_slot)
       .def("check", &CacheManager::check);
 

@@ -176,6 +176,9 @@ class CacheManager {
 
   // Logical page -> physical page of the request in group g; -1 where a page was given back.
   const std::vector<int>& block_table(int slot, int g) const { return get(slot).tables.at(g); }
+  // Number of logical pages of the request in group g (cheap: lets a caller keep a copy of the table
+  // of a group without a window and fetch it again only when it has grown).
+  int table_len(int slot, int g) const { return (int)get(slot).tables.at(g).size(); }
 
   // Token slot (page * page_size + offset) of position pos.
   int token_slot(int slot, int g, int pos) const {

@@ -105,10 +105,13 @@ class Engine:
             return []
         for slot in self.scheduler.take_new_slots():
             self.pool.clear_state(slot)
-        entries = [StepEntry(p.slot, p.start, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
+        entries = []
+        for p in plan:
+            toks = p.tokens                    # one conversion from the native plan
+            entries.append(StepEntry(p.slot, p.start, toks, [len(toks) - 1] if p.sample else []))
         logits = self.runner.step(entries, borrow=True)
         self.steps += 1
-        self.last_step_tokens = sum(len(p.tokens) for p in plan)
+        self.last_step_tokens = sum(len(e.tokens) for e in entries)
         self.tokens_run += self.last_step_tokens
         sampling = [p for p in plan if p.sample]
         if not sampling:
@@ -133,7 +136,8 @@ class Engine:
                                 dtype=torch.int64).to(logits.device)
             ops.sample(logits, temps, keys, out)
         tokens = out.cpu().tolist()
-        ops.raise_if_kernel_errors(logits.device)        # the host has just waited for the step anyway
+        if self.last_step_tokens > R:                    # a step with prompt portions may have run the tcgen05 product
+            ops.raise_if_kernel_errors(logits.device)    # (the host has just waited for the step anyway)
         return tokens
 
     def generate(self, prompts: Sequence[Sequence[int]],

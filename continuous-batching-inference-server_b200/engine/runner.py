@@ -125,6 +125,7 @@ class ModelRunner:
         self._scratch = torch.empty(max(worst, 1), dtype=torch.float32, device=self.device)
         self._counters = torch.zeros(max(S * heads, 1), dtype=torch.int32, device=self.device)
         self.graph_replays = 0
+        self._table_cache: Dict[tuple, tuple] = {}   # (slot, group) -> (request id, pages, numpy row)
 
     # ------------------------------------------------------------------
     def _dev_view(self, name, n=None):
@@ -237,9 +238,10 @@ class ModelRunner:
             if pad_rows:
                 sm[n_real_rows:] = -1
                 bt[n_real_segs:] = -1
+            windowed = mgr.window(g) > 0
             for s, ei in enumerate(order):
                 e = entries[ei]
-                table = np.asarray(mgr.block_table(e.slot, g), dtype=np.int32)
+                table = self._table(e.slot, g, windowed)
                 bt[s, :len(table)] = table
                 bt[s, len(table):] = -1
                 pos = positions[cu[s]:cu[s + 1]]
@@ -266,6 +268,19 @@ class ModelRunner:
             ctx.groups.append(GroupView(self._dev_view(f"block_table{g}", S * mb).view(S, mb),
                                         self._dev_view(f"slot_mapping{g}", T), mb))
         return ctx
+
+    def _table(self, slot: int, g: int, windowed: bool) -> np.ndarray:
+        """The request's block table as an int32 array.  Tables of groups without a window only grow, so a
+        copy is kept per (slot, group) and fetched again only when the request or its page count changed."""
+        mgr = self.pool.manager
+        if windowed:
+            return np.asarray(mgr.block_table(slot, g), dtype=np.int32)
+        rid, n = mgr.request_id(slot), mgr.table_len(slot, g)
+        have = self._table_cache.get((slot, g))
+        if have is None or have[0] != rid or have[1] != n:
+            have = (rid, n, np.asarray(mgr.block_table(slot, g), dtype=np.int32))
+            self._table_cache[(slot, g)] = have
+        return have[2]
 
     def _bucket(self, n: int) -> int:
         b = 1
