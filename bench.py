@@ -36,6 +36,13 @@ sys.path.insert(0, ROOT)
 CONFIG_1_3B = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=24, n_embd=2048, n_head=16,
                    n_inner=8192, vocab_size=50257, n_positions=2048, activation_function="gelu",
                    layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+# Cerebras-GPT-6.7B and GPT-2 XL layer sizes (further configurations of the benchmark set)
+CONFIG_6_7B = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=32, n_embd=4096, n_head=32,
+                   n_inner=16384, vocab_size=50257, n_positions=2048, activation_function="gelu",
+                   layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+CONFIG_XL = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=48, n_embd=1600, n_head=25,
+                 n_inner=6400, vocab_size=50257, n_positions=1024, activation_function="gelu_new",
+                 layer_norm_epsilon=1e-5, tie_word_embeddings=True)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -104,8 +111,11 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl"],
+                    help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
+                         "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each)")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64, prefill and e2e")
@@ -129,7 +139,16 @@ def main() -> int:
     from cbis_b200.kernels import ops
 
     torch.cuda.set_device(0)
-    cfgd = dict(CONFIG_1_3B)
+    if args.config == "xl":
+        return mixed_workload(args, cb, torch)
+    if args.config == "6.7b":
+        args.skip_points = True
+        args.batch = args.batch or 64
+        args.steps = min(args.steps, 64)
+        args.prompt_len = args.prompt_len or (CONFIG_6_7B["n_positions"] - args.warmup - args.steps - 24)
+    args.batch = args.batch or 8
+    args.prompt_len = args.prompt_len or 1024
+    cfgd = dict(CONFIG_6_7B if args.config == "6.7b" else CONFIG_1_3B)
     n_layer_config = cfgd["n_layer"]
     if args.layers:
         cfgd["n_layer"] = args.layers
@@ -211,17 +230,17 @@ def main() -> int:
     step_bytes = model.weight_bytes() + B * ctx_mean * eng.pool.bytes_per_token()
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
     result = {
-        "metric": "decode tokens/s (Cerebras-GPT-1.3B shapes, batch 8, context 1024->2048)",
+        "metric": f"decode tokens/s (Cerebras-GPT-{args.config.upper()} shapes, batch {B}, context {PL}->{P})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), uniform random token ids)",
         "impl": "b200",
-        "config": {"model": "Cerebras-GPT-1.3B shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"],
+        "config": {"model": f"Cerebras-GPT-{args.config.upper()} shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"],
                    "n_layer_config": n_layer_config, "n_embd": cfgd["n_embd"], "n_head": cfgd["n_head"],
                    "n_inner": cfgd["n_inner"], "vocab_size": V, "n_positions": P, "activation": "gelu",
                    "tied_head": True, "global_batch": B, "prompt_len": PL, "seq_len": P,
                    "page_size": args.page_size, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2: every step reads all weights (2.6 GB) and the live cache"},
+                   "l2": "inputs larger than L2: every step reads all weights and the live cache"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"],
                      "bytes_per_step": int(step_bytes)},
@@ -271,6 +290,40 @@ def main() -> int:
                          "h2d_bytes_per_step": int(runner.bytes_per_step_h2d()), "d2h_bytes_per_step": 4 * B,
                          "device_ms_per_step": round(e0.elapsed_time(e1) / steps_e2e, 4)}
     print(json.dumps(result))
+    return 0
+
+
+def mixed_workload(args, cb, torch) -> int:
+    """GPT-2 XL layer sizes: 64 requests, prompt lengths uniform in 32..768, 256 outputs each, all submitted at
+    t = 0 and run by the scheduler (token budget 2,048, prompt portions of 512)."""
+    import random
+    cfgd = dict(CONFIG_XL)
+    if args.layers:
+        cfgd["n_layer"] = args.layers
+    n_req, n_out = 64, 256
+    eng = cb.Engine.from_random(cfgd, seed=1234, dtype="bfloat16", page_size=args.page_size,
+                                max_tokens=n_req * cfgd["n_positions"], max_num_seqs=n_req, max_batched_tokens=2048,
+                                prefill_chunk=512)
+    rng = random.Random(0)
+    prompts = [[rng.randrange(cfgd["vocab_size"]) for _ in range(rng.randint(32, 768))] for _ in range(n_req)]
+    eng.generate(prompts[:8], cb.SamplingParams(max_new_tokens=4))       # warm-up: kernels, some graphs
+    eng.generate(prompts, cb.SamplingParams(max_new_tokens=2))           # graphs of the large buckets
+    torch.cuda.synchronize()
+    steps0 = eng.steps
+    t0 = time.perf_counter()
+    outs = eng.generate(prompts, cb.SamplingParams(max_new_tokens=n_out))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    n_prompt, n_gen = sum(map(len, prompts)), sum(map(len, outs))
+    print(json.dumps({
+        "metric": "mixed continuous-batching workload, tokens/s (GPT-2 XL shapes, 64 requests, prompts 32-768, 256 outputs)",
+        "value": round((n_prompt + n_gen) / wall, 1), "unit": "tokens/s", "n_gpus": 1, "impl": "b200", "dtype": "bf16",
+        "decode_tokens_per_s": round(n_gen / wall, 1), "wall_s": round(wall, 3), "steps": eng.steps - steps0,
+        "prompt_tokens": n_prompt, "output_tokens": n_gen, "preemptions": eng.scheduler.preemptions(),
+        "higher_is_better": True, "data": "synthetic (random weights, uniform random token ids)",
+        "config": {"model": "GPT-2 XL shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"], "n_layer_config": 48,
+                   "n_embd": 1600, "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,
+                   "requests": n_req, "max_batched_tokens": 2048, "prefill_chunk": 512, "page_size": args.page_size}}))
     return 0
 
 

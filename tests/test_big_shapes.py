@@ -11,15 +11,21 @@ pytestmark = pytest.mark.gpu
 
 BIG = dict(architectures=["GPT2LMHeadModel"], n_layer=2, n_embd=2048, n_head=16, n_inner=8192, vocab_size=50257,
            n_positions=2048, activation_function="gelu", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+# GPT-2 XL layer sizes: 25 heads of 64, a width and an inner size that are no powers of two, tanh GELU
+XL = dict(architectures=["GPT2LMHeadModel"], n_layer=2, n_embd=1600, n_head=25, n_inner=6400, vocab_size=50257,
+          n_positions=1024, activation_function="gelu_new", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
 
 
-@pytest.fixture(scope="module")
-def engines():
+@pytest.fixture(scope="module", params=["1.3b", "xl"])
+def engines(request):
     import cbis_b200 as cb
+    cfg = BIG if request.param == "1.3b" else XL
     opts = dict(page_size=16, num_pages=80, max_num_seqs=4, max_batched_tokens=1024)
-    e32 = cb.Engine.from_random(BIG, seed=3, dtype="float32", weight_dtype=torch.bfloat16, **opts)
-    e16 = cb.Engine.from_random(BIG, seed=3, dtype="bfloat16", **opts)
-    return e32, e16
+    e32 = cb.Engine.from_random(cfg, seed=3, dtype="float32", weight_dtype=torch.bfloat16, **opts)
+    e16 = cb.Engine.from_random(cfg, seed=3, dtype="bfloat16", **opts)
+    yield e32, e16
+    del e32, e16
+    torch.cuda.empty_cache()
 
 
 def run_cut(eng, seqs, plan):
