@@ -4,6 +4,7 @@
 
 #include "cache_manager.hpp"
 #include "scheduler.hpp"
+#include "step_packer.hpp"
 
 namespace py = pybind11;
 using namespace cbis;
@@ -67,6 +68,7 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def_readonly("slot", &PlannedEntry::slot)
       .def_readonly("start", &PlannedEntry::start)
       .def_readonly("tokens", &PlannedEntry::tokens)
+      .def_property_readonly("n_tokens", [](const PlannedEntry& e) { return (int)e.tokens.size(); })
       .def_readonly("sample", &PlannedEntry::sample)
       .def_readonly("output_index", &PlannedEntry::output_index);
 
@@ -74,6 +76,38 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def_readonly("request_id", &Finished::request_id)
       .def_readonly("reason", &Finished::reason)
       .def_readonly("output", &Finished::output);
+
+  py::class_<PackEntry>(m, "PackEntry")
+      .def(py::init([](int slot, int start, std::vector<int> tokens, std::vector<int> want) {
+             PackEntry e;
+             e.slot = slot;
+             e.start = start;
+             e.tokens = std::move(tokens);
+             e.want = std::move(want);
+             return e;
+           }),
+           py::arg("slot"), py::arg("start"), py::arg("tokens"), py::arg("want"));
+
+  py::class_<PackInfo>(m, "PackInfo")
+      .def_readonly("n_rows", &PackInfo::n_rows)
+      .def_readonly("n_segments", &PackInfo::n_segments)
+      .def_readonly("n_logit_rows", &PackInfo::n_logit_rows)
+      .def_readonly("n_decode", &PackInfo::n_decode)
+      .def_readonly("max_seg_rows", &PackInfo::max_seg_rows)
+      .def_readonly("max_ctx", &PackInfo::max_ctx)
+      .def_readonly("seg_rows", &PackInfo::seg_rows)
+      .def_readonly("seg_ctx", &PackInfo::seg_ctx);
+
+  py::class_<StepPacker>(m, "StepPacker")
+      .def(py::init<const CacheManager*, int, int, int, int, std::vector<int>, int>(), py::arg("cache"),
+           py::arg("max_tokens"), py::arg("max_seqs"), py::arg("vocab"), py::arg("max_positions"),
+           py::arg("max_blocks"), py::arg("n_groups"), py::keep_alive<1, 2>())
+      .def("words", &StepPacker::words)
+      .def("layout", &StepPacker::layout)
+      .def("pack", &StepPacker::pack, py::arg("buffer"), py::arg("entries"), py::arg("pad_rows") = 0,
+           py::arg("all_logits") = false, py::arg("reserved_ahead") = false)
+      .def("pack_plan", &StepPacker::pack_plan, py::arg("buffer"), py::arg("plan"), py::arg("pad_rows") = 0,
+           py::arg("all_logits") = false);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<CacheManager*, SchedulerLimits>(), py::arg("cache"), py::arg("limits"),

@@ -105,13 +105,9 @@ class Engine:
             return []
         for slot in self.scheduler.take_new_slots():
             self.pool.clear_state(slot)
-        entries = []
-        for p in plan:
-            toks = p.tokens                    # one conversion from the native plan
-            entries.append(StepEntry(p.slot, p.start, toks, [len(toks) - 1] if p.sample else []))
-        logits = self.runner.step(entries, borrow=True)
+        logits = self.runner.step(plan, borrow=True)     # the native plan goes to the native packer as it is
         self.steps += 1
-        self.last_step_tokens = sum(len(e.tokens) for e in entries)
+        self.last_step_tokens = sum(p.n_tokens for p in plan)
         self.tokens_run += self.last_step_tokens
         sampling = [p for p in plan if p.sample]
         if not sampling:

@@ -18,6 +18,7 @@ import torch
 
 from ..cache import CachePool
 from ..kernels import ops
+from ..kernels.library import host
 from .attention_dispatch import run_attention
 
 
@@ -89,26 +90,16 @@ class ModelRunner:
         self.max_tokens, self.max_seqs = int(max_batched_tokens), int(max_num_seqs)
         self.device = model.device
         T, S = self.max_tokens, self.max_seqs
-        self._layout: Dict[str, tuple] = {}
-        off = 0
-
-        def field_(name, n):
-            nonlocal off
-            self._layout[name] = (off, n)
-            off += (n + 3) // 4 * 4      # 16-byte aligned fields
-
-        for name in ("tokens", "positions", "row_seq", "logit_rows"):
-            field_(name, T)
-        for name in ("seg_slot", "seg_start", "seg_ctx"):
-            field_(name, S)
-        field_("cu_rows", S + 1)
         self._n_groups = len(pool.groups)
-        for g in range(self._n_groups):
-            field_(f"slot_mapping{g}", T)
-            field_(f"block_table{g}", S * pool.max_blocks(g))
+        # the native packer validates a step and writes its description into the pinned buffer
+        self._packer = host().StepPacker(pool.manager, T, S, model.spec.vocab_size, model.spec.max_positions,
+                                         [pool.max_blocks(g) for g in range(self._n_groups)], self._n_groups)
+        self._layout: Dict[str, tuple] = dict(self._packer.layout())
+        off = self._packer.words()
         self._host = torch.zeros(off, dtype=torch.int32).pin_memory() if torch.cuda.is_available() \
             else torch.zeros(off, dtype=torch.int32)
         self._host_np = self._host.numpy()
+        self._host_ptr = self._host.data_ptr()
         self._dev = torch.zeros(off, dtype=torch.int32, device=self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = None    # event after the last host->device copy of the packed buffer
@@ -125,7 +116,6 @@ class ModelRunner:
         self._scratch = torch.empty(max(worst, 1), dtype=torch.float32, device=self.device)
         self._counters = torch.zeros(max(S * heads, 1), dtype=torch.int32, device=self.device)
         self.graph_replays = 0
-        self._table_cache: Dict[tuple, tuple] = {}   # (slot, group) -> (request id, pages, numpy row)
 
     # ------------------------------------------------------------------
     def _dev_view(self, name, n=None):
@@ -152,135 +142,55 @@ class ModelRunner:
                 self._counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
         return self._scratch, self._counters
 
-    def validate(self, entries: Sequence[StepEntry], reserved_ahead: bool = False) -> None:
-        spec, mgr = self.model.spec, self.pool.manager
-        if not entries:
-            raise StepError("a step needs at least one entry")
-        if len(entries) > self.max_seqs:
-            raise StepError(f"{len(entries)} requests in one step; the engine was made for {self.max_seqs}")
-        total = sum(len(e.tokens) for e in entries)
-        if total > self.max_tokens:
-            raise StepError(f"{total} tokens in one step; the engine was made for {self.max_tokens}")
-        seen = set()
-        for e in entries:
-            n = len(e.tokens)
-            if n == 0:
-                raise StepError(f"slot {e.slot}: an entry without tokens")
-            if e.slot in seen:
-                raise StepError(f"slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            if not mgr.live(e.slot):
-                raise StepError(f"slot {e.slot} holds no request")
-            if e.start < 0 or e.start + n > spec.max_positions:
-                raise StepError(f"slot {e.slot}: positions {e.start}..{e.start + n - 1} exceed the model's "
-                                f"{spec.max_positions} positions")
-            if reserved_ahead and mgr.length(e.slot) >= e.start + n:
-                pass
-            elif mgr.length(e.slot) != e.start + n:
-                raise StepError(f"slot {e.slot}: the cache holds room for {mgr.length(e.slot)} tokens, the step "
-                                f"brings tokens {e.start}..{e.start + n - 1}")
-            lo, hi = min(e.tokens), max(e.tokens)
-            if lo < 0 or hi >= spec.vocab_size:
-                raise StepError(f"slot {e.slot}: token id {lo if lo < 0 else hi} outside the vocabulary of "
-                                f"{spec.vocab_size}")
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise StepError(f"slot {e.slot}: wanted place {w} outside its {n} tokens")
+    def _pack(self, entries, pad_rows: int, all_logits: bool, reserved_ahead: bool):
+        """Validates and packs a step (StepEntry objects, or the scheduler's native plan) into the pinned
+        buffer and starts its copy to the device; returns the packer's summary."""
+        if self._copied is not None:
+            self._copied.synchronize()   # the last step's copy must have left the pinned buffer
+        try:
+            if entries and not isinstance(entries[0], StepEntry):
+                info = self._packer.pack_plan(self._host_ptr, entries, pad_rows, all_logits)
+            else:
+                native = [host().PackEntry(e.slot, e.start, list(e.tokens), list(e.want)) for e in entries]
+                info = self._packer.pack(self._host_ptr, native, pad_rows, all_logits, reserved_ahead)
+        except ValueError as err:
+            raise StepError(str(err)) from None
+        self._dev.copy_(self._host, non_blocking=True)
+        if self._copied is None:
+            self._copied = torch.cuda.Event()
+        self._copied.record()
+        return info
 
-    def build_context(self, entries: Sequence[StepEntry], pad_rows: int = 0, all_logits: bool = False,
+    def validate(self, entries: Sequence[StepEntry], reserved_ahead: bool = False) -> None:
+        """Raises StepError if the step does not fit the cache's state or the engine's limits (it is packed
+        into the host buffer on the way, which does no harm)."""
+        self._pack(entries, 0, False, reserved_ahead)
+
+    def build_context(self, entries, pad_rows: int = 0, all_logits: bool = False,
                       reserved_ahead: bool = False) -> StepContext:
         """Packs the step into the host buffer, copies it over, returns the views.
 
         ``pad_rows`` > 0 (decode-only steps): the step is laid out for exactly that many rows and
         segments; rows beyond the entries are padding (segment -1: no cache write, zero attention
         output).  ``all_logits``: every row's logits, whatever the entries want."""
-        self.validate(entries, reserved_ahead)
-        if self._copied is not None:
-            self._copied.synchronize()   # the last step's copy must have left the pinned buffer
-        mgr, pool = self.pool.manager, self.pool
-        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
-        S = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        tokens, positions, row_seq = (self._host_view(n, T) for n in ("tokens", "positions", "row_seq"))
-        seg_slot, seg_start, seg_ctx = (self._host_view(n, S) for n in ("seg_slot", "seg_start", "seg_ctx"))
-        cu = self._host_view("cu_rows", S + 1)
-        row0_of_entry = [0] * S
-        r = 0
-        cu[0] = 0
-        for s, ei in enumerate(order):
-            e = entries[ei]
-            n = len(e.tokens)
-            row0_of_entry[ei] = r
-            tokens[r:r + n] = np.asarray(e.tokens, dtype=np.int32)
-            positions[r:r + n] = np.arange(e.start, e.start + n, dtype=np.int32)
-            row_seq[r:r + n] = s
-            seg_slot[s], seg_start[s], seg_ctx[s] = e.slot, e.start, e.start + n
-            r += n
-            cu[s + 1] = r
-        n_real_rows, n_real_segs = T, S
-        if pad_rows:
-            assert all(len(e.tokens) == 1 for e in entries) and pad_rows >= S
-            for name, fill in (("tokens", 0), ("positions", 0), ("row_seq", -1)):
-                self._host_view(name, pad_rows)[T:] = fill
-            for name in ("seg_slot", "seg_start", "seg_ctx"):
-                self._host_view(name, pad_rows)[S:] = 0
-            self._host_view("cu_rows", pad_rows + 1)[:] = np.minimum(np.arange(pad_rows + 1), T)
-            T = S = pad_rows
-        want_rows = (list(range(T)) if all_logits
-                     else [row0_of_entry[ei] + w for ei, e in enumerate(entries) for w in e.want])
-        R = len(want_rows)
-        if R:
-            self._host_view("logit_rows", R)[:] = np.asarray(want_rows, dtype=np.int32)
-        for g in range(self._n_groups):
-            ps, mb = pool.page_size, pool.max_blocks(g)
-            sm = self._host_view(f"slot_mapping{g}", T)
-            bt = self._host_view(f"block_table{g}", S * mb).reshape(S, mb)
-            if pad_rows:
-                sm[n_real_rows:] = -1
-                bt[n_real_segs:] = -1
-            windowed = mgr.window(g) > 0
-            for s, ei in enumerate(order):
-                e = entries[ei]
-                table = self._table(e.slot, g, windowed)
-                bt[s, :len(table)] = table
-                bt[s, len(table):] = -1
-                pos = positions[cu[s]:cu[s + 1]]
-                sm[cu[s]:cu[s + 1]] = table[pos // ps] * ps + pos % ps
-        self._dev.copy_(self._host, non_blocking=True)
-        if self._copied is None:
-            self._copied = torch.cuda.Event()
-        self._copied.record()
-
+        info = self._pack(entries, pad_rows, all_logits, reserved_ahead)
+        pool = self.pool
+        T, S, R = info.n_rows, info.n_segments, info.n_logit_rows
         ctx = StepContext()
         ctx.dtype, ctx.pool, ctx.error_flag = self.model.dtype, pool, self.error_flag
         ctx.runner, ctx.max_positions, ctx.fixed_shapes = self, self.model.spec.max_positions, bool(pad_rows)
-        ctx.n_rows, ctx.n_segments, ctx.n_logit_rows = T, S, R
-        ctx.n_decode = T if pad_rows else sum(1 for e in entries if len(e.tokens) == 1)
+        ctx.n_rows, ctx.n_segments, ctx.n_logit_rows, ctx.n_decode = T, S, R, info.n_decode
         ctx.tokens, ctx.positions, ctx.row_seq = (self._dev_view(n, T) for n in ("tokens", "positions", "row_seq"))
         ctx.seg_slot, ctx.seg_start, ctx.seg_ctx = (self._dev_view(n, S) for n in ("seg_slot", "seg_start", "seg_ctx"))
         ctx.cu_rows = self._dev_view("cu_rows", S + 1)
         ctx.logit_rows = self._dev_view("logit_rows", R)
-        ctx.host_seg_rows = [len(entries[ei].tokens) for ei in order] + [1] * (S - n_real_segs)
-        ctx.host_seg_ctx = [entries[ei].start + len(entries[ei].tokens) for ei in order] + [0] * (S - n_real_segs)
-        ctx.max_seg_rows, ctx.max_ctx = max(ctx.host_seg_rows), max(ctx.host_seg_ctx)
+        ctx.host_seg_rows, ctx.host_seg_ctx = list(info.seg_rows), list(info.seg_ctx)
+        ctx.max_seg_rows, ctx.max_ctx = info.max_seg_rows, info.max_ctx
         for g in range(self._n_groups):
             mb = pool.max_blocks(g)
             ctx.groups.append(GroupView(self._dev_view(f"block_table{g}", S * mb).view(S, mb),
                                         self._dev_view(f"slot_mapping{g}", T), mb))
         return ctx
-
-    def _table(self, slot: int, g: int, windowed: bool) -> np.ndarray:
-        """The request's block table as an int32 array.  Tables of groups without a window only grow, so a
-        copy is kept per (slot, group) and fetched again only when the request or its page count changed."""
-        mgr = self.pool.manager
-        if windowed:
-            return np.asarray(mgr.block_table(slot, g), dtype=np.int32)
-        rid, n = mgr.request_id(slot), mgr.table_len(slot, g)
-        have = self._table_cache.get((slot, g))
-        if have is None or have[0] != rid or have[1] != n:
-            have = (rid, n, np.asarray(mgr.block_table(slot, g), dtype=np.int32))
-            self._table_cache[(slot, g)] = have
-        return have[2]
 
     def _bucket(self, n: int) -> int:
         b = 1
@@ -298,26 +208,31 @@ class ModelRunner:
         A step of single tokens only (decoding) is captured once per batch-size bucket as a CUDA
         graph and replayed, so its few hundred launches cost one; any other step runs launch by
         launch."""
-        if self.use_graphs and all(len(e.tokens) == 1 for e in entries):
-            out = self._decode_step_graph(entries)
+        native = bool(entries) and not isinstance(entries[0], StepEntry)
+        decode_only = all((e.n_tokens if native else len(e.tokens)) == 1 for e in entries)
+        if self.use_graphs and decode_only:
+            out = self._decode_step_graph(entries, native)
             return out if borrow else out.clone()
         ctx = self.build_context(entries)
         return self.model.forward(ctx)
 
-    def _decode_step_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _decode_step_graph(self, entries, native: bool) -> torch.Tensor:
         rows = self._bucket(len(entries))
-        ctx = self.build_context(entries, pad_rows=rows, all_logits=True)
-        if rows not in self._graphs:
+        have = self._graphs.get(rows)
+        if have is None:
+            ctx = self.build_context(entries, pad_rows=rows, all_logits=True)
             self.model.forward(ctx)                       # warm-up outside the capture (writes the same cache values)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
-            self._graphs[rows] = (graph, logits)
-        graph, logits = self._graphs[rows]
+            have = self._graphs[rows] = (graph, logits)
+        else:
+            self._pack(entries, rows, True, False)        # the captured kernels read the same buffer: no views needed
+        graph, logits = have
         graph.replay()
         self.graph_replays += 1
-        want = [i for i, e in enumerate(entries) if len(e.want)]
+        want = [i for i, e in enumerate(entries) if (e.sample if native else len(e.want))]
         if len(want) == rows:
             return logits
         return logits[torch.tensor(want, dtype=torch.long, device=logits.device)] if want else logits[:0]
