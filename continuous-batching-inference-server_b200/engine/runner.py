@@ -105,7 +105,8 @@ class ModelRunner:
         self._copied = None    # event after the last host->device copy of the packed buffer
         # decode-only steps replay a captured CUDA graph unless a part reads device values on the host
         self.use_graphs = all(getattr(part, "capturable", True)
-                              for layer in model.layers for _, part in layer.parts())
+                              for layer in model.layers for _, part in layer.parts()) \
+            and getattr(model.position, "capturable", True) and getattr(model.final_norm, "capturable", True)
         self._graphs: Dict[int, tuple] = {}      # rows of a decode-only step -> (graph, context, logits)
         worst = heads = 0
         for layer in model.layers:

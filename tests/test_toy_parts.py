@@ -183,3 +183,106 @@ def test_toy_mixer_with_state_builds_and_steps(window):
         for t in o:
             assert t == int(plain_toy_forward(w, cfgd, seq)[-1].argmax())
             seq.append(t)
+
+
+def test_toy_feed_forward_with_routing_and_another_position_encoding():
+    """A feed-forward that routes every row to one of three small experts (router logits and choice in
+    32-bit) and a position encoding computed from the position instead of looked up, both defined here
+    and registered without touching the framework; the built-in attention runs between them."""
+    import math
+
+    import cbis_b200 as cb
+    import plain_gpt
+    from cbis_b200.config import LayerSpec, ModelSpec, PartSpec
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+    from cbis_b200.models import Model
+    from cbis_b200.parts import Delta, FeedForward, PositionEncoding, register_feed_forward, register_position
+    from cbis_b200.weights import InitScheme, TensorDecl, random_tensors
+
+    class RoutedExperts(FeedForward):
+        capturable = False          # nonzero() below makes the host wait for the device
+
+        def __init__(self, width, inner, n_experts):
+            self.width, self.inner, self.n = width, inner, n_experts
+
+        def tensors(self, prefix):
+            out = [TensorDecl(prefix + "router.weight", (self.width, self.n))]
+            for e in range(self.n):
+                out += [TensorDecl(f"{prefix}experts.{e}.up.weight", (self.width, self.inner)),
+                        TensorDecl(f"{prefix}experts.{e}.down.weight", (self.inner, self.width))]
+            return out
+
+        def load(self, prefix, tensors, dtype, device):
+            f = lambda name: tensors[prefix + name].to(device=device, dtype=torch.float32)
+            self.router = f("router.weight")
+            self.up = [f(f"experts.{e}.up.weight") for e in range(self.n)]
+            self.down = [f(f"experts.{e}.down.weight") for e in range(self.n)]
+
+        def forward(self, ctx, h):
+            h = h.float()
+            choice = (h @ self.router).argmax(-1)                   # routing decided on the device, per row
+            out = torch.zeros_like(h)
+            for e in range(self.n):
+                rows = (choice == e).nonzero().squeeze(-1)          # a step-local index tensor
+                if rows.numel():
+                    out.index_add_(0, rows, torch.relu(h[rows] @ self.up[e]) @ self.down[e])
+            return Delta(out)
+
+    class SinusoidalPositions(PositionEncoding):
+        def __init__(self, width, base):
+            self.width, self.base = width, base
+
+        def embed(self, ctx, token_table):
+            x = torch.empty((ctx.n_rows, self.width), dtype=torch.float32, device=token_table.device)
+            ops.embed_pos_add(ctx.tokens, ctx.positions, token_table, None, x, ctx.error_flag)   # token rows only
+            i = torch.arange(self.width // 2, device=x.device, dtype=torch.float32)
+            ang = ctx.positions.float()[:, None] * torch.exp(-math.log(self.base) * 2 * i / self.width)[None, :]
+            return x + torch.cat([ang.sin(), ang.cos()], 1)
+
+    register_feed_forward("routed_test", RoutedExperts)
+    register_position("sinusoidal_test", SinusoidalPositions)
+    W, V, P = 32, 29, 40
+    norm = PartSpec("layernorm", {"width": W, "eps": 1e-5})
+    att = PartSpec("attention", {"width": W, "n_head": 2, "n_kv_head": 2, "head_dim": 16, "scale": 0.25, "window": 0})
+    layers = (LayerSpec("h.0.", "pre_norm", att, PartSpec("routed_test", {"width": W, "inner": 20, "n_experts": 3}), norm, norm),
+              LayerSpec("h.1.", "pre_norm", att, PartSpec("dense", {"width": W, "inner": 48, "activation": "gelu_tanh"}), norm, norm))
+    spec = ModelSpec(W, V, P, "wte.weight", PartSpec("sinusoidal_test", {"width": W, "base": 50.0}), layers, (0, 1),
+                     norm, "ln_f.", None)
+    model = Model(spec)
+    tensors = random_tensors(model.declared(), 4, InitScheme(0.3, 0.1, 0.1, 0.1), torch.float32)
+    model.load(tensors, "float32", "cuda")
+    eng = cb.Engine(model, dtype="float32", page_size=4, num_pages=24, max_num_seqs=2, max_batched_tokens=64)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    def plain(tokens):
+        T = len(tokens)
+        i = torch.arange(W // 2, dtype=torch.float64)
+        ang = torch.arange(T, dtype=torch.float64)[:, None] * torch.exp(-math.log(50.0) * 2 * i / W)[None, :]
+        x = w["wte.weight"][tokens] + torch.cat([ang.sin(), ang.cos()], 1)
+        for li in (0, 1):
+            p = f"h.{li}."
+            ln = lambda x, q: plain_gpt.layer_norm(x, w[p + q + "weight"], w[p + q + "bias"], 1e-5)
+            x = x + plain_gpt.attention(ln(x, "ln_1."), w[p + "attn.c_attn.weight"], w[p + "attn.c_attn.bias"],
+                                        w[p + "attn.c_proj.weight"], w[p + "attn.c_proj.bias"], 2)
+            h = ln(x, "ln_2.")
+            if li == 0:
+                choice = (h @ w[p + "router.weight"]).argmax(-1)
+                f = torch.stack([torch.relu(h[t] @ w[f"{p}experts.{int(choice[t])}.up.weight"])
+                                 @ w[f"{p}experts.{int(choice[t])}.down.weight"] for t in range(T)])
+                assert len(set(choice.tolist())) > 1                # the rows really go to different experts
+            else:
+                f = plain_gpt.mlp(h, w[p + "mlp.c_fc.weight"], w[p + "mlp.c_fc.bias"], w[p + "mlp.c_proj.weight"],
+                                  w[p + "mlp.c_proj.bias"], "gelu_new")
+            x = x + f
+        return plain_gpt.layer_norm(x, w["ln_f.weight"], w["ln_f.bias"], 1e-5) @ w["wte.weight"].T
+
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(0, V, (37,), generator=g).tolist()
+    ref = plain(toks)
+    slot = eng.open_request(0)
+    got, pos = [], 0
+    for n in (9, 2, 1, 1, 13, 2, 1, 1, 1, 6):                       # portions and single tokens
+        got.append(eng.forward_step([StepEntry(slot, pos, toks[pos:pos + n], list(range(n)))]).double().cpu())
+        pos += n
+    assert pos == len(toks) and (torch.cat(got) - ref).abs().max() < 1e-4
