@@ -336,6 +336,25 @@ def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out
     _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
 
 
+def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
+                      n_head, n_kv_head, head_dim, page_size, scale, window=0):
+    """The same attention as ``paged_prefill_bf16`` on the tcgen05 tensor cores (TMA operands, S and P V in
+    tensor memory).  Head size 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering."""
+    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
+    if head_dim != 128:
+        raise KernelError(f"tcgen05 prefill attention: head_dim={head_dim} is not 128")
+    if page_size & (page_size - 1) or not 8 <= page_size <= 128:
+        raise KernelError(f"tcgen05 prefill attention: page_size={page_size} is not a power of two in 8..128")
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous() and k_cache.is_contiguous()
+    st = kernels().cbis_paged_prefill_tc5(
+        _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_rows), _ptr(seg_start), _ptr(out),
+        c_int(out.stride(0)), c_int(seg0), c_int(n_seg), c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head),
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), _ptr(tcgen05_error_flag(q.device)), _stream())
+    _check(st, "paged_prefill_tc5", f"segments={n_seg} heads={n_head}/{n_kv_head} page={page_size}")
+
+
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):
     """tokens <- sampled, positions/seg_start/seg_ctx += 1 for the first n rows (all on the device)."""
     st = kernels().cbis_decode_advance(_ptr(tokens), _ptr(positions), _ptr(seg_start), _ptr(seg_ctx), _ptr(sampled),

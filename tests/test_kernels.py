@@ -432,3 +432,27 @@ def test_gemm_tcgen05(ops, M, N, K, out_dtype):
     tol = 1e-5 * math.sqrt(K) if out_dtype == torch.float32 else 1e-2
     assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
     assert ops.tcgen05_error_flag("cuda").item() == 0            # no bounded wait ran out
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,ps,window", [(2, 2, 16, 0), (4, 2, 16, 0), (3, 1, 64, 0), (2, 2, 8, 0),
+                                                        (2, 2, 16, 100), (1, 1, 32, 37), (2, 1, 128, 0)])
+def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window):
+    """The TMA + tcgen05 form (head size 128): the same cases as the mma.sync form, in a cache whose unused
+    slots hold NaN (what an earlier owner of a page may have left must not reach another request)."""
+    hd = 128
+    seg_ctx, seg_rows = [200, 333, 64, 70, 1, 130, 600], [200, 77, 64, 3, 1, 65, 257]
+    c = paged_case(ops, torch.bfloat16, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed=ps + window)
+    S = len(seg_ctx)
+    cu = torch.tensor([0] + list(np.cumsum(seg_rows)), dtype=torch.int32)
+    start = torch.tensor([cx - n for cx, n in zip(seg_ctx, seg_rows)], dtype=torch.int32)
+    out = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_tc5(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out, 0, S, max(seg_rows),
+                          n_head, n_kv_head, hd, ps, c["scale"], window)
+    assert ops.tcgen05_error_flag("cuda").item() == 0
+    err = (out.double().cpu() - c["ref"]).abs().max().item()
+    assert err < 1.5e-2 * max(1.0, c["ref"].abs().max().item()), err
+    # agrees with the mma.sync form to rounding
+    out2 = torch.empty_like(out)
+    ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 0, S, max(seg_rows),
+                           n_head, n_kv_head, hd, ps, c["scale"], window)
+    assert (out.float() - out2.float()).abs().max().item() < 2e-2 * max(1.0, c["ref"].abs().max().item())
