@@ -3,8 +3,8 @@
 // A block takes 128 consecutive rows of one (segment, head).  Keys and values come in tiles of 128
 // keys, page by page through the block table, with TMA (cp.async.bulk.tensor, 128-byte swizzle, two
 // stages).  One thread issues the products: S = Q K^T (tcgen05.mma, 128x128x16, eight per tile) into
-// tensor memory, and P V into a second accumulator.  Four warps own one query row per thread: they
-// read S with tcgen05.ld (a whole row per thread, so the row maximum and sum need no shuffles), scale
+// tensor memory (double-buffered), and P V into another accumulator.  Eight warps share the query rows, two
+// threads per row: they read S with tcgen05.ld (half a row per thread: no shuffles for the maximum and sum), scale
 // and mask in 32-bit, keep the running maximum and sum, write P in bfloat16 into shared memory in the
 // swizzled layout the product reads, and add each tile's P V to the output they keep in registers,
 // rescaled in 32-bit.  V is used as it lies in the cache ([key][head dim], head dim contiguous): it is
@@ -29,7 +29,7 @@ constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int HALF_BYTES = 128 * 128;          // 128 rows of 128 bytes (64 bf16 of the head dim, or 64 keys of P)
 constexpr int TILE_BYTES = 2 * HALF_BYTES;     // a 128 x 128 bf16 tile as two swizzled halves
 constexpr int STAGES = 2;
-constexpr int THREADS = 192;                   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: softmax
+constexpr int THREADS = 320;                   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..9: softmax
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -119,7 +119,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   unsigned char* sP = sV + STAGES * TILE_BYTES;               // 2 halves (keys 0..63, 64..127)
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + TILE_BYTES);
   unsigned long long *q_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *p_ready = bars + 7,
-                     *pv_full = bars + 8;
+                     *pv_full = bars + 8, *pair_bar = bars + 10;   // pair_bar: one per quarter of the rows
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -149,8 +149,9 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     bar_init(&s_full[0], 1);
     bar_init(&s_full[1], 1);
-    bar_init(p_ready, 4);
+    bar_init(p_ready, 8);
     bar_init(pv_full, 1);
+    for (int q = 0; q < 4; ++q) bar_init(&pair_bar[q], 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -251,13 +252,19 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
     }
   } else {
-    const int quarter = warp & 3;
+    // Eight softmax warps: a warp reads the quarter of tensor memory given by its index % 4, so two warps share a
+    // quarter: two threads per query row.  Thread `half` takes keys [64*half, 64*half+64) of every tile for the
+    // scores and head dims [64*half, 64*half+64) of the output; the two exchange the row maximum through shared
+    // memory (an mbarrier per quarter, waited on with a limit like every other) and add their parts of the row
+    // sum at the end.
+    __shared__ float xmax[2][BM];
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;              // this thread's query row within the tile
     const int p = pos0 + r;                         // its position
     const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
-    float o[HD];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -265,15 +272,16 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!bar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(error, 15); ok = false; break; }
       if (*abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const unsigned s_addr = tmem_s + (j & 1) * 128 + lane_addr;
+      const unsigned s_addr = tmem_s + (j & 1) * 128 + lane_addr + half * 64;
       const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
-      // keys this row may see in this tile: [lo, hi)
+      // keys this row may see in this tile: [lo, hi), as columns of the tile; this thread's columns start at c_base
       const int hi = min(min(p + 1, kend) - j0, BN);
       const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
-      // pass 1: the row's maximum over this tile (of the raw scores: the scale is positive)
+      const int c_base = half * 64;
+      // pass 1: the maximum of this thread's 64 raw scores (the scale is positive), then of the row
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float v[32];
         tmem_ld32(s_addr + c0, v);
         if (!edge) {
@@ -282,17 +290,21 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c0 + i >= lo && c0 + i < hi) mx = fmaxf(mx, v[i]);
+            if (c_base + c0 + i >= lo && c_base + c0 + i < hi) mx = fmaxf(mx, v[i]);
         }
       }
-      mx *= scale_log2e;
+      xmax[half][r] = mx;
+      __syncwarp();
+      if (lane == 0) bar_arrive(&pair_bar[quarter]);
+      if (!bar_wait(&pair_bar[quarter], j & 1)) { atomicExch(error, 17); ok = false; break; }
+      mx = fmaxf(mx, xmax[half ^ 1][r]) * scale_log2e;
       const float m_new = fmaxf(m, mx);
       const float ref = m_new == -INFINITY ? 0.f : m_new;   // a row with no key in range yet
       const float corr = exp2f(m - ref);
       // pass 2: P = exp2(S * scale - max) in bfloat16 into shared memory (swizzled rows of 64 keys), and its sum
       float psum = 0.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float v[32];
         tmem_ld32(s_addr + c0, v);
         unsigned pk[16];
@@ -300,23 +312,23 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int i = 0; i < 32; i += 2) {
           float e0 = exp2f(fmaf(v[i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[i + 1], scale_log2e, -ref));
           if (edge) {
-            if (c0 + i < lo || c0 + i >= hi) e0 = 0.f;
-            if (c0 + i + 1 < lo || c0 + i + 1 >= hi) e1 = 0.f;
+            if (c_base + c0 + i < lo || c_base + c0 + i >= hi) e0 = 0.f;
+            if (c_base + c0 + i + 1 < lo || c_base + c0 + i + 1 >= hi) e1 = 0.f;
           }
           psum += e0 + e1;
           __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
           pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
         }
-        unsigned char* prow = sP + (c0 / 64) * HALF_BYTES + r * 128;
+        unsigned char* prow = sP + half * HALF_BYTES + r * 128;   // this thread's 64 keys are one swizzled row
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c0 % 64) / 8 + q4) ^ (r & 7);     // 16-byte piece within the 128-byte row, swizzled
+          const int chunk = (c0 / 8 + q4) ^ (r & 7);            // 16-byte piece within the 128-byte row, swizzled
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
         }
       }
       l = l * corr + psum;
       m = m_new;
-      if (j0 + BN > kend && j0 + r >= kend) {
+      if (j0 + BN > kend && half == 0 && j0 + r >= kend) {
         // the last tile: values of keys past the end are whatever the page held; P is zero there, but zero
         // times a NaN left by an earlier owner of the page would still be NaN: this thread clears key row r
         unsigned char* vrow = sV + (j % STAGES) * TILE_BYTES + r * 128;
@@ -333,18 +345,25 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!bar_wait(pv_full, j & 1)) { atomicExch(error, 16); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float v[32];
-        tmem_ld32(tmem_pv + lane_addr + c0, v);
+        tmem_ld32(tmem_pv + lane_addr + half * 64 + c0, v);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, v[i]);
       }
     }
+    // the two threads of a row add their parts of the row sum
+    if (ok) {
+      xmax[half][r] = l;
+      __syncwarp();
+      if (lane == 0) bar_arrive(&pair_bar[quarter]);
+      if (!bar_wait(&pair_bar[quarter], n_tiles & 1)) { atomicExch(error, 17); ok = false; }
+    }
     if (ok && r < rows_here) {
-      const float inv = 1.f / l;
-      __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD;
+      const float inv = 1.f / (l + xmax[half ^ 1][r]);
+      __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD + half * 64;
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
+      for (int i = 0; i < 64; i += 8) {
         uint4 q4;
         __nv_bfloat162 a = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
         __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), d = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);

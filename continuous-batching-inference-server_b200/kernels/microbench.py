@@ -53,6 +53,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--splits", type=int, default=0, help="0: the engine's own choice")
     ap.add_argument("--layers", type=int, default=24, help="distinct weight/cache buffers per timed call")
+    ap.add_argument("--act", default="gelu_erf", choices=["none", "gelu_erf", "gelu_tanh"], help="gemm_tc: the fused activation")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--reps", type=int, default=20)
     a = ap.parse_args()
@@ -83,7 +84,7 @@ def main():
 
         def fn():
             for w in W:
-                ops.gemm_tcgen05(x, w, bias, "gelu_erf", out)
+                ops.gemm_tcgen05(x, w, bias, a.act, out)
 
         def lib():
             for w in W:
@@ -91,7 +92,7 @@ def main():
         fl = 2.0 * M * a.n * a.k
         t = timed(fn, not a.no_graph, a.reps) / len(W)
         tl = timed(lib, not a.no_graph, a.reps) / len(W)
-        print(f"gemm_tc M={M} N={a.n} K={a.k}: tcgen05 with bias+GELU {t:.1f} us ({fl / t / 1e6:.0f} TFLOP/s)  "
+        print(f"gemm_tc M={M} N={a.n} K={a.k}: tcgen05 with bias+{a.act} {t:.1f} us ({fl / t / 1e6:.0f} TFLOP/s)  "
               f"library, no epilogue {tl:.1f} us ({fl / tl / 1e6:.0f} TFLOP/s)  error flag {ops.tcgen05_error_flag(dev).item()}")
     elif a.op == "layernorm":
         x = torch.randn(M, a.k, device=dev)

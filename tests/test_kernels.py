@@ -418,10 +418,12 @@ def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal(ops):
     assert (out.double().cpu() - p @ v.double()).abs().max() < 2e-2
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 136), (1000, 512, 2048), (77, 5001, 96), (2048, 768, 320)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 136), (1000, 512, 2048), (77, 5001, 96), (2048, 768, 320),
+                                   (257, 520, 72), (2304, 8200, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tcgen05(ops, M, N, K, out_dtype):
-    """The TMA + tcgen05 product with its fused epilogue: sizes that are no multiple of its 128x256x64 tiles."""
+    """The TMA + tcgen05 product with its fused epilogue: sizes that are no multiple of its tiles (128x256x64 on
+    one block up to 128 rows, 256x256x64 on pairs of blocks above), one of them with several tiles per block."""
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
