@@ -1,0 +1,534 @@
+// Prefill attention over the paged cache on the 5th-generation tensor cores (bfloat16, head size 128).
+//
+// A block takes 128 consecutive rows of one (segment, head); Q comes with TMA (cp.async.bulk.tensor, 128-byte
+// swizzle).  Keys and values come in tiles of 64 keys, gathered through the block table by one warp with
+// 16-byte cp.async copies that write the same swizzled layout (two stages each; keys past the end or before
+// the window are written as zeros).  With pages of 16 keys a tile would be sixteen TMA copies of 2 KB, and one
+// thread issues those at about 70 ns apiece: more than the tile's whole share of the time.
+// One thread issues the products: S = Q K^T (tcgen05.mma, 128x64x16, eight per tile) into tensor memory
+// (two buffers, so the scores of the next tile are computed while the softmax of this one runs), and
+// O += P V (128x128x16, four per tile) into an accumulator that STAYS in tensor memory for the whole row
+// tile.  Eight warps share the query rows, two threads per row: each reads its half of the row's scores
+// with one tcgen05.ld, masks and takes the maximum in 32-bit; the two exchange their maxima, compute
+// P = exp2(S * scale - m) in 32-bit, write it in bfloat16 into shared memory in the swizzled layout the
+// product reads, and keep the running sum.  The reference value m only has to be shared by a row's
+// numbers, not to be their exact maximum: it is raised, and O in tensor memory and the sum rescaled (in
+// 32-bit), only when a tile's maximum exceeds it by more than 2^8, which after the first tiles is rare;
+// the quotient O / sum at the end is the same.  V is used as it lies in the cache ([key][head dim],
+// head dim contiguous): it is the MN-major B operand of P V.
+//
+// Shared memory (113 KB) and tensor memory (256 of 512 columns) are sized for TWO blocks per SM: while
+// one block's softmax warps work, the other's products run.
+//
+// Every wait on an mbarrier is bounded; when a limit runs out the block sets *error, stops, frees its
+// tensor memory and returns (its output rows are then invalid, and the host raises).
+#include "common.cuh"
+
+#include <cuda.h>
+#include <math.h>
+#include <mutex>
+
+namespace cbis {
+namespace tc5 {
+__device__ unsigned long long g_tl[1024];
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TL(i) do { if (blockIdx.x == 0 && (i) < 1024) g_tl[(i)] = gtime(); } while (0)
+
+constexpr int BM = 128, BN = 64, HD = 128;
+constexpr int Q_HALF_BYTES = BM * 128;         // 128 rows of 128 bytes: 64 of the 128 head dims
+constexpr int Q_BYTES = 2 * Q_HALF_BYTES;
+constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 of the 128 head dims
+constexpr int KV_BYTES = 2 * KV_HALF_BYTES;    // a tile of keys, or of values
+constexpr int P_BYTES = BM * 128;              // 128 rows of 64 keys
+constexpr int STAGES = 2;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 512 + 160;   // + maxima exchange + barriers
+constexpr float RAISE_BY = 8.f;                // the reference is raised when a tile's maximum exceeds it by 2^8
+constexpr int THREADS = 320;                   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..9: softmax
+constexpr unsigned SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(bar)), "r"(count));
+}
+__device__ __forceinline__ void bar_expect(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(void* bar, unsigned parity) {
+  const unsigned a = s32(bar);
+  for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_2d(void* smem, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(s32(smem)), "l"(map), "r"(x), "r"(y), "r"(s32(bar)) : "memory");
+}
+// K-major operand: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long desc_kmajor(const void* smem) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((s32(smem) & 0x3FFFF) >> 4);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+// MN-major operand (V as B of P*V: N = head dim contiguous, K = keys): atoms of 8 keys x 64 head dims (1024 bytes);
+// the next atom along N (the other half of the head dim) lies `mn_stride` bytes further, the next 8 keys 1024 bytes.
+__device__ __forceinline__ unsigned long long desc_mnmajor(const void* smem, unsigned mn_stride, unsigned k_stride) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((s32(smem) & 0x3FFFF) >> 4);
+  d |= (unsigned long long)((mn_stride >> 4) & 0x3FFF) << 16;
+  d |= (unsigned long long)((k_stride >> 4) & 0x3FFF) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+// D = F32, A = B = BF16, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr unsigned idesc(bool b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned id,
+                                    unsigned accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.u32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(id), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// grid: row tiles of the longest segment x heads x segments from seg0 on, in one dimension
+__global__ void __launch_bounds__(THREADS, 2)
+paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
+                         const int* block_table, int max_blocks,
+                         const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_seg,
+                         int n_head, int n_kv_head, int ps, float scale_log2e, int window, int* error) {
+  extern __shared__ __align__(1024) unsigned char base[];   // no byte to spare for rounding the address up: checked below
+  unsigned char* sQ = base;                                   // 2 halves of the head dim
+  unsigned char* sK = sQ + Q_BYTES;                           // STAGES tiles
+  unsigned char* sV = sK + STAGES * KV_BYTES;                 // STAGES tiles
+  unsigned char* sP = sV + STAGES * KV_BYTES;                 // 128 rows of 64 keys
+  __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(sP + P_BYTES);   // [2][BM]: a row's two maxima, rounded up
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES + 512);
+  // keys and values have barriers of their own: a stage of keys is free as soon as Q K^T has read it, long before
+  // the values of the same tile are, so the keys of tile j+2 are on their way while tile j is still being worked on
+  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
+                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12, *pair_bar = bars + 13;   // pair_bar: one per quarter of the rows
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // late row tiles have the most keys to walk: blocks are numbered so that those of ALL heads and segments come
+  // first, and an SM's second block is a light one
+  const int per_rank = n_head * n_seg, n_row_tiles = gridDim.x / per_rank;
+  const int tile = n_row_tiles - 1 - (int)blockIdx.x / per_rank, seg = seg0 + ((int)blockIdx.x % per_rank) / n_head,
+            h = (int)blockIdx.x % n_head;
+  pdl_trigger();
+  const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
+  if (tile * BM >= n_rows) return;
+  if (s32(base) & 1023) {   // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(error, 18);
+    return;
+  }
+  const int hk = h / (n_head / n_kv_head);
+  const int pos0 = seg_start[seg] + tile * BM;
+  const int rows_here = min(BM, n_rows - tile * BM);
+  const int kend = pos0 + rows_here;
+  const int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kt_first = kbegin / BN, kt_last = (kend - 1) / BN, n_tiles = kt_last - kt_first + 1;
+  const int* bt = block_table + (size_t)seg * max_blocks;
+
+  if (threadIdx.x == 0) {
+    bar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      bar_init(&k_full[s], 32);    // every lane of the copying warp arrives when its copies have landed
+      bar_init(&k_empty[s], 1);
+      bar_init(&v_full[s], 32);
+      bar_init(&v_empty[s], 1);
+    }
+    bar_init(&s_full[0], 1);
+    bar_init(&s_full[1], 1);
+    bar_init(p_ready, 8);
+    bar_init(pv_done, 1);
+    for (int q = 0; q < 4; ++q) bar_init(&pair_bar[q], 2);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {  // half of tensor memory: S twice (64 columns each) and O (128 columns)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+  pdl_wait();  // q and this step's keys/values come from the kernels before
+  if (threadIdx.x == 0) TL(0);
+
+  if (warp == 0) {
+    // The whole warp copies: a lane owns one 16-byte piece of the 256-byte rows (of two keys per step); lane i also
+    // looks up the page of the tile's i-th run of keys (a page, or 64 keys of a larger page) in the block table.
+    if (lane == 0) {
+      bar_expect(q_full, Q_BYTES);
+      const int qrow = r_begin + tile * BM;
+      tma_2d(sQ, &map_q, h * HD, qrow, q_full);
+      tma_2d(sQ + Q_HALF_BYTES, &map_q, h * HD + 64, qrow, q_full);
+    }
+    const int piece = min(ps, BN), pieces_per_tile = BN / piece;
+    const int piece_shift = 31 - __clz(piece);
+    const int ch = lane & 15, sub = lane >> 4;
+    const unsigned dst_col = (unsigned)(ch >> 3) * KV_HALF_BYTES;   // which half of the head dim
+    unsigned dst_u[4];   // key 2u + sub of a group of eight: its row, and the lane's piece of it after the swizzle
+#pragma unroll
+    for (int u = 0; u < 4; ++u) dst_u[u] = (unsigned)(2 * u + sub) * 128 + ((unsigned)((ch & 7) ^ (2 * u + sub)) << 4);
+    // copies tile j's keys (kv = 0) or values (kv = 1) into their stage; false when the block has given up
+    auto load = [&](int j, int kv, int page) -> bool {
+      const int s = j % STAGES, kt = kt_first + j;
+      int stop = 0;
+      if (lane == 0) {
+        if (j >= STAGES && !bar_wait(kv ? &v_empty[s] : &k_empty[s], ((j / STAGES) - 1) & 1)) {
+          *abort_flag = 1;
+          atomicExch(error, 11);
+        }
+        stop = *abort_flag;
+      }
+      stop = __shfl_sync(0xffffffffu, stop, 0);
+      if (stop) return false;
+      // Eight groups of eight keys; in a group this lane copies four pieces, of keys 2u + sub (u = 0..3).  Only
+      // the group's addresses change from group to group: what depends on u is kept in dst_u[] and in constants.
+      const char* src_base = reinterpret_cast<const char*>(kv ? vc : kc) + ch * 16 + sub * (HD * 2);
+      const unsigned dst0 = s32((kv ? sV : sK) + s * KV_BYTES) + dst_col;
+      const int t0 = kt * BN;
+      const bool whole = t0 >= kbegin && t0 + BN <= kend;   // no key of the tile is past the end or before the window
+      const char* src = src_base;
+#pragma unroll
+      for (int g = 0; g < BN / 8; ++g) {
+        if (((g * 8) & (piece - 1)) == 0) {   // a new run: its page
+          const int pg = __shfl_sync(0xffffffffu, page, (g * 8) >> piece_shift);
+          src = src_base + (((long long)pg * n_kv_head + hk) * ps + ((t0 + g * 8) & (ps - 1))) * (HD * 2);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          unsigned n_src = 16u;
+          if (!whole) {
+            // keys past the end, and keys before the window (their pages may have been given back), are not read:
+            // their rows are written as zeros, so that P = 0 there never meets a NaN left by a page's earlier owner
+            const int jk = t0 + g * 8 + 2 * u + sub;
+            n_src = (jk < kend && jk >= kbegin) ? 16u : 0u;
+          }
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                       ::"r"(dst0 + g * 1024 + dst_u[u]), "l"(src + u * (2 * HD * 2)), "r"(n_src) : "memory");
+        }
+        src += 8 * HD * 2;
+      }
+      // this lane's arrival is made when its copies so far have landed
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s32(kv ? &v_full[s] : &k_full[s])) : "memory");
+      return true;
+    };
+    // The page of this lane's run is looked up a tile before it is used: the block table is in global memory, and
+    // a lookup inside load() would put its latency between every two tiles.
+    auto page_of = [&](int j) -> int {
+      const int j0 = (kt_first + j) * BN + lane * piece;
+      return (j < n_tiles && lane < pieces_per_tile && j0 < kend && j0 + piece > kbegin) ? __ldg(bt + j0 / ps) : 0;
+    };
+    // The keys run a tile ahead of the values: a stage of keys is free two tiles before the stage of values of the
+    // same tile is, and waiting for the values' stage first would hold the keys back.
+    int page_before = 0, page_now = page_of(0);
+    for (int t = 0; t <= n_tiles; ++t) {
+      const int page_next = page_of(t + 1);
+      if (t < n_tiles && !load(t, 0, page_now)) break;
+      if (t > 0 && !load(t - 1, 1, page_before)) break;
+      page_before = page_now;
+      page_now = page_next;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");   // nothing of this warp's is in flight when the block ends
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // The descriptors are built once: the one thread that issues the products has nothing to overlap their
+      // arithmetic with.  An operand further on in shared memory is the same descriptor plus its offset in 16-byte
+      // units (the address field holds shared-memory addresses with room to spare).
+      const unsigned long long dq = desc_kmajor(sQ), dk = desc_kmajor(sK), dp = desc_kmajor(sP),
+                               dv = desc_mnmajor(sV, KV_HALF_BYTES, 1024);
+      bool ok = bar_wait(q_full, 0);
+      if (!ok) { *abort_flag = 2; atomicExch(error, 12); }
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % STAGES;
+        if (!bar_wait(&k_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); return false; }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the copies were ordinary writes; the products read through the async proxy
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (j < 100) TL(512 + j * 4 + 2);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {   // eight steps of 16 along the head dim, four in each 64-wide half
+          mma(tmem_s + (j & 1) * BN, dq + (unsigned)(((kk / 4) * Q_HALF_BYTES + (kk % 4) * 32) >> 4),
+              dk + (unsigned)((s * KV_BYTES + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32) >> 4), idesc(false, BN), kk > 0 ? 1u : 0u);
+        }
+        if (j < 100) TL(512 + j * 4 + 3);
+        commit(&k_empty[s]);   // the keys' stage is free again when these products have read it
+        commit(&s_full[j & 1]);
+        return true;
+      };
+      // Q K^T runs two tiles ahead (S has two buffers), so P V of a tile is issued the moment its P is there
+      if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
+      for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
+        const int s = j % STAGES;
+        TL(16 + j * 8 + 4);
+        if (!bar_wait(p_ready, j & 1)) { *abort_flag = 4; atomicExch(error, 14); break; }
+        TL(16 + j * 8 + 5);
+        if (!bar_wait(&v_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); break; }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TL(512 + j * 4 + 0);
+        // O += P V: four steps of 16 keys; V is MN-major: 16 keys are two 1024-byte atoms, the other half of the
+        // head dim KV_HALF_BYTES on
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          mma(tmem_o, dp + (unsigned)((kk * 32) >> 4), dv + (unsigned)((s * KV_BYTES + kk * 2048) >> 4), idesc(true, HD),
+              (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        TL(512 + j * 4 + 1);
+        commit(&v_empty[s]);   // the values' stage is free again when these products have read it
+        commit(pv_done);
+        TL(16 + j * 8 + 6);
+        // the scores of tile j+2 go where those of tile j were: the softmax has read them (it said so with p_ready)
+        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
+      }
+    }
+  } else {
+    // Eight softmax warps: a warp reads the quarter of tensor memory given by its index % 4, so two warps share a
+    // quarter: two threads per query row.  Thread `half` takes keys [32*half, 32*half+32) of every tile and, for
+    // rescaling and the result, head dims [64*half, 64*half+64).
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;              // this thread's query row within the tile
+    const int p = pos0 + r;                         // its position
+    const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+    const int c_base = half * 32;
+    float m = -INFINITY, l = 0.f;                   // the row's reference (log2 units) and the sum of its P
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int j0 = (kt_first + j) * BN;
+      if (!bar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(error, 15); ok = false; break; }
+      if (warp == 2 && lane == 0) TL(16 + j * 8 + 0);
+      if (*abort_flag) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float v[32];
+      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr + c_base, v);
+      const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
+      if (edge) {
+        // keys this row may see in this tile: [lo, hi), as columns of the tile
+        const int hi = min(min(p + 1, kend) - j0, BN);
+        const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c_base + i < lo || c_base + i >= hi) v[i] = -INFINITY;
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+      // the other thread of the row has read the maxima of the tile before (it arrived on p_ready after that)
+      if (j > 0 && !bar_wait(p_ready, (j - 1) & 1)) { atomicExch(error, 19); ok = false; break; }
+      xmax[half * BM + r] = __float2bfloat16_ru(mx);   // rounded UP: both threads derive the same reference from the pair
+      __syncwarp();
+      if (lane == 0) bar_arrive(&pair_bar[quarter]);
+      if (!bar_wait(&pair_bar[quarter], j & 1)) { atomicExch(error, 17); ok = false; break; }
+      if (warp == 2 && lane == 0) TL(16 + j * 8 + 1);
+      const float m_tile = fmaxf(__bfloat162float(xmax[r]), __bfloat162float(xmax[BM + r])) * scale_log2e;
+      // the products of the tile before have read P and written O
+      if (j > 0 && !bar_wait(pv_done, (j - 1) & 1)) { atomicExch(error, 16); ok = false; break; }
+      if (warp == 2 && lane == 0) TL(16 + j * 8 + 2);
+      const bool raise = m_tile > m + RAISE_BY || m == -INFINITY;
+      if (j > 0 && __any_sync(0xffffffffu, raise && m_tile > m)) {
+        // rescale this thread's half of the row of O in tensor memory; rows that keep their reference multiply by 1
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float f = (raise && m_tile > m) ? exp2f(m - m_tile) : 1.f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32(tmem_o + lane_addr + half * 64 + c0, o);
+        }
+        l *= f;
+      }
+      if (raise && m_tile > m) m = m_tile;
+      const float ref = m == -INFINITY ? 0.f : m;   // a row with no key in range yet: every P is exp2(-inf) = 0
+      // P = exp2(S * scale - m) in bfloat16 into shared memory (rows of 64 keys, 128-byte swizzle), and its sum
+      float psum = 0.f;
+      unsigned char* prow = sP + r * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        unsigned pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float e0 = exp2f(fmaf(v[q4 * 8 + 2 * i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[q4 * 8 + 2 * i + 1], scale_log2e, -ref));
+          psum += e0 + e1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+          pk[i] = *reinterpret_cast<unsigned*>(&b2);
+        }
+        const int chunk = (half * 4 + q4) ^ (r & 7);            // 16-byte piece within the 128-byte row, swizzled
+        *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l += psum;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P must be visible to the tensor cores' reads
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive(p_ready);
+      if (warp == 2 && lane == 0) TL(16 + j * 8 + 3);
+    }
+    if (ok && !bar_wait(pv_done, (n_tiles - 1) & 1)) { atomicExch(error, 16); ok = false; }
+    if (ok) {
+      // the two threads of a row add their parts of the row sum (P's buffer is free now)
+      float* xsum = reinterpret_cast<float*>(sP);
+      xsum[half * BM + r] = l;
+      __syncwarp();
+      if (lane == 0) bar_arrive(&pair_bar[quarter]);
+      if (!bar_wait(&pair_bar[quarter], n_tiles & 1)) { atomicExch(error, 17); ok = false; }
+      if (ok) l += xsum[(half ^ 1) * BM + r];
+    }
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.f / l;
+      __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD + half * 64;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
+        if (r < rows_here) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 q4;
+            __nv_bfloat162 a = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), d = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            q4.x = *reinterpret_cast<unsigned*>(&a);
+            q4.y = *reinterpret_cast<unsigned*>(&b);
+            q4.z = *reinterpret_cast<unsigned*>(&c);
+            q4.w = *reinterpret_cast<unsigned*>(&d);
+            *reinterpret_cast<uint4*>(dst + c0 + i) = q4;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(256) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+// [rows, cols] bfloat16 with row pitch ld elements; boxes of 64 columns x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encoder();
+  if (!fn) return CBIS_ERR_BAD_SIZE;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? CBIS_OK : CBIS_ERR_BAD_SIZE;
+}
+
+}  // namespace tc5
+}  // namespace cbis
+
+using namespace cbis;
+
+// q: [total_rows, q_ld] bfloat16 with head h in columns h*128..; kc/vc: [num_pages, n_kv_head, ps, 128].
+// Takes head size 128 and page sizes 8, 16, 32, 64, 128; refuses anything else.
+CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, const void* kc, const void* vc,
+                                       int num_pages, const int* block_table, int max_blocks, const int* cu_rows,
+                                       const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
+                                       int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
+                                       int window, int* error, void* stream) {
+  if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
+  if (hd != 128 || ps < 8 || ps > 128 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
+    return CBIS_ERR_BAD_SIZE;
+  if (q_ld % 8 || out_ld % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
+      ((uintptr_t)out & 15) || error == nullptr)
+    return CBIS_ERR_ALIGNMENT;
+  CUtensorMap map_q;
+  int st = tc5::make_map(&map_q, q, total_rows, n_head * hd, q_ld, tc5::BM);
+  if (st != CBIS_OK) return st;
+  const size_t smem = tc5::SMEM_BYTES;
+  auto kern = tc5::paged_prefill_tc5_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg);
+  e = launch_pdl(kern, grid, dim3(tc5::THREADS), smem, (cudaStream_t)stream, map_q, (const __nv_bfloat16*)kc,
+                 (const __nv_bfloat16*)vc, block_table, max_blocks,
+                 cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, n_seg, n_head, n_kv_head, ps,
+                 scale * 1.4426950408889634f, window, error);
+  return (int)e;
+}
+
+// How many blocks of the kernel above an SM holds at a time (it is sized for two); negative: a CUDA error.
+CBIS_EXPORT int cbis_paged_prefill_tc5_blocks_per_sm() {
+  auto kern = tc5::paged_prefill_tc5_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc5::SMEM_BYTES);
+  if (e != cudaSuccess) return -(int)e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return -(int)e;
+  int n = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tc5::THREADS, tc5::SMEM_BYTES);
+  return e == cudaSuccess ? n : -(int)e;
+}
+
+CBIS_EXPORT int cbis_tl_read(unsigned long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, cbis::tc5::g_tl, sizeof(unsigned long long) * 1024);
+}

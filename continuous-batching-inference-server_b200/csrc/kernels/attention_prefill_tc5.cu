@@ -1,18 +1,26 @@
 // Prefill attention over the paged cache on the 5th-generation tensor cores (bfloat16, head size 128).
 //
-// A block takes 128 consecutive rows of one (segment, head).  Keys and values come in tiles of 128
-// keys, page by page through the block table, with TMA (cp.async.bulk.tensor, 128-byte swizzle, two
-// stages).  One thread issues the products: S = Q K^T (tcgen05.mma, 128x128x16, eight per tile) into
-// tensor memory (double-buffered), and P V into another accumulator.  Eight warps share the query rows, two
-// threads per row: they read S with tcgen05.ld (half a row per thread: no shuffles for the maximum and sum), scale
-// and mask in 32-bit, keep the running maximum and sum, write P in bfloat16 into shared memory in the
-// swizzled layout the product reads, and add each tile's P V to the output they keep in registers,
-// rescaled in 32-bit.  V is used as it lies in the cache ([key][head dim], head dim contiguous): it is
-// the MN-major B operand of P V.
+// A block takes 128 consecutive rows of one (segment, head).  Keys and values come in tiles of 64 keys,
+// page by page through the block table, with TMA (cp.async.bulk.tensor, 128-byte swizzle): one warp brings
+// the keys and another the values, each with two stages and barriers of its own, because a stage of keys
+// is free long before the stage of values of the same tile is, and because a thread issues a TMA copy
+// in about 60 ns: the sixteen copies of a tile of 16-key pages would take one warp the tile's whole time.
+// (Gathering them with 16-byte cp.async copies from one warp was tried and is slower: a warp cannot keep
+// enough of those in flight.)
+// One thread issues the products: S = Q K^T (tcgen05.mma, 128x64x16, eight per tile) into tensor memory
+// (two buffers, so the scores of the next tile are computed while the softmax of this one runs), and
+// O += P V (128x128x16, four per tile) into an accumulator that STAYS in tensor memory for the whole row
+// tile.  Eight warps share the query rows, two threads per row: each reads its half of the row's scores
+// with one tcgen05.ld, masks and takes the maximum in 32-bit; the two exchange their maxima, compute
+// P = exp2(S * scale - m) in 32-bit, write it in bfloat16 into shared memory in the swizzled layout the
+// product reads, and keep the running sum.  The reference value m only has to be shared by a row's
+// numbers, not to be their exact maximum: it is raised, and O in tensor memory and the sum rescaled (in
+// 32-bit), only when a tile's maximum exceeds it by more than 2^8, which after the first tiles is rare;
+// the quotient O / sum at the end is the same.  V is used as it lies in the cache ([key][head dim],
+// head dim contiguous): it is the MN-major B operand of P V.
 //
-// The mma.sync kernel in attention_prefill.cu spends 1,044 instructions per warp and 64 keys with the
-// tensor pipe idle three quarters of the time; here the products run asynchronously at the tensor
-// cores' own rate and a thread spends about 600 instructions per 128 keys.
+// Shared memory (113 KB) and tensor memory (256 of 512 columns) are sized for TWO blocks per SM: while
+// one block's softmax warps work, the other's products run.
 //
 // Every wait on an mbarrier is bounded; when a limit runs out the block sets *error, stops, frees its
 // tensor memory and returns (its output rows are then invalid, and the host raises).
@@ -25,11 +33,16 @@
 namespace cbis {
 namespace tc5 {
 
-constexpr int BM = 128, BN = 128, HD = 128;
-constexpr int HALF_BYTES = 128 * 128;          // 128 rows of 128 bytes (64 bf16 of the head dim, or 64 keys of P)
-constexpr int TILE_BYTES = 2 * HALF_BYTES;     // a 128 x 128 bf16 tile as two swizzled halves
+constexpr int BM = 128, BN = 64, HD = 128;
+constexpr int Q_HALF_BYTES = BM * 128;         // 128 rows of 128 bytes: 64 of the 128 head dims
+constexpr int Q_BYTES = 2 * Q_HALF_BYTES;
+constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 of the 128 head dims
+constexpr int KV_BYTES = 2 * KV_HALF_BYTES;    // a tile of keys, or of values
+constexpr int P_BYTES = BM * 128;              // 128 rows of 64 keys
 constexpr int STAGES = 2;
-constexpr int THREADS = 320;                   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..9: softmax
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 512 + 160;   // + maxima exchange + barriers
+constexpr float RAISE_BY = 8.f;                // the reference is raised when a tile's maximum exceeds it by 2^8
+constexpr int THREADS = 352;                   // warp 0: Q and keys, warp 1: MMA + tensor memory, warps 2..9: softmax, warp 10: values
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -77,9 +90,9 @@ __device__ __forceinline__ unsigned long long desc_mnmajor(const void* smem, uns
   d |= (unsigned long long)2 << 61;
   return d;
 }
-// D = F32, A = B = BF16, M = 128, N = 128; b_mn: B is MN-major.
-__host__ __device__ constexpr unsigned idesc(bool b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(BN >> 3) << 17) |
+// D = F32, A = B = BF16, M = 128, N = n; b_mn: B is MN-major.
+__host__ __device__ constexpr unsigned idesc(bool b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) |
          ((unsigned)(BM >> 4) << 24);
 }
 __device__ __forceinline__ void mma(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned id,
@@ -104,280 +117,317 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
-// grid: (row tiles of the longest segment, heads, segments from seg0 on)
-__global__ void __launch_bounds__(THREADS, 1)
+// grid: row tiles of the longest segment x heads x segments from seg0 on, in one dimension
+__global__ void __launch_bounds__(THREADS, 2)
 paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const int* block_table, int max_blocks,
-                         const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_head,
-                         int n_kv_head, int ps, float scale_log2e, int window, int* error) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* sQ = base;                                   // 2 halves
-  unsigned char* sK = sQ + TILE_BYTES;                        // STAGES tiles
-  unsigned char* sV = sK + STAGES * TILE_BYTES;               // STAGES tiles
-  unsigned char* sP = sV + STAGES * TILE_BYTES;               // 2 halves (keys 0..63, 64..127)
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + TILE_BYTES);
-  unsigned long long *q_full = bars, *kv_full = bars + 1, *kv_empty = bars + 3, *s_full = bars + 5, *p_ready = bars + 7,
-                     *pv_full = bars + 8, *pair_bar = bars + 10;   // pair_bar: one per quarter of the rows
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 9);
+                         const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_seg,
+                         int n_head, int n_kv_head, int ps, float scale_log2e, int window, int* error) {
+  extern __shared__ __align__(1024) unsigned char base[];   // no byte to spare for rounding the address up: checked below
+  unsigned char* sQ = base;                                   // 2 halves of the head dim
+  unsigned char* sK = sQ + Q_BYTES;                           // STAGES tiles
+  unsigned char* sV = sK + STAGES * KV_BYTES;                 // STAGES tiles
+  unsigned char* sP = sV + STAGES * KV_BYTES;                 // 128 rows of 64 keys
+  __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(sP + P_BYTES);   // [2][BM]: a row's two maxima, rounded up
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES + 512);
+  // keys and values have barriers of their own: a stage of keys is free as soon as Q K^T has read it, long before
+  // the values of the same tile are, so the keys of tile j+2 are on their way while tile j is still being worked on
+  unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
+                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12, *pair_bar = bars + 13;   // pair_bar: one per quarter of the rows
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // late row tiles have the most keys to walk: they are given out first
-  const int seg = seg0 + blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  // late row tiles have the most keys to walk: blocks are numbered so that those of ALL heads and segments come
+  // first, and an SM's second block is a light one
+  const int per_rank = n_head * n_seg, n_row_tiles = gridDim.x / per_rank;
+  const int tile = n_row_tiles - 1 - (int)blockIdx.x / per_rank, seg = seg0 + ((int)blockIdx.x % per_rank) / n_head,
+            h = (int)blockIdx.x % n_head;
   pdl_trigger();
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * BM >= n_rows) return;
+  if (s32(base) & 1023) {   // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicExch(error, 18);
+    return;
+  }
   const int hk = h / (n_head / n_kv_head);
   const int pos0 = seg_start[seg] + tile * BM;
   const int rows_here = min(BM, n_rows - tile * BM);
   const int kend = pos0 + rows_here;
   const int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int live_from = (kbegin / ps) * ps;
   const int kt_first = kbegin / BN, kt_last = (kend - 1) / BN, n_tiles = kt_last - kt_first + 1;
   const int* bt = block_table + (size_t)seg * max_blocks;
 
   // keys and values of rows that no copy will fill must be finite: P is zero there, and 0 * NaN is NaN
-  for (int i = threadIdx.x; i < 2 * STAGES * TILE_BYTES / 16; i += THREADS)
+  for (int i = threadIdx.x; i < 2 * STAGES * KV_BYTES / 16; i += THREADS)
     reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
+
   if (threadIdx.x == 0) {
     bar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
-      bar_init(&kv_full[s], 1);
-      bar_init(&kv_empty[s], 1);
+      bar_init(&k_full[s], 1);
+      bar_init(&k_empty[s], 1);
+      bar_init(&v_full[s], 1);
+      bar_init(&v_empty[s], 1);
     }
     bar_init(&s_full[0], 1);
     bar_init(&s_full[1], 1);
     bar_init(p_ready, 8);
-    bar_init(pv_full, 1);
+    bar_init(pv_done, 1);
     for (int q = 0; q < 4; ++q) bar_init(&pair_bar[q], 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  if (warp == 1) {  // three accumulators of 128 columns (S twice, P V) in an allocation of 512
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(512) : "memory");
+  if (warp == 1) {  // half of tensor memory: S twice (64 columns each) and O (128 columns)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(256) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const unsigned tmem_s = *tmem_slot, tmem_pv = tmem_s + 256;
+  const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
   pdl_wait();  // q and this step's keys/values come from the kernels before
 
-  if (warp == 0) {
-    // The whole warp produces: lane i looks up page i of the tile in the block table (one coalesced load instead of
-    // a chain of dependent ones) and issues the four copies of that page; lane 0 posts the expected bytes first.
-    if (lane == 0) {
-      bar_expect(q_full, TILE_BYTES);
+  if (warp == 0 || warp == 10) {
+    // Warp 0 brings Q and the keys, warp 10 the values, each as far ahead as its two stages allow (one thread issues
+    // a TMA copy in about 60 ns, and a tile of 16-key pages is eight copies of keys and eight of values).
+    // The whole warp produces: lane i looks up run i of the tile (a page, or 64 keys of a larger page) in the block
+    // table and issues its two copies; lane 0 posts the expected bytes first.
+    if (warp == 0 && lane == 0) {
+      bar_expect(q_full, Q_BYTES);
       const int qrow = r_begin + tile * BM;
       tma_2d(sQ, &map_q, h * HD, qrow, q_full);
-      tma_2d(sQ + HALF_BYTES, &map_q, h * HD + 64, qrow, q_full);
+      tma_2d(sQ + Q_HALF_BYTES, &map_q, h * HD + 64, qrow, q_full);
     }
-    const int pages_per_tile = BN / ps;
-    for (int j = 0; j < n_tiles; ++j) {
+    const int piece = min(ps, BN), pieces_per_tile = BN / piece, piece_shift = 31 - __clz(piece);
+    // copies tile j's keys (kv = 0) or values (kv = 1) into their stage; false when the block has given up
+    auto load = [&](int j, int kv, int page) -> bool {
       const int s = j % STAGES, kt = kt_first + j;
+      // runs of the tile with a key in [kbegin, kend): from the one holding the first such key to the one holding the last
+      const int n_valid = ((min(kend, (kt + 1) * BN) - 1) >> piece_shift) - (max(kbegin, kt * BN) >> piece_shift) + 1;
+      const int p0 = lane * piece, j0 = kt * BN + p0;
+      // runs wholly before the window may lie in pages already given back: they are not read
+      const bool mine = lane < pieces_per_tile && j0 < kend && j0 + piece > kbegin;
+      unsigned long long* full = kv ? &v_full[s] : &k_full[s];
       int stop = 0;
       if (lane == 0) {
-        if (j >= STAGES && !bar_wait(&kv_empty[s], ((j / STAGES) - 1) & 1)) {
+        if (j >= STAGES && !bar_wait(kv ? &v_empty[s] : &k_empty[s], ((j / STAGES) - 1) & 1)) {
           *abort_flag = 1;
           atomicExch(error, 11);
         }
         stop = *abort_flag;
-        if (!stop) {
-          int n_valid = 0;
-          for (int p0 = 0; p0 < BN; p0 += ps) {
-            const int j0 = kt * BN + p0;
-            if (j0 < kend && j0 + ps > live_from) ++n_valid;
-          }
-          bar_expect(&kv_full[s], (unsigned)n_valid * ps * 128u * 2u * 2u);
-        }
+        if (!stop) bar_expect(full, (unsigned)n_valid * piece * 128u * 2u);
       }
       stop = __shfl_sync(0xffffffffu, stop, 0);
-      if (stop) break;
-      if (lane < pages_per_tile) {
-        const int p0 = lane * ps, j0 = kt * BN + p0;
-        if (j0 < kend && j0 + ps > live_from) {
-          const int page = bt[j0 / ps];
-          const int grow = (page * n_kv_head + hk) * ps;       // row of the page's first key in the [rows, HD] view
-          unsigned char* dk = sK + s * TILE_BYTES + p0 * 128;
-          unsigned char* dv = sV + s * TILE_BYTES + p0 * 128;
-          tma_2d(dk, &map_k, 0, grow, &kv_full[s]);
-          tma_2d(dk + HALF_BYTES, &map_k, 64, grow, &kv_full[s]);
-          tma_2d(dv, &map_v, 0, grow, &kv_full[s]);
-          tma_2d(dv + HALF_BYTES, &map_v, 64, grow, &kv_full[s]);
-        }
+      if (stop) return false;
+      if (mine) {
+        const int grow = (page * n_kv_head + hk) * ps + j0 % ps;   // row of the run's first key in the [rows, HD] view
+        unsigned char* d = (kv ? sV : sK) + s * KV_BYTES + p0 * 128;
+        tma_2d(d, kv ? &map_v : &map_k, 0, grow, full);
+        tma_2d(d + KV_HALF_BYTES, kv ? &map_v : &map_k, 64, grow, full);
       }
       __syncwarp();
+      return true;
+    };
+    // The page of this lane's run is looked up a tile before it is used: the block table is in global memory, and
+    // a lookup inside load() would put its latency between every two tiles.
+    auto page_of = [&](int j) -> int {
+      const int j0 = (kt_first + j) * BN + lane * piece;
+      return (j < n_tiles && lane < pieces_per_tile && j0 < kend && j0 + piece > kbegin) ? __ldg(bt + j0 / ps) : 0;
+    };
+    const int kv = warp == 0 ? 0 : 1;
+    int page_now = page_of(0);
+    for (int t = 0; t < n_tiles; ++t) {
+      const int page_next = page_of(t + 1);
+      if (!load(t, kv, page_now)) break;
+      page_now = page_next;
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // S is double-buffered in tensor memory: Q K^T of tile j+1 is issued before the softmax of tile j is awaited,
-      // so the tensor cores work while the softmax warps do.
+      // The descriptors are built once: the one thread that issues the products has nothing to overlap their
+      // arithmetic with.  An operand further on in shared memory is the same descriptor plus its offset in 16-byte
+      // units (the address field holds shared-memory addresses with room to spare).
+      const unsigned long long dq = desc_kmajor(sQ), dk = desc_kmajor(sK), dp = desc_kmajor(sP),
+                               dv = desc_mnmajor(sV, KV_HALF_BYTES, 1024);
       bool ok = bar_wait(q_full, 0);
       if (!ok) { *abort_flag = 2; atomicExch(error, 12); }
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES;
-        if (!bar_wait(&kv_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); return false; }
+        if (!bar_wait(&k_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); return false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {   // eight steps of 16 along the head dim, four in each 64-wide half
-          const int off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma(tmem_s + (j & 1) * 128, desc_kmajor(sQ + off), desc_kmajor(sK + s * TILE_BYTES + off), idesc(false),
-              kk > 0 ? 1u : 0u);
+          mma(tmem_s + (j & 1) * BN, dq + (unsigned)(((kk / 4) * Q_HALF_BYTES + (kk % 4) * 32) >> 4),
+              dk + (unsigned)((s * KV_BYTES + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32) >> 4), idesc(false, BN), kk > 0 ? 1u : 0u);
         }
+        commit(&k_empty[s]);   // the keys' stage is free again when these products have read it
         commit(&s_full[j & 1]);
         return true;
       };
+      // Q K^T runs two tiles ahead (S has two buffers), so P V of a tile is issued the moment its P is there
       if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
         const int s = j % STAGES;
-        // the next tile's scores: its S buffer was read by the softmax of tile j-1, which p_ready(j-1) has told
-        if (j + 1 < n_tiles) {
-          ok = issue_qk(j + 1);
-          if (!ok) break;
-        }
         if (!bar_wait(p_ready, j & 1)) { *abort_flag = 4; atomicExch(error, 14); break; }
+        if (!bar_wait(&v_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        // P V: eight steps of 16 keys; V is MN-major: 16 keys are two 1024-byte atoms, the other half of the head dim 16 KB on
+        // O += P V: four steps of 16 keys; V is MN-major: 16 keys are two 1024-byte atoms, the other half of the
+        // head dim KV_HALF_BYTES on
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const int poff = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma(tmem_pv, desc_kmajor(sP + poff), desc_mnmajor(sV + s * TILE_BYTES + kk * 2048, HALF_BYTES, 1024),
-              idesc(true), kk > 0 ? 1u : 0u);
+          mma(tmem_o, dp + (unsigned)((kk * 32) >> 4), dv + (unsigned)((s * KV_BYTES + kk * 2048) >> 4), idesc(true, HD),
+              (j > 0 || kk > 0) ? 1u : 0u);
         }
-        commit(&kv_empty[s]);   // this stage's keys and values are free again when the products have read them
-        commit(pv_full);
+        commit(&v_empty[s]);   // the values' stage is free again when these products have read it
+        commit(pv_done);
+        // the scores of tile j+2 go where those of tile j were: the softmax has read them (it said so with p_ready)
+        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
       }
     }
   } else {
     // Eight softmax warps: a warp reads the quarter of tensor memory given by its index % 4, so two warps share a
-    // quarter: two threads per query row.  Thread `half` takes keys [64*half, 64*half+64) of every tile for the
-    // scores and head dims [64*half, 64*half+64) of the output; the two exchange the row maximum through shared
-    // memory (an mbarrier per quarter, waited on with a limit like every other) and add their parts of the row
-    // sum at the end.
-    __shared__ float xmax[2][BM];
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    // quarter: two threads per query row.  Thread `half` takes keys [32*half, 32*half+32) of every tile and, for
+    // rescaling and the result, head dims [64*half, 64*half+64).
+    const int quarter = warp & 3, half = (warp - 2) >> 2;   // warps 2..9
     const int r = quarter * 32 + lane;              // this thread's query row within the tile
     const int p = pos0 + r;                         // its position
     const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    const int c_base = half * 32;
+    float m = -INFINITY, l = 0.f;                   // the row's reference (log2 units) and the sum of its P
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int j0 = (kt_first + j) * BN;
       if (!bar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(error, 15); ok = false; break; }
       if (*abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const unsigned s_addr = tmem_s + (j & 1) * 128 + lane_addr + half * 64;
+      float v[32];
+      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr + c_base, v);
       const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
-      // keys this row may see in this tile: [lo, hi), as columns of the tile; this thread's columns start at c_base
-      const int hi = min(min(p + 1, kend) - j0, BN);
-      const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
-      const int c_base = half * 64;
-      // pass 1: the maximum of this thread's 64 raw scores (the scale is positive), then of the row
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float v[32];
-        tmem_ld32(s_addr + c0, v);
-        if (!edge) {
+      if (edge) {
+        // keys this row may see in this tile: [lo, hi), as columns of the tile
+        const int hi = min(min(p + 1, kend) - j0, BN);
+        const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c_base + c0 + i >= lo && c_base + c0 + i < hi) mx = fmaxf(mx, v[i]);
-        }
+        for (int i = 0; i < 32; ++i)
+          if (c_base + i < lo || c_base + i >= hi) v[i] = -INFINITY;
       }
-      xmax[half][r] = mx;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+      // the other thread of the row has read the maxima of the tile before (it arrived on p_ready after that)
+      if (j > 0 && !bar_wait(p_ready, (j - 1) & 1)) { atomicExch(error, 19); ok = false; break; }
+      xmax[half * BM + r] = __float2bfloat16_ru(mx);   // rounded UP: both threads derive the same reference from the pair
       __syncwarp();
       if (lane == 0) bar_arrive(&pair_bar[quarter]);
       if (!bar_wait(&pair_bar[quarter], j & 1)) { atomicExch(error, 17); ok = false; break; }
-      mx = fmaxf(mx, xmax[half ^ 1][r]) * scale_log2e;
-      const float m_new = fmaxf(m, mx);
-      const float ref = m_new == -INFINITY ? 0.f : m_new;   // a row with no key in range yet
-      const float corr = exp2f(m - ref);
-      // pass 2: P = exp2(S * scale - max) in bfloat16 into shared memory (swizzled rows of 64 keys), and its sum
-      float psum = 0.f;
+      const float m_tile = fmaxf(__bfloat162float(xmax[r]), __bfloat162float(xmax[BM + r])) * scale_log2e;
+      // the products of the tile before have read P and written O
+      if (j > 0 && !bar_wait(pv_done, (j - 1) & 1)) { atomicExch(error, 16); ok = false; break; }
+      const bool raise = m_tile > m + RAISE_BY || m == -INFINITY;
+      if (j > 0 && __any_sync(0xffffffffu, raise && m_tile > m)) {
+        // rescale this thread's half of the row of O in tensor memory; rows that keep their reference multiply by 1
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float f = (raise && m_tile > m) ? exp2f(m - m_tile) : 1.f;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float v[32];
-        tmem_ld32(s_addr + c0, v);
-        unsigned pk[16];
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          float o[32];
+          tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = exp2f(fmaf(v[i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[i + 1], scale_log2e, -ref));
-          if (edge) {
-            if (c_base + c0 + i < lo || c_base + c0 + i >= hi) e0 = 0.f;
-            if (c_base + c0 + i + 1 < lo || c_base + c0 + i + 1 >= hi) e1 = 0.f;
-          }
-          psum += e0 + e1;
-          __nv_bfloat162 b = __floats2bfloat162_rn(e0, e1);
-          pk[i >> 1] = *reinterpret_cast<unsigned*>(&b);
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32(tmem_o + lane_addr + half * 64 + c0, o);
         }
-        unsigned char* prow = sP + half * HALF_BYTES + r * 128;   // this thread's 64 keys are one swizzled row
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c0 / 8 + q4) ^ (r & 7);            // 16-byte piece within the 128-byte row, swizzled
-          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-        }
+        l *= f;
       }
-      l = l * corr + psum;
-      m = m_new;
-      if (j0 + BN > kend && half == 0 && j0 + r >= kend) {
+      if (raise && m_tile > m) m = m_tile;
+      const float ref = m == -INFINITY ? 0.f : m;   // a row with no key in range yet: every P is exp2(-inf) = 0
+      // P = exp2(S * scale - m) in bfloat16 into shared memory (rows of 64 keys, 128-byte swizzle), and its sum
+      float psum = 0.f;
+      unsigned char* prow = sP + r * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        unsigned pk[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float e0 = exp2f(fmaf(v[q4 * 8 + 2 * i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[q4 * 8 + 2 * i + 1], scale_log2e, -ref));
+          psum += e0 + e1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
+          pk[i] = *reinterpret_cast<unsigned*>(&b2);
+        }
+        const int chunk = (half * 4 + q4) ^ (r & 7);            // 16-byte piece within the 128-byte row, swizzled
+        *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l += psum;
+      if (j0 + BN > kend && half == 0 && r < BN && j0 + r >= kend) {
         // the last tile: values of keys past the end are whatever the page held; P is zero there, but zero
         // times a NaN left by an earlier owner of the page would still be NaN: this thread clears key row r
-        unsigned char* vrow = sV + (j % STAGES) * TILE_BYTES + r * 128;
+        if (!bar_wait(&v_full[j % STAGES], (j / STAGES) & 1)) { atomicExch(error, 13); ok = false; break; }   // they have landed
+        unsigned char* vrow = sV + (j % STAGES) * KV_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(vrow + HALF_BYTES + c * 16) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(vrow + KV_HALF_BYTES + c * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P must be visible to the tensor cores' reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) bar_arrive(p_ready);
-      if (!bar_wait(pv_full, j & 1)) { atomicExch(error, 16); ok = false; break; }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_pv + lane_addr + half * 64 + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, v[i]);
-      }
     }
-    // the two threads of a row add their parts of the row sum
+    if (ok && !bar_wait(pv_done, (n_tiles - 1) & 1)) { atomicExch(error, 16); ok = false; }
     if (ok) {
-      xmax[half][r] = l;
+      // the two threads of a row add their parts of the row sum (P's buffer is free now)
+      float* xsum = reinterpret_cast<float*>(sP);
+      xsum[half * BM + r] = l;
       __syncwarp();
       if (lane == 0) bar_arrive(&pair_bar[quarter]);
       if (!bar_wait(&pair_bar[quarter], n_tiles & 1)) { atomicExch(error, 17); ok = false; }
+      if (ok) l += xsum[(half ^ 1) * BM + r];
     }
-    if (ok && r < rows_here) {
-      const float inv = 1.f / (l + xmax[half ^ 1][r]);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.f / l;
       __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD + half * 64;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
+        if (r < rows_here) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 8) {
-        uint4 q4;
-        __nv_bfloat162 a = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-        __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), d = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-        q4.x = *reinterpret_cast<unsigned*>(&a);
-        q4.y = *reinterpret_cast<unsigned*>(&b);
-        q4.z = *reinterpret_cast<unsigned*>(&c);
-        q4.w = *reinterpret_cast<unsigned*>(&d);
-        *reinterpret_cast<uint4*>(dst + i) = q4;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 q4;
+            __nv_bfloat162 a = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), d = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            q4.x = *reinterpret_cast<unsigned*>(&a);
+            q4.y = *reinterpret_cast<unsigned*>(&b);
+            q4.z = *reinterpret_cast<unsigned*>(&c);
+            q4.w = *reinterpret_cast<unsigned*>(&d);
+            *reinterpret_cast<uint4*>(dst + c0 + i) = q4;
+          }
+        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(512) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(256) : "memory");
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -431,17 +481,31 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   int st = tc5::make_map(&map_q, q, total_rows, n_head * hd, q_ld, tc5::BM);
   if (st != CBIS_OK) return st;
   const long long cache_rows = (long long)num_pages * n_kv_head * ps;
-  st = tc5::make_map(&map_k, kc, cache_rows, hd, hd, ps);
+  st = tc5::make_map(&map_k, kc, cache_rows, hd, hd, ps < tc5::BN ? ps : tc5::BN);
   if (st != CBIS_OK) return st;
-  st = tc5::make_map(&map_v, vc, cache_rows, hd, hd, ps);
+  st = tc5::make_map(&map_v, vc, cache_rows, hd, hd, ps < tc5::BN ? ps : tc5::BN);
   if (st != CBIS_OK) return st;
-  const size_t smem = (size_t)(2 + 2 * tc5::STAGES) * tc5::TILE_BYTES + 1024 + 256;
+  const size_t smem = tc5::SMEM_BYTES;
   auto kern = tc5::paged_prefill_tc5_kernel;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((max_seg_rows + tc5::BM - 1) / tc5::BM, n_head, n_seg);
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid((unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg);
   e = launch_pdl(kern, grid, dim3(tc5::THREADS), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
-                 cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, n_head, n_kv_head, ps,
+                 cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, n_seg, n_head, n_kv_head, ps,
                  scale * 1.4426950408889634f, window, error);
   return (int)e;
+}
+
+// How many blocks of the kernel above an SM holds at a time (it is sized for two); negative: a CUDA error.
+CBIS_EXPORT int cbis_paged_prefill_tc5_blocks_per_sm() {
+  auto kern = tc5::paged_prefill_tc5_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc5::SMEM_BYTES);
+  if (e != cudaSuccess) return -(int)e;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return -(int)e;
+  int n = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tc5::THREADS, tc5::SMEM_BYTES);
+  return e == cudaSuccess ? n : -(int)e;
 }

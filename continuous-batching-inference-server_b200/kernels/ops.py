@@ -338,7 +338,7 @@ def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out
 
 def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
                       n_head, n_kv_head, head_dim, page_size, scale, window=0):
-    """The same attention as ``paged_prefill_bf16`` on the tcgen05 tensor cores (TMA operands, S and P V in
+    """The same attention as ``paged_prefill_bf16`` on the tcgen05 tensor cores (TMA operands, S and the output in
     tensor memory).  Head size 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering."""
     _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
     if head_dim != 128:
@@ -353,6 +353,14 @@ def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out,
         c_int(out.stride(0)), c_int(seg0), c_int(n_seg), c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head),
         c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), _ptr(tcgen05_error_flag(q.device)), _stream())
     _check(st, "paged_prefill_tc5", f"segments={n_seg} heads={n_head}/{n_kv_head} page={page_size}")
+
+
+def paged_prefill_tc5_blocks_per_sm():
+    """How many blocks of the tcgen05 prefill attention an SM holds at a time (the kernel is sized for two)."""
+    n = kernels().cbis_paged_prefill_tc5_blocks_per_sm()
+    if n < 0:
+        raise KernelError(f"paged_prefill_tc5: occupancy query failed with CUDA error {-n}")
+    return n
 
 
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):

@@ -458,3 +458,9 @@ def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window):
     ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 0, S, max(seg_rows),
                            n_head, n_kv_head, hd, ps, c["scale"], window)
     assert (out.float() - out2.float()).abs().max().item() < 2e-2 * max(1.0, c["ref"].abs().max().item())
+
+
+def test_prefill_attention_tcgen05_two_blocks_per_sm(ops):
+    """Its shared memory, registers and tensor memory are sized so that an SM holds two blocks: one block's
+    softmax runs while the other's products do."""
+    assert ops.paged_prefill_tc5_blocks_per_sm() >= 1
