@@ -8,15 +8,16 @@
 // (Gathering them with 16-byte cp.async copies from one warp was tried and is slower: a warp cannot keep
 // enough of those in flight.)
 // One thread issues the products: S = Q K^T (tcgen05.mma, 128x64x16, eight per tile) into tensor memory
-// (two buffers, so the scores of the next tile are computed while the softmax of this one runs), and
+// (two buffers, so the scores of the next two tiles are computed while the softmax of this one runs), and
 // O += P V (128x128x16, four per tile) into an accumulator that STAYS in tensor memory for the whole row
-// tile.  Eight warps share the query rows, two threads per row: each reads its half of the row's scores
-// with one tcgen05.ld, masks and takes the maximum in 32-bit; the two exchange their maxima, compute
-// P = exp2(S * scale - m) in 32-bit, write it in bfloat16 into shared memory in the swizzled layout the
-// product reads, and keep the running sum.  The reference value m only has to be shared by a row's
-// numbers, not to be their exact maximum: it is raised, and O in tensor memory and the sum rescaled (in
-// 32-bit), only when a tile's maximum exceeds it by more than 2^8, which after the first tiles is rare;
-// the quotient O / sum at the end is the same.  V is used as it lies in the cache ([key][head dim],
+// tile.  Four warps own one query row per thread: a thread reads its row's 64 scores with tcgen05.ld,
+// masks and takes the maximum in 32-bit (no shuffles, no exchange), computes P = exp2(S * scale - m) in
+// 32-bit, writes it in bfloat16 into shared memory in the swizzled layout the product reads, and keeps
+// the running sum.  The reference value m only has to be common to a row's numbers, not to be their
+// exact maximum: it is raised, and O in tensor memory and the sum rescaled (in 32-bit), only when a
+// tile's maximum exceeds it by more than 2^8, which after the first tiles is rare; the quotient
+// O / sum at the end is the same.  (Two threads per row, each with half the scores, were slower: the
+// exchange of the two maxima costs more than the shorter loops save.)  V is used as it lies in the cache ([key][head dim],
 // head dim contiguous): it is the MN-major B operand of P V.
 //
 // Shared memory (113 KB) and tensor memory (256 of 512 columns) are sized for TWO blocks per SM: while
@@ -40,9 +41,9 @@ constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 of th
 constexpr int KV_BYTES = 2 * KV_HALF_BYTES;    // a tile of keys, or of values
 constexpr int P_BYTES = BM * 128;              // 128 rows of 64 keys
 constexpr int STAGES = 2;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 512 + 160;   // + maxima exchange + barriers
+constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 128;   // + barriers
 constexpr float RAISE_BY = 8.f;                // the reference is raised when a tile's maximum exceeds it by 2^8
-constexpr int THREADS = 352;                   // warp 0: Q and keys, warp 1: MMA + tensor memory, warps 2..9: softmax, warp 10: values
+constexpr int THREADS = 224;                   // warp 0: Q and keys, warp 1: MMA + tensor memory, warps 2..5: softmax, warp 6: values
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -144,13 +145,12 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   unsigned char* sK = sQ + Q_BYTES;                           // STAGES tiles
   unsigned char* sV = sK + STAGES * KV_BYTES;                 // STAGES tiles
   unsigned char* sP = sV + STAGES * KV_BYTES;                 // 128 rows of 64 keys
-  __nv_bfloat16* xmax = reinterpret_cast<__nv_bfloat16*>(sP + P_BYTES);   // [2][BM]: a row's two maxima, rounded up
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES + 512);
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES);
   // keys and values have barriers of their own: a stage of keys is free as soon as Q K^T has read it, long before
   // the values of the same tile are, so the keys of tile j+2 are on their way while tile j is still being worked on
   unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12, *pair_bar = bars + 13;   // pair_bar: one per quarter of the rows
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 17);
+                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -188,9 +188,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     bar_init(&s_full[0], 1);
     bar_init(&s_full[1], 1);
-    bar_init(p_ready, 8);
+    bar_init(p_ready, 4);
     bar_init(pv_done, 1);
-    for (int q = 0; q < 4; ++q) bar_init(&pair_bar[q], 2);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -205,8 +204,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
   pdl_wait();  // q and this step's keys/values come from the kernels before
 
-  if (warp == 0 || warp == 10) {
-    // Warp 0 brings Q and the keys, warp 10 the values, each as far ahead as its two stages allow (one thread issues
+  if (warp == 0 || warp == 6) {
+    // Warp 0 brings Q and the keys, warp 6 the values, each as far ahead as its two stages allow (one thread issues
     // a TMA copy in about 60 ns, and a tile of 16-key pages is eight copies of keys and eight of values).
     // The whole warp produces: lane i looks up run i of the tile (a page, or 64 keys of a larger page) in the block
     // table and issues its two copies; lane 0 posts the expected bytes first.
@@ -303,14 +302,13 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
     }
   } else {
-    // Eight softmax warps: a warp reads the quarter of tensor memory given by its index % 4, so two warps share a
-    // quarter: two threads per query row.  Thread `half` takes keys [32*half, 32*half+32) of every tile and, for
-    // rescaling and the result, head dims [64*half, 64*half+64).
-    const int quarter = warp & 3, half = (warp - 2) >> 2;   // warps 2..9
+    // Four softmax warps, one thread per query row: a warp reads the quarter of tensor memory given by its index % 4.
+    // With the output in tensor memory a thread's share of a tile is one load of 64 scores, their maximum, 64
+    // exponentials and eight 16-byte stores of P: no exchange between threads anywhere.
+    const int quarter = warp & 3;                    // warps 2..5
     const int r = quarter * 32 + lane;              // this thread's query row within the tile
     const int p = pos0 + r;                         // its position
     const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
-    const int c_base = half * 32;
     float m = -INFINITY, l = 0.f;                   // the row's reference (log2 units) and the sum of its P
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -318,64 +316,58 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (!bar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(error, 15); ok = false; break; }
       if (*abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float v[32];
-      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr + c_base, v);
+      float v[BN];
+      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr, v);
+      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr + 32, v + 32);
       const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
       if (edge) {
         // keys this row may see in this tile: [lo, hi), as columns of the tile
         const int hi = min(min(p + 1, kend) - j0, BN);
         const int lo = window > 0 ? max(p - window + 1 - j0, 0) : 0;
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c_base + i < lo || c_base + i >= hi) v[i] = -INFINITY;
+        for (int i = 0; i < BN; ++i)
+          if (i < lo || i >= hi) v[i] = -INFINITY;
       }
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
-      // the other thread of the row has read the maxima of the tile before (it arrived on p_ready after that)
-      if (j > 0 && !bar_wait(p_ready, (j - 1) & 1)) { atomicExch(error, 19); ok = false; break; }
-      xmax[half * BM + r] = __float2bfloat16_ru(mx);   // rounded UP: both threads derive the same reference from the pair
-      __syncwarp();
-      if (lane == 0) bar_arrive(&pair_bar[quarter]);
-      if (!bar_wait(&pair_bar[quarter], j & 1)) { atomicExch(error, 17); ok = false; break; }
-      const float m_tile = fmaxf(__bfloat162float(xmax[r]), __bfloat162float(xmax[BM + r])) * scale_log2e;
+      for (int i = 0; i < BN; ++i) mx = fmaxf(mx, v[i]);
+      const float m_tile = mx * scale_log2e;
       // the products of the tile before have read P and written O
       if (j > 0 && !bar_wait(pv_done, (j - 1) & 1)) { atomicExch(error, 16); ok = false; break; }
-      const bool raise = m_tile > m + RAISE_BY || m == -INFINITY;
-      if (j > 0 && __any_sync(0xffffffffu, raise && m_tile > m)) {
-        // rescale this thread's half of the row of O in tensor memory; rows that keep their reference multiply by 1
+      const bool raise = m_tile > m + RAISE_BY || (m == -INFINITY && m_tile > m);
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        // rescale the row of O in tensor memory; rows that keep their reference multiply by 1
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float f = (raise && m_tile > m) ? exp2f(m - m_tile) : 1.f;
+        const float f = raise ? exp2f(m - m_tile) : 1.f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           float o[32];
-          tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
+          tmem_ld32(tmem_o + lane_addr + c0, o);
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] *= f;
-          tmem_st32(tmem_o + lane_addr + half * 64 + c0, o);
+          tmem_st32(tmem_o + lane_addr + c0, o);
         }
         l *= f;
       }
-      if (raise && m_tile > m) m = m_tile;
+      if (raise) m = m_tile;
       const float ref = m == -INFINITY ? 0.f : m;   // a row with no key in range yet: every P is exp2(-inf) = 0
       // P = exp2(S * scale - m) in bfloat16 into shared memory (rows of 64 keys, 128-byte swizzle), and its sum
       float psum = 0.f;
       unsigned char* prow = sP + r * 128;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
+      for (int q8 = 0; q8 < 8; ++q8) {
         unsigned pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float e0 = exp2f(fmaf(v[q4 * 8 + 2 * i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[q4 * 8 + 2 * i + 1], scale_log2e, -ref));
+          const float e0 = exp2f(fmaf(v[q8 * 8 + 2 * i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[q8 * 8 + 2 * i + 1], scale_log2e, -ref));
           psum += e0 + e1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
           pk[i] = *reinterpret_cast<unsigned*>(&b2);
         }
-        const int chunk = (half * 4 + q4) ^ (r & 7);            // 16-byte piece within the 128-byte row, swizzled
-        *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4*>(prow + ((q8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);   // swizzled
       }
       l += psum;
-      if (j0 + BN > kend && half == 0 && r < BN && j0 + r >= kend) {
+      if (j0 + BN > kend && r < BN && j0 + r >= kend) {
         // the last tile: values of keys past the end are whatever the page held; P is zero there, but zero
         // times a NaN left by an earlier owner of the page would still be NaN: this thread clears key row r
         if (!bar_wait(&v_full[j % STAGES], (j / STAGES) & 1)) { atomicExch(error, 13); ok = false; break; }   // they have landed
@@ -393,22 +385,13 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     if (ok && !bar_wait(pv_done, (n_tiles - 1) & 1)) { atomicExch(error, 16); ok = false; }
     if (ok) {
-      // the two threads of a row add their parts of the row sum (P's buffer is free now)
-      float* xsum = reinterpret_cast<float*>(sP);
-      xsum[half * BM + r] = l;
-      __syncwarp();
-      if (lane == 0) bar_arrive(&pair_bar[quarter]);
-      if (!bar_wait(&pair_bar[quarter], n_tiles & 1)) { atomicExch(error, 17); ok = false; }
-      if (ok) l += xsum[(half ^ 1) * BM + r];
-    }
-    if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = 1.f / l;
-      __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD + half * 64;
+      __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         float o[32];
-        tmem_ld32(tmem_o + lane_addr + half * 64 + c0, o);
+        tmem_ld32(tmem_o + lane_addr + c0, o);
         if (r < rows_here) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
