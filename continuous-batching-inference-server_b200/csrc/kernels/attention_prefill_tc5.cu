@@ -41,10 +41,10 @@ constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 of th
 constexpr int KV_BYTES = 2 * KV_HALF_BYTES;    // a tile of keys, or of values
 constexpr int P_BYTES = BM * 128;              // 128 rows of 64 keys
 constexpr int STAGES = 2;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 128;   // + barriers
+constexpr int SMEM_BYTES = Q_BYTES + (1 + STAGES) * KV_BYTES + 2 * P_BYTES + 128;   // Q, keys (one stage), values, P (two buffers), barriers
 constexpr float RAISE_BY = 8.f;                // the reference is raised when a tile's maximum exceeds it by 2^8
 constexpr int THREADS = 224;                   // warp 0: Q and keys, warp 1: MMA + tensor memory, warps 2..5: softmax, warp 6: values
-constexpr unsigned SPIN_LIMIT = 1u << 24;
+constexpr unsigned SPIN_LIMIT = 1u << 21;      // tries of up to 1 us each
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(void* bar, unsigned count) {
@@ -60,8 +60,10 @@ __device__ __forceinline__ bool bar_wait(void* bar, unsigned parity) {
   const unsigned a = s32(bar);
   for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
     unsigned ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(a), "r"(parity) : "memory");
+    // with a time hint the thread sleeps in hardware until the phase completes (or 1 us passes) instead of polling:
+    // the many waiting warps of a block leave the issue slots to the few that work
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(a), "r"(parity), "r"(1000u) : "memory");
     if (ok) return true;
   }
   return false;
@@ -118,6 +120,26 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// Two loads of 32 columns in flight together, then one wait.
+__device__ __forceinline__ void tmem_ld64(unsigned taddr, float* v) {
+  unsigned r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+      "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -134,31 +156,36 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// grid: row tiles of the longest segment x heads x segments from seg0 on, in one dimension
-__global__ void __launch_bounds__(THREADS, 2)
+// grid: row tiles of the longest segment x heads x segments from seg0 on, in one dimension, times two: the two
+// blocks of a cluster share a row tile, the first takes the first half of its key tiles and the second the rest,
+// and at the end the second hands its sum, reference and output to the first through distributed shared memory.
+// The row tile with the most keys decides how long the kernel runs, and its chain of tiles is halved this way.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 2)
 paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const int* block_table, int max_blocks,
                          const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_seg,
                          int n_head, int n_kv_head, int ps, float scale_log2e, int window, int* error) {
   extern __shared__ __align__(1024) unsigned char base[];   // no byte to spare for rounding the address up: checked below
   unsigned char* sQ = base;                                   // 2 halves of the head dim
-  unsigned char* sK = sQ + Q_BYTES;                           // STAGES tiles
-  unsigned char* sV = sK + STAGES * KV_BYTES;                 // STAGES tiles
-  unsigned char* sP = sV + STAGES * KV_BYTES;                 // 128 rows of 64 keys
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES);
+  unsigned char* sK = sQ + Q_BYTES;                           // one tile: Q K^T runs two tiles ahead, so the next keys have time
+  unsigned char* sV = sK + KV_BYTES;                          // STAGES tiles
+  unsigned char* sP = sV + STAGES * KV_BYTES;                 // two buffers of 128 rows of 64 keys: P V of a tile runs beside the next softmax
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + 2 * P_BYTES);
   // keys and values have barriers of their own: a stage of keys is free as soon as Q K^T has read it, long before
   // the values of the same tile are, so the keys of tile j+2 are on their way while tile j is still being worked on
   unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12;
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 13);
+                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12;   // k_full/k_empty: [0] only; pv_done: [2], tiles in turn
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // late row tiles have the most keys to walk: blocks are numbered so that those of ALL heads and segments come
   // first, and an SM's second block is a light one
-  const int per_rank = n_head * n_seg, n_row_tiles = gridDim.x / per_rank;
-  const int tile = n_row_tiles - 1 - (int)blockIdx.x / per_rank, seg = seg0 + ((int)blockIdx.x % per_rank) / n_head,
-            h = (int)blockIdx.x % n_head;
+  unsigned rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int pair = (int)blockIdx.x >> 1;
+  const int per_rank = n_head * n_seg, n_row_tiles = (gridDim.x >> 1) / per_rank;
+  const int tile = n_row_tiles - 1 - pair / per_rank, seg = seg0 + (pair % per_rank) / n_head, h = pair % n_head;
   pdl_trigger();
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * BM >= n_rows) return;
@@ -171,11 +198,13 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int rows_here = min(BM, n_rows - tile * BM);
   const int kend = pos0 + rows_here;
   const int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int kt_first = kbegin / BN, kt_last = (kend - 1) / BN, n_tiles = kt_last - kt_first + 1;
+  const int kt_all = kbegin / BN, n_all = (kend - 1) / BN - kt_all + 1, n_first = (n_all + 1) / 2;
+  // this block's key tiles: the first takes n_first of them, the second the rest (none, if there is only one)
+  const int kt_first = kt_all + (rank ? n_first : 0), n_tiles = rank ? n_all - n_first : n_first;
   const int* bt = block_table + (size_t)seg * max_blocks;
 
   // keys and values of rows that no copy will fill must be finite: P is zero there, and 0 * NaN is NaN
-  for (int i = threadIdx.x; i < 2 * STAGES * KV_BYTES / 16; i += THREADS)
+  for (int i = threadIdx.x; i < (1 + STAGES) * KV_BYTES / 16; i += THREADS)
     reinterpret_cast<uint4*>(sK)[i] = make_uint4(0, 0, 0, 0);
 
   if (threadIdx.x == 0) {
@@ -189,7 +218,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     bar_init(&s_full[0], 1);
     bar_init(&s_full[1], 1);
     bar_init(p_ready, 4);
-    bar_init(pv_done, 1);
+    bar_init(&pv_done[0], 1);
+    bar_init(&pv_done[1], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -204,6 +234,12 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
   pdl_wait();  // q and this step's keys/values come from the kernels before
 
+  // softmax state of this thread's query row (warps 2..5; declared here because the hand-over after the loops needs it)
+  const int quarter = warp & 3;
+  const int r = quarter * 32 + lane;              // this thread's query row within the tile
+  const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+  float m = -INFINITY, l = 0.f;                   // the row's reference (log2 units) and the sum of its P
+  bool ok = true;
   if (warp == 0 || warp == 6) {
     // Warp 0 brings Q and the keys, warp 6 the values, each as far ahead as its two stages allow (one thread issues
     // a TMA copy in about 60 ns, and a tile of 16-key pages is eight copies of keys and eight of values).
@@ -218,7 +254,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int piece = min(ps, BN), pieces_per_tile = BN / piece, piece_shift = 31 - __clz(piece);
     // copies tile j's keys (kv = 0) or values (kv = 1) into their stage; false when the block has given up
     auto load = [&](int j, int kv, int page) -> bool {
-      const int s = j % STAGES, kt = kt_first + j;
+      const int s = kv ? j % STAGES : 0, kt = kt_first + j;   // the keys have one stage
       // runs of the tile with a key in [kbegin, kend): from the one holding the first such key to the one holding the last
       const int n_valid = ((min(kend, (kt + 1) * BN) - 1) >> piece_shift) - (max(kbegin, kt * BN) >> piece_shift) + 1;
       const int p0 = lane * piece, j0 = kt * BN + p0;
@@ -227,7 +263,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       unsigned long long* full = kv ? &v_full[s] : &k_full[s];
       int stop = 0;
       if (lane == 0) {
-        if (j >= STAGES && !bar_wait(kv ? &v_empty[s] : &k_empty[s], ((j / STAGES) - 1) & 1)) {
+        if (kv ? (j >= STAGES && !bar_wait(&v_empty[s], ((j / STAGES) - 1) & 1)) : (j >= 1 && !bar_wait(&k_empty[0], (j - 1) & 1))) {
           *abort_flag = 1;
           atomicExch(error, 11);
         }
@@ -268,20 +304,19 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       bool ok = bar_wait(q_full, 0);
       if (!ok) { *abort_flag = 2; atomicExch(error, 12); }
       auto issue_qk = [&](int j) -> bool {
-        const int s = j % STAGES;
-        if (!bar_wait(&k_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); return false; }
+        if (!bar_wait(&k_full[0], j & 1)) { *abort_flag = 3; atomicExch(error, 13); return false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {   // eight steps of 16 along the head dim, four in each 64-wide half
           mma(tmem_s + (j & 1) * BN, dq + (unsigned)(((kk / 4) * Q_HALF_BYTES + (kk % 4) * 32) >> 4),
-              dk + (unsigned)((s * KV_BYTES + (kk / 4) * KV_HALF_BYTES + (kk % 4) * 32) >> 4), idesc(false, BN), kk > 0 ? 1u : 0u);
+              dk + (unsigned)(((kk / 4) * KV_HALF_BYTES + (kk % 4) * 32) >> 4), idesc(false, BN), kk > 0 ? 1u : 0u);
         }
-        commit(&k_empty[s]);   // the keys' stage is free again when these products have read it
+        commit(&k_empty[0]);   // the keys' stage is free again when these products have read it
         commit(&s_full[j & 1]);
         return true;
       };
       // Q K^T runs two tiles ahead (S has two buffers), so P V of a tile is issued the moment its P is there
-      if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 0) ok = issue_qk(0);
       if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
         const int s = j % STAGES;
@@ -292,11 +327,11 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // head dim KV_HALF_BYTES on
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          mma(tmem_o, dp + (unsigned)((kk * 32) >> 4), dv + (unsigned)((s * KV_BYTES + kk * 2048) >> 4), idesc(true, HD),
+          mma(tmem_o, dp + (unsigned)(((j & 1) * P_BYTES + kk * 32) >> 4), dv + (unsigned)((s * KV_BYTES + kk * 2048) >> 4), idesc(true, HD),
               (j > 0 || kk > 0) ? 1u : 0u);
         }
         commit(&v_empty[s]);   // the values' stage is free again when these products have read it
-        commit(pv_done);
+        commit(&pv_done[j & 1]);
         // the scores of tile j+2 go where those of tile j were: the softmax has read them (it said so with p_ready)
         if (j + 2 < n_tiles) ok = issue_qk(j + 2);
       }
@@ -305,20 +340,14 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // Four softmax warps, one thread per query row: a warp reads the quarter of tensor memory given by its index % 4.
     // With the output in tensor memory a thread's share of a tile is one load of 64 scores, their maximum, 64
     // exponentials and eight 16-byte stores of P: no exchange between threads anywhere.
-    const int quarter = warp & 3;                    // warps 2..5
-    const int r = quarter * 32 + lane;              // this thread's query row within the tile
-    const int p = pos0 + r;                         // its position
-    const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
-    float m = -INFINITY, l = 0.f;                   // the row's reference (log2 units) and the sum of its P
-    bool ok = true;
+    const int p = pos0 + r;                         // this row's position
     for (int j = 0; j < n_tiles; ++j) {
       const int j0 = (kt_first + j) * BN;
       if (!bar_wait(&s_full[j & 1], (j >> 1) & 1)) { atomicExch(error, 15); ok = false; break; }
       if (*abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float v[BN];
-      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr, v);
-      tmem_ld32(tmem_s + (j & 1) * BN + lane_addr + 32, v + 32);
+      tmem_ld64(tmem_s + (j & 1) * BN + lane_addr, v);
       const bool edge = (j0 + BN - 1 > pos0) || (window > 0 && j0 < pos0 + BM - window + 1) || j0 + BN > kend;
       if (edge) {
         // keys this row may see in this tile: [lo, hi), as columns of the tile
@@ -328,15 +357,23 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int i = 0; i < BN; ++i)
           if (i < lo || i >= hi) v[i] = -INFINITY;
       }
-      float mx = -INFINITY;
+      // four independent chains: a single one would be 64 dependent instructions
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BN; ++i) mx = fmaxf(mx, v[i]);
-      const float m_tile = mx * scale_log2e;
-      // the products of the tile before have read P and written O
-      if (j > 0 && !bar_wait(pv_done, (j - 1) & 1)) { atomicExch(error, 16); ok = false; break; }
+      for (int i = 0; i < BN; i += 4) {
+        mx0 = fmaxf(mx0, v[i]);
+        mx1 = fmaxf(mx1, v[i + 1]);
+        mx2 = fmaxf(mx2, v[i + 2]);
+        mx3 = fmaxf(mx3, v[i + 3]);
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * scale_log2e;
+      // this tile's buffer of P was read by the products of the tile before the last
+      if (j > 1 && !bar_wait(&pv_done[j & 1], ((j - 2) >> 1) & 1)) { atomicExch(error, 16); ok = false; break; }
       const bool raise = m_tile > m + RAISE_BY || (m == -INFINITY && m_tile > m);
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // rescale the row of O in tensor memory; rows that keep their reference multiply by 1
+        // rescale the row of O in tensor memory; rows that keep their reference multiply by 1.  Only here does the
+        // softmax wait for the products of the tile before, which write O.
+        if (!bar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1)) { atomicExch(error, 16); ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float f = raise ? exp2f(m - m_tile) : 1.f;
 #pragma unroll 1
@@ -352,21 +389,22 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (raise) m = m_tile;
       const float ref = m == -INFINITY ? 0.f : m;   // a row with no key in range yet: every P is exp2(-inf) = 0
       // P = exp2(S * scale - m) in bfloat16 into shared memory (rows of 64 keys, 128-byte swizzle), and its sum
-      float psum = 0.f;
-      unsigned char* prow = sP + r * 128;
+      float psum = 0.f, psum1 = 0.f;
+      unsigned char* prow = sP + (j & 1) * P_BYTES + r * 128;
 #pragma unroll
       for (int q8 = 0; q8 < 8; ++q8) {
         unsigned pk[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float e0 = exp2f(fmaf(v[q8 * 8 + 2 * i], scale_log2e, -ref)), e1 = exp2f(fmaf(v[q8 * 8 + 2 * i + 1], scale_log2e, -ref));
-          psum += e0 + e1;
+          psum += e0;
+          psum1 += e1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
           pk[i] = *reinterpret_cast<unsigned*>(&b2);
         }
         *reinterpret_cast<uint4*>(prow + ((q8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);   // swizzled
       }
-      l += psum;
+      l += psum + psum1;
       if (j0 + BN > kend && r < BN && j0 + r >= kend) {
         // the last tile: values of keys past the end are whatever the page held; P is zero there, but zero
         // times a NaN left by an earlier owner of the page would still be NaN: this thread clears key row r
@@ -383,10 +421,48 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       __syncwarp();
       if (lane == 0) bar_arrive(p_ready);
     }
-    if (ok && !bar_wait(pv_done, (n_tiles - 1) & 1)) { atomicExch(error, 16); ok = false; }
-    if (ok) {
+    if (ok && n_tiles > 1 && !bar_wait(&pv_done[n_tiles & 1], ((n_tiles - 2) >> 1) & 1)) { atomicExch(error, 16); ok = false; }
+    if (ok && n_tiles > 0 && !bar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) { atomicExch(error, 16); ok = false; }
+  }
+  // ---- the second block's part goes to the first ------------------------------------------------------------
+  // In the first block's shared memory, where its keys and values were: O as [head dim / 4][row][4] floats (64 KB,
+  // 16 bytes per thread and store, no bank conflicts on either side), then reference and sum per row.
+  const bool softmax_warp = warp >= 2 && warp < 6;
+  float* xo = reinterpret_cast<float*>(sK);
+  float* xml = reinterpret_cast<float*>(sK + HD * BM * 4);   // [2][BM], after O (which ends inside P's second buffer)
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");   // the first block's products are done with that memory
+  if (softmax_warp && rank == 1) {
+    unsigned remote_o, remote_ml;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote_o) : "r"(s32(xo)));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote_ml) : "r"(s32(xml)));
+    const bool have = ok && n_tiles > 0;
+    if (have) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = 1.f / l;
+#pragma unroll 1
+      for (int c0 = 0; c0 < HD; c0 += 32) {
+        float o[32];
+        tmem_ld32(tmem_o + lane_addr + c0, o);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(remote_o + (unsigned)((((c0 + i) >> 2) * BM + r) * 16)), "f"(o[i]), "f"(o[i + 1]), "f"(o[i + 2]), "f"(o[i + 3])
+                       : "memory");
+      }
+    }
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_ml + (unsigned)(r * 4)), "f"(have ? m : -INFINITY) : "memory");
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_ml + (unsigned)((BM + r) * 4)), "f"(have ? l : 0.f) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");   // it has arrived
+  if (softmax_warp && rank == 0) {
+    if (ok) {
+      // O = O0 * 2^(m0 - m) + O1 * 2^(m1 - m) with m the larger reference, the sums alike; then O / sum
+      const float m1 = xml[r], l1 = xml[BM + r];
+      const float mm = fmaxf(m, m1);
+      const float f0 = m == -INFINITY ? 0.f : exp2f(m - mm), f1 = (m1 == -INFINITY || l1 == 0.f) ? 0.f : exp2f(m1 - mm);
+      const float inv = 1.f / (l * f0 + l1 * f1);
+      const float g0 = f0 * inv, g1 = f1 * inv;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -394,10 +470,19 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tmem_ld32(tmem_o + lane_addr + c0, o);
         if (r < rows_here) {
 #pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 o1 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (f1 != 0.f) o1 = *reinterpret_cast<const float4*>(xo + (((c0 + i) >> 2) * BM + r) * 4);
+            o[i] = o[i] * g0 + o1.x * g1;
+            o[i + 1] = o[i + 1] * g0 + o1.y * g1;
+            o[i + 2] = o[i + 2] * g0 + o1.z * g1;
+            o[i + 3] = o[i + 3] * g0 + o1.w * g1;
+          }
+#pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 q4;
-            __nv_bfloat162 a = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-            __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), d = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            __nv_bfloat162 a = __floats2bfloat162_rn(o[i], o[i + 1]), b = __floats2bfloat162_rn(o[i + 2], o[i + 3]);
+            __nv_bfloat162 c = __floats2bfloat162_rn(o[i + 4], o[i + 5]), d = __floats2bfloat162_rn(o[i + 6], o[i + 7]);
             q4.x = *reinterpret_cast<unsigned*>(&a);
             q4.y = *reinterpret_cast<unsigned*>(&b);
             q4.z = *reinterpret_cast<unsigned*>(&c);
@@ -474,7 +559,7 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   if (e != cudaSuccess) return (int)e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid((unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg);
+  dim3 grid(2u * (unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg);
   e = launch_pdl(kern, grid, dim3(tc5::THREADS), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
                  cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, n_seg, n_head, n_kv_head, ps,
                  scale * 1.4426950408889634f, window, error);
