@@ -174,8 +174,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   // keys and values have barriers of their own: a stage of keys is free as soon as Q K^T has read it, long before
   // the values of the same tile are, so the keys of tile j+2 are on their way while tile j is still being worked on
   unsigned long long *q_full = bars, *k_full = bars + 1, *k_empty = bars + 3, *v_full = bars + 5, *v_empty = bars + 7,
-                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 12;   // k_full/k_empty: [0] only; pv_done: [2], tiles in turn
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+                     *s_full = bars + 9, *p_ready = bars + 11, *pv_done = bars + 13;   // k_full/k_empty: [0] only; p_ready, pv_done: [2], tiles in turn
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -186,7 +186,6 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int pair = (int)blockIdx.x >> 1;
   const int per_rank = n_head * n_seg, n_row_tiles = (gridDim.x >> 1) / per_rank;
   const int tile = n_row_tiles - 1 - pair / per_rank, seg = seg0 + (pair % per_rank) / n_head, h = pair % n_head;
-  pdl_trigger();
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * BM >= n_rows) return;
   if (s32(base) & 1023) {   // the swizzled tiles need 1024-byte alignment
@@ -217,7 +216,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     bar_init(&s_full[0], 1);
     bar_init(&s_full[1], 1);
-    bar_init(p_ready, 4);
+    bar_init(&p_ready[0], 4);
+    bar_init(&p_ready[1], 4);
     bar_init(&pv_done[0], 1);
     bar_init(&pv_done[1], 1);
     *abort_flag = 0;
@@ -232,6 +232,9 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 128;
+  // The kernel after this one may start only now that this block holds its tensor memory: a block of a later
+  // kernel that allocated first and then waited for this kernel to finish would wait for ever.
+  pdl_trigger();
   pdl_wait();  // q and this step's keys/values come from the kernels before
 
   // softmax state of this thread's query row (warps 2..5; declared here because the hand-over after the loops needs it)
@@ -320,7 +323,9 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; j < n_tiles && ok && !*abort_flag; ++j) {
         const int s = j % STAGES;
-        if (!bar_wait(p_ready, j & 1)) { *abort_flag = 4; atomicExch(error, 14); break; }
+        // Two barriers, tiles in turn: with one, the softmax can finish tile j+1 (its scores are there two tiles ahead)
+        // before this thread has looked at tile j's phase, and a wait by parity then mistakes tile j+2's phase for it
+        if (!bar_wait(&p_ready[j & 1], (j >> 1) & 1)) { *abort_flag = 4; atomicExch(error, 14); break; }
         if (!bar_wait(&v_full[s], (j / STAGES) & 1)) { *abort_flag = 3; atomicExch(error, 13); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         // O += P V: four steps of 16 keys; V is MN-major: 16 keys are two 1024-byte atoms, the other half of the
@@ -419,7 +424,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P must be visible to the tensor cores' reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) bar_arrive(p_ready);
+      if (lane == 0) bar_arrive(&p_ready[j & 1]);
     }
     if (ok && n_tiles > 1 && !bar_wait(&pv_done[n_tiles & 1], ((n_tiles - 2) >> 1) & 1)) { atomicExch(error, 16); ok = false; }
     if (ok && n_tiles > 0 && !bar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1)) { atomicExch(error, 16); ok = false; }

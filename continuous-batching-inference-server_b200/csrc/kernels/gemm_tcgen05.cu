@@ -174,7 +174,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int num_tiles = m_tiles * n_tiles;
   const int n_kt = (K + TC_BK - 1) / TC_BK;
 
-  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -197,6 +196,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
+  // The kernel after this one may start only now that this block holds its tensor memory: a block of a later
+  // kernel that allocated first and then waited for this kernel to finish would wait for ever.
+  pdl_trigger();
   pdl_wait();  // A comes from the kernel before
 
   if (warp == 0) {
@@ -366,7 +368,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const int num_tiles = m_tiles * n_tiles;
   const int n_kt = (K + TC_BK - 1) / TC_BK;
 
-  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < P2_STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -390,6 +391,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   cluster_sync_all();   // the other block's barriers exist before anything here signals them
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const unsigned tmem_base = *tmem_slot;
+  pdl_trigger();   // only now that both blocks hold their tensor memory (see the single-block kernel)
   pdl_wait();  // A comes from the kernel before
 
   if (warp == 0) {

@@ -176,7 +176,12 @@ class Engine:
             if not mgr.append(e.slot, len(e.tokens)):
                 raise RuntimeError(f"slot {e.slot}: no pages left for {len(e.tokens)} more tokens "
                                    f"(free pages per group: {[mgr.free_pages(g) for g in range(mgr.num_groups())]})")
-        return self.runner.step(entries)
+        out = self.runner.step(entries)
+        if any(len(e.tokens) > 1 for e in entries):
+            # a step with prompt portions may have run kernels whose waits are bounded (TMA + tcgen05): a wait that
+            # ran out left wrong logits, and says so through a flag on the device
+            ops.raise_if_kernel_errors(out.device)
+        return out
 
     @torch.no_grad()
     def logits(self, tokens: Sequence[int]) -> torch.Tensor:

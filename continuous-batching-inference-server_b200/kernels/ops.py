@@ -186,7 +186,8 @@ def raise_if_kernel_errors(device="cuda") -> None:
         code = int(flag.item())
         if code:
             flag.zero_()
-            raise KernelError(f"gemm_tcgen05: a bounded wait inside the kernel ran out (code {code}); its results are invalid")
+            raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
+                              f"product, 11-19 the prefill attention); the step's results are invalid")
 
 
 
