@@ -460,6 +460,29 @@ def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window):
     assert (out.float() - out2.float()).abs().max().item() < 2e-2 * max(1.0, c["ref"].abs().max().item())
 
 
+def test_prefill_attention_tcgen05_is_repeatable(ops):
+    """Three hundred launches of a case with many short key ranges (where the threads of a block run furthest
+    apart): every launch gives the bits of the first, and no bounded wait runs out."""
+    hd, ps, n_head = 128, 16, 4
+    seg_ctx, seg_rows = [193, 72, 400, 130, 64, 1000], [61, 70, 2, 130, 7, 300]
+    c = paged_case(ops, torch.bfloat16, n_head, n_head, hd, ps, 0, seg_ctx, seg_rows, seed=5)
+    S = len(seg_ctx)
+    cu = dev(torch.tensor([0] + list(np.cumsum(seg_rows)), dtype=torch.int32))
+    start = dev(torch.tensor([cx - n for cx, n in zip(seg_ctx, seg_rows)], dtype=torch.int32))
+    q, bt = dev(c["q"]), dev(c["bt"])
+    first = None
+    for _ in range(300):
+        out = torch.full_like(c["q"], float("nan")).cuda()
+        ops.paged_prefill_tc5(q, c["kc"], c["vc"], bt, cu, start, out, 0, S, max(seg_rows), n_head, n_head, hd, ps,
+                              c["scale"], 0)
+        if first is None:
+            first = out
+            assert (out.double().cpu() - c["ref"]).abs().max().item() < 1.5e-2 * max(1.0, c["ref"].abs().max().item())
+        else:
+            assert torch.equal(out, first)
+    assert ops.tcgen05_error_flag("cuda").item() == 0
+
+
 def test_prefill_attention_tcgen05_two_blocks_per_sm(ops):
     """Its shared memory, registers and tensor memory are sized so that an SM holds two blocks: one block's
     softmax runs while the other's products do."""
