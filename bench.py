@@ -199,16 +199,20 @@ def main() -> int:
         del loop
         return batch * steps / (ms / 1e3), ms / steps, per_step
 
-    def prefill_once(T):
-        """Median milliseconds of one T-token prompt run as ONE step (3 warm-ups, 5 timed)."""
+    def prefill_once(T, portion=None):
+        """Median milliseconds of one T-token prompt run as ONE step, or in steps of ``portion`` tokens
+        (3 warm-ups, 5 timed)."""
         toks = prompts(1, T)[0]
+        portion = portion or T
         times = []
         for it in range(3 + 5):
             slot = eng.open_request(1000 + it)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            eng.forward_step([StepEntry(slot, 0, toks, [T - 1])])
+            for at in range(0, T, portion):
+                part = toks[at:at + portion]
+                eng.forward_step([StepEntry(slot, at, part, [len(part) - 1] if at + portion >= T else [])])
             e1.record()
             torch.cuda.synchronize()
             if it >= 3:
@@ -257,6 +261,8 @@ def main() -> int:
         result["prefill"] = {"value": round(T / (ms / 1e3), 1), "tokens": T, "ms": round(ms, 3),
                              "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                              "flops": int(flops), "peak_tflops": pk["bf16_tflops"], "of": pk["source"]}
+        ms512 = prefill_once(T, 512)     # the same prompt in four steps of 512 tokens, as a scheduler would cut it
+        result["prefill"]["in_portions_of_512"] = {"value": round(T / (ms512 / 1e3), 1), "ms": round(ms512, 3)}
         # ---- decode at batch 1 and 64 -----------------------------------------------------------
         pts = {}
         for b in (1, 64):
@@ -320,6 +326,7 @@ def mixed_workload(args, cb, torch) -> int:
         "value": round((n_prompt + n_gen) / wall, 1), "unit": "tokens/s", "n_gpus": 1, "impl": "b200", "dtype": "bf16",
         "decode_tokens_per_s": round(n_gen / wall, 1), "wall_s": round(wall, 3), "steps": eng.steps - steps0,
         "prompt_tokens": n_prompt, "output_tokens": n_gen, "preemptions": eng.scheduler.preemptions(),
+        "graph_replays": eng.runner.graph_replays, "step_shapes_captured": eng.runner.shape_captures,
         "higher_is_better": True, "data": "synthetic (random weights, uniform random token ids)",
         "config": {"model": "GPT-2 XL shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"], "n_layer_config": 48,
                    "n_embd": 1600, "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,

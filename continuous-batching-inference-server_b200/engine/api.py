@@ -162,6 +162,7 @@ class Engine:
 
     def close_request(self, slot: int) -> None:
         self.pool.manager.release(slot)
+        ops.raise_if_kernel_errors(self.runner.device)    # waits for the queued steps: nothing bad goes unreported
 
     @torch.no_grad()
     def forward_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -179,8 +180,9 @@ class Engine:
         out = self.runner.step(entries)
         if any(len(e.tokens) > 1 for e in entries):
             # a step with prompt portions may have run kernels whose waits are bounded (TMA + tcgen05): a wait that
-            # ran out left wrong logits, and says so through a flag on the device
-            ops.raise_if_kernel_errors(out.device)
+            # ran out left wrong logits, and says so through a flag on the device (read without stalling the host:
+            # a bad step is reported at one of the next calls, or when the request is closed)
+            ops.poll_kernel_errors(out.device)
         return out
 
     @torch.no_grad()

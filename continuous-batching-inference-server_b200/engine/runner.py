@@ -10,6 +10,8 @@ table per REQUEST and token slots; only wanted rows reach the head; logits stay 
 """
 from __future__ import annotations
 
+import os
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -108,6 +110,16 @@ class ModelRunner:
                               for layer in model.layers for _, part in layer.parts()) \
             and getattr(model.position, "capturable", True) and getattr(model.final_norm, "capturable", True)
         self._graphs: Dict[int, tuple] = {}      # rows of a decode-only step -> (graph, context, logits)
+        # Steps with prompt portions: a step's SHAPE (tokens and wanted rows per entry, in order) fixes every launch
+        # of it; what differs between two steps of one shape (tokens, positions, block tables, wanted rows) is in
+        # the packed buffer on the device.  A shape seen for the eighth time is captured (that costs about 60 ms) and
+        # replayed from then on: a 512-token portion then costs the host 0.1 ms instead of 3 (250 launches from Python).
+        self.shape_graphs = os.environ.get("CBIS_SHAPE_GRAPHS", "1") != "0"
+        self.max_shape_graphs = 24
+        self.shape_graph_after = int(os.environ.get("CBIS_SHAPE_GRAPH_AFTER", "8"))
+        self._shape_seen: Dict[tuple, int] = {}
+        self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self.shape_captures = self.shape_replays = 0
         worst = heads = 0
         for layer in model.layers:
             m = layer.mixer
@@ -168,7 +180,7 @@ class ModelRunner:
         self._pack(entries, 0, False, reserved_ahead)
 
     def build_context(self, entries, pad_rows: int = 0, all_logits: bool = False,
-                      reserved_ahead: bool = False) -> StepContext:
+                      reserved_ahead: bool = False, fixed_shapes: bool = False) -> StepContext:
         """Packs the step into the host buffer, copies it over, returns the views.
 
         ``pad_rows`` > 0 (decode-only steps): the step is laid out for exactly that many rows and
@@ -179,7 +191,7 @@ class ModelRunner:
         T, S, R = info.n_rows, info.n_segments, info.n_logit_rows
         ctx = StepContext()
         ctx.dtype, ctx.pool, ctx.error_flag = self.model.dtype, pool, self.error_flag
-        ctx.runner, ctx.max_positions, ctx.fixed_shapes = self, self.model.spec.max_positions, bool(pad_rows)
+        ctx.runner, ctx.max_positions, ctx.fixed_shapes = self, self.model.spec.max_positions, bool(pad_rows) or fixed_shapes
         ctx.n_rows, ctx.n_segments, ctx.n_logit_rows, ctx.n_decode = T, S, R, info.n_decode
         ctx.tokens, ctx.positions, ctx.row_seq = (self._dev_view(n, T) for n in ("tokens", "positions", "row_seq"))
         ctx.seg_slot, ctx.seg_start, ctx.seg_ctx = (self._dev_view(n, S) for n in ("seg_slot", "seg_start", "seg_ctx"))
@@ -214,8 +226,45 @@ class ModelRunner:
         if self.use_graphs and decode_only:
             out = self._decode_step_graph(entries, native)
             return out if borrow else out.clone()
+        if self.use_graphs and self.shape_graphs and entries:
+            out = self._shape_step_graph(entries, native)
+            if out is not None:
+                return out if borrow else out.clone()
         ctx = self.build_context(entries)
         return self.model.forward(ctx)
+
+    def _shape_step_graph(self, entries, native: bool):
+        """Replays the graph of this step's shape, captures it if the shape has been seen often enough, or returns
+        None (the caller then runs the step launch by launch)."""
+        if native:
+            shape = tuple((e.n_tokens, 1 if e.sample else 0) for e in entries)
+        else:
+            shape = tuple((len(e.tokens), len(e.want)) for e in entries)
+        have = self._shape_graphs.get(shape)
+        if have is not None:
+            self._shape_graphs.move_to_end(shape)
+            self._pack(entries, 0, False, False)
+            graph, logits = have
+            graph.replay()
+            self.graph_replays += 1
+            self.shape_replays += 1
+            return logits
+        seen = self._shape_seen.get(shape, 0) + 1
+        if len(self._shape_seen) > 4096:
+            self._shape_seen.clear()
+        self._shape_seen[shape] = seen
+        if seen < self.shape_graph_after:                # capturing costs as much as twenty runs: not for a passing shape
+            return None
+        ctx = self.build_context(entries, fixed_shapes=True)
+        self.model.forward(ctx)                           # warm-up outside the capture (writes the same cache values)
+        graph, logits = capture_graph(lambda: self.model.forward(ctx))
+        while len(self._shape_graphs) >= self.max_shape_graphs:
+            self._shape_graphs.popitem(last=False)        # the shape not used for the longest time makes room
+        self._shape_graphs[shape] = (graph, logits)
+        self.shape_captures += 1
+        graph.replay()
+        self.graph_replays += 1
+        return logits
 
     def _decode_step_graph(self, entries, native: bool) -> torch.Tensor:
         rows = self._bucket(len(entries))
@@ -223,11 +272,7 @@ class ModelRunner:
         if have is None:
             ctx = self.build_context(entries, pad_rows=rows, all_logits=True)
             self.model.forward(ctx)                       # warm-up outside the capture (writes the same cache values)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx)
-            have = self._graphs[rows] = (graph, logits)
+            have = self._graphs[rows] = capture_graph(lambda: self.model.forward(ctx))
         else:
             self._pack(entries, rows, True, False)        # the captured kernels read the same buffer: no views needed
         graph, logits = have
@@ -242,6 +287,24 @@ class ModelRunner:
     def decode_loop(self, entries: Sequence[StepEntry]) -> "DecodeLoop":
         """A run of greedy decode steps that never leaves the device: see ``DecodeLoop``."""
         return DecodeLoop(self, entries)
+
+
+def capture_graph(fn):
+    """Captures the launches of ``fn()`` into a CUDA graph on a side stream; returns (graph, what fn returned).
+    ``torch.cuda.graph`` does the same but first collects garbage and empties the allocator's cache, which costs
+    up to seconds when much memory is cached: too much for a capture in the middle of serving."""
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph.capture_begin()
+        try:
+            out = fn()
+        finally:
+            graph.capture_end()
+    torch.cuda.current_stream().wait_stream(side)
+    return graph, out
 
 
 class DecodeLoop:
@@ -259,10 +322,7 @@ class DecodeLoop:
         self.ctx = ctx
         self.sampled = torch.zeros(n, dtype=torch.int32, device=runner.device)
         self._one_step()                                  # warm-up, also moves the rows on by one
-        torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self._one_step()
+        self.graph, _ = capture_graph(self._one_step)
         self.steps_done = 1
 
     def _one_step(self):

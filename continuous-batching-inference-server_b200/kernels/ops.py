@@ -61,7 +61,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return c_void_p(t.data_ptr()) if t is not None else None
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
+    """The current stream of the current device as a raw handle.  torch.cuda.current_stream() builds a Python
+    object through several layers (about 5 us, a third of the host's share of a launch); the two calls below are
+    what it ends in."""
+    if _raw_stream is not None and _raw_device is not None:
+        return c_void_p(_raw_stream(_raw_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -189,6 +198,35 @@ def raise_if_kernel_errors(device="cuda") -> None:
             raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
                               f"product, 11-19 the prefill attention); the step's results are invalid")
 
+
+
+_tc_pending = {}     # device index -> (pinned copy of the flag, event recorded after the copy)
+
+
+def poll_kernel_errors(device="cuda") -> None:
+    """The same check without making the host wait: looks at the copy of the flag that the call before this one
+    asked for (if that copy has been made by now) and asks for a new one behind the work queued so far.  A step
+    whose wait ran out is therefore reported one or two calls late, but steps keep overlapping with the host."""
+    key = torch.device(device).index or 0
+    flag = _tc_error.get(key)
+    if flag is None:
+        return
+    pending = _tc_pending.get(key)
+    if pending is not None:
+        host, event = pending
+        if not event.query():
+            return                      # the copy asked for earlier has not run yet: ask again next time
+        code = int(host[0])
+        if code:
+            _tc_pending.pop(key, None)
+            flag.zero_()
+            raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
+                              f"product, 11-19 the prefill attention); the results of a recent step are invalid")
+    else:
+        host, event = torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event()
+    host.copy_(flag, non_blocking=True)
+    event.record()
+    _tc_pending[key] = (host, event)
 
 
 def tcgen05_error_flag(device) -> torch.Tensor:

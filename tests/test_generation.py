@@ -140,3 +140,28 @@ def test_command_line(folder_a, tmp_path):
     outs = [json.loads(l)["tokens"] for l in r.stdout.splitlines() if l.startswith("{")]
     cfg, w = plain_gpt.read_model_folder(folder_a, torch.float64)
     assert outs == [plain_gpt.generate(cfg, w, p, 6) for p in prompts]
+
+
+def test_repeated_step_shapes_replay_a_graph_and_give_the_same_logits(tiny):
+    """A step shape that keeps coming back (here: portions of 6 tokens of one request, then of another) is captured
+    as a CUDA graph and replayed; the logits are those of the launch-by-launch path."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    folder, cfgd, page = tiny
+    toks = [(7 * i + 3) % cfgd["vocab_size"] for i in range(60)]
+
+    def run(after):
+        eng = cb.Engine(folder, dtype="bfloat16", page_size=page, num_pages=64, max_num_seqs=2, max_batched_tokens=64)
+        eng.runner.shape_graph_after = after
+        outs = []
+        for req in range(2):
+            slot = eng.open_request(req)
+            for at in range(0, 60, 6):
+                outs.append(eng.forward_step([StepEntry(slot, at, toks[at:at + 6], [0, 5])]).float().cpu())
+            eng.close_request(slot)
+        return torch.cat(outs), eng.runner.shape_captures, eng.runner.shape_replays
+
+    eager, c0, r0 = run(10 ** 9)
+    graphed, c1, r1 = run(3)
+    assert (c0, r0) == (0, 0) and c1 == 1 and r1 == 17       # 20 steps of one shape: 2 launch by launch, 1 captured, 17 replayed
+    assert torch.equal(eager, graphed)
