@@ -132,8 +132,13 @@ class Engine:
                                 dtype=torch.int64).to(logits.device)
             ops.sample(logits, temps, keys, out)
         tokens = out.cpu().tolist()
-        if self.last_step_tokens > R:                    # a step with prompt portions may have run the tcgen05 product
-            ops.raise_if_kernel_errors(logits.device)    # (the host has just waited for the step anyway)
+        # kernels with bounded waits report through one flag on the device: read after every step with prompt
+        # portions (several such kernels) and every 64th decode step (the few-rows tcgen05 product); the host has
+        # just waited for the step anyway
+        self._unchecked = getattr(self, "_unchecked", 0) + 1
+        if self.last_step_tokens > R or self._unchecked >= 64:
+            self._unchecked = 0
+            ops.raise_if_kernel_errors(logits.device)
         return tokens
 
     def generate(self, prompts: Sequence[Sequence[int]],

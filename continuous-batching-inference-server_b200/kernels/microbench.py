@@ -75,7 +75,13 @@ def main():
         mb = a.n * a.k * 2 / 1e6
         t = timed(fn, not a.no_graph, a.reps) / L
         tl = timed(lib, not a.no_graph, a.reps) / L
-        print(f"gemm M={M} N={a.n} K={a.k}: {mb:.1f} MB  own {t:.2f} us ({mb / t:.2f} TB/s)  library {tl:.2f} us ({mb / tl:.2f} TB/s)")
+
+        def few():
+            for l in range(L):
+                ops.gemm_few_rows(x, W[l], bias, None, out, a.splits)
+        tf = timed(few, not a.no_graph, a.reps) / L
+        print(f"gemm M={M} N={a.n} K={a.k}: {mb:.1f} MB  mma.sync {t:.2f} us ({mb / t:.2f} TB/s)  tcgen05 swapped {tf:.2f} us "
+              f"({mb / tf:.2f} TB/s)  library {tl:.2f} us ({mb / tl:.2f} TB/s)  flag {ops.tcgen05_error_flag(dev).item()}")
     elif a.op == "gemm_tc":
         x = torch.randn(M, a.k, device=dev, dtype=torch.bfloat16)
         W = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(min(L, 4))]

@@ -183,8 +183,28 @@ def gemm_small_m(x, w_nk, bias, act, out):
     _check(st, "gemm_small_m", f"M={M} N={N} K={K}")
 
 
+def gemm_few_rows(x, w_nk, bias, act, out, ksplit=0):
+    """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16 on the tcgen05 tensor cores with the operands
+    swapped: the weights stream through shared memory by TMA, K split over the blocks of a cluster
+    (``ksplit`` 0: the launcher's choice)."""
+    _need_cuda(x, w_nk, bias, out)
+    M, K = x.shape
+    N = w_nk.shape[0]
+    assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
+    ref = _next_weight.get(w_nk.data_ptr())
+    nxt = ref() if ref is not None else None
+    st = kernels().cbis_gemm_few_rows_tc5(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
+                                          c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
+                                          c_int(dtype_code(out.dtype)), c_int(ksplit), _ptr(nxt),
+                                          ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0),
+                                          _ptr(tcgen05_error_flag(x.device)), _stream())
+    _check(st, "gemm_few_rows", f"M={M} N={N} K={K} ksplit={ksplit}")
+
+
 _tc_error = {}
 USE_TCGEN05 = __import__("os").environ.get("CBIS_TCGEN05", "1") != "0"
+USE_FEW_ROWS = USE_TCGEN05 and __import__("os").environ.get("CBIS_FEW_ROWS", "1") != "0"
 
 
 def raise_if_kernel_errors(device="cuda") -> None:
@@ -255,9 +275,10 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
     """act(x @ W^T + bias) with W stored [N, K] (K contiguous).
 
     32-bit inputs: this package's FFMA kernel (no reduced-precision matrix mode).  bfloat16
-    inputs: up to 16 rows go to the weight-streaming tensor-core kernel; more rows with a bias or an
-    activation go to the TMA + tcgen05 kernel; both apply bias and activation to the 32-bit sums
-    and round once.  More rows without an epilogue go to the library GEMM."""
+    inputs: up to 16 rows go to the weight-streaming mma.sync kernel; a head over a vocabulary at
+    17..64 rows goes to the TMA + tcgen05 kernel with swapped operands; more rows with a bias or an
+    activation go to the TMA + tcgen05 kernel; all apply bias and activation to the 32-bit sums and
+    round once.  More rows without an epilogue go to the library GEMM."""
     M, K = x.shape
     N = w_nk.shape[0]
     if x.dtype == torch.float32:
@@ -266,11 +287,22 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
         return out
     _need_cuda(x, w_nk)
     out_dtype = out_dtype or x.dtype
-    if M <= SMALL_M and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0:
+    aligned = K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+    if M <= SMALL_M and aligned:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_small_m(x, w_nk, bias, act, out)
         return out
     plain = bias is None and not ACT[act]
+    if USE_FEW_ROWS and M <= 64 and aligned and plain and (N % 8 != 0 or N >= 32768):
+        # a head over a vocabulary at 17..64 rows: the library product is slow when N is no multiple of 8 (212 us at
+        # 64 rows of 50,257 x 2,048), the TMA + tcgen05 kernel with swapped operands streams it at 4.9 TB/s (42 us).
+        # (Up to 16 rows, and inside a layer, the mma.sync kernel stays: the tcgen05 one is as fast alone and keeps
+        # more bytes in flight on large matrices, 5.8 TB/s on 134 MB against 4.4, but its blocks need 90 KB of
+        # shared memory each and cannot start beside the blocks of the kernel before them: in the chain of a
+        # decode step that costs more than it wins, 1.75 ms per step against 1.29.)
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        gemm_few_rows(x, w_nk, bias, act, out)
+        return out
     if out_dtype != torch.float32 and plain:
         return torch.mm(x, w_nk.t())
     enough_tiles = -(-M // 128) * -(-N // 256) >= 96       # its 128x256 tiles must cover most of the 148 SMs

@@ -418,6 +418,25 @@ def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal(ops):
     assert (out.double().cpu() - p @ v.double()).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("M,N,K,ksplit", [(1, 48, 64, 1), (5, 4800, 1600, 0), (8, 8192, 2048, 0), (8, 6144, 2048, 4),
+                                          (16, 2048, 8192, 8), (3, 1000, 520, 2), (8, 2048, 2048, 0), (33, 777, 264, 1),
+                                          (64, 4096, 1024, 2), (20, 50257, 256, 0)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_few_rows_tcgen05(ops, M, N, K, ksplit, out_dtype):
+    """The few-rows product with swapped operands (weights by TMA, tcgen05, K split over a cluster): sizes that are
+    no multiple of its tiles, every cluster size, against the product in 64-bit."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+    ops.gemm_few_rows(dev(x), dev(w), dev(b), "gelu_erf", out, ksplit)
+    ref = plain_gpt.gelu(x.double() @ w.double().t() + b.double(), "gelu")
+    tol = 1e-5 * math.sqrt(K) if out_dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, ref.abs().max().item())
+    assert ops.tcgen05_error_flag("cuda").item() == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 136), (1000, 512, 2048), (77, 5001, 96), (2048, 768, 320),
                                    (257, 520, 72), (2304, 8200, 128)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
