@@ -1,4 +1,5 @@
-// Prefill attention over the paged cache on the 5th-generation tensor cores (bfloat16, head size 128).
+// Prefill attention over the paged cache on the 5th-generation tensor cores (bfloat16, head size 64 or 128; the
+// numbers below are for 128).
 //
 // A block takes 128 consecutive rows of one (segment, head).  Keys and values come in tiles of 64 keys,
 // page by page through the block table, with TMA (cp.async.bulk.tensor, 128-byte swizzle): one warp brings
@@ -34,14 +35,13 @@
 namespace cbis {
 namespace tc5 {
 
-constexpr int BM = 128, BN = 64, HD = 128;
-constexpr int Q_HALF_BYTES = BM * 128;         // 128 rows of 128 bytes: 64 of the 128 head dims
-constexpr int Q_BYTES = 2 * Q_HALF_BYTES;
-constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 of the 128 head dims
-constexpr int KV_BYTES = 2 * KV_HALF_BYTES;    // a tile of keys, or of values
+constexpr int BM = 128, BN = 64;
+constexpr int Q_HALF_BYTES = BM * 128;         // 128 rows of 128 bytes: 64 head dims
+constexpr int KV_HALF_BYTES = BN * 128;        // 64 keys of 128 bytes: 64 head dims
 constexpr int P_BYTES = BM * 128;              // 128 rows of 64 keys
 constexpr int STAGES = 2;
-constexpr int SMEM_BYTES = Q_BYTES + (1 + STAGES) * KV_BYTES + 2 * P_BYTES + 128;   // Q, keys (one stage), values, P (two buffers), barriers
+// Q, keys (one stage), values (STAGES), P (two buffers), barriers; HD: the head size, 64 or 128
+constexpr int smem_bytes(int HD) { return (HD / 64) * (Q_HALF_BYTES + (1 + STAGES) * KV_HALF_BYTES) + 2 * P_BYTES + 128; }
 constexpr float RAISE_BY = 8.f;                // the reference is raised when a tile's maximum exceeds it by 2^8
 constexpr int THREADS = 224;                   // warp 0: Q and keys, warp 1: MMA + tensor memory, warps 2..5: softmax, warp 6: values
 constexpr unsigned SPIN_LIMIT = 1u << 21;      // tries of up to 1 us each
@@ -160,11 +160,13 @@ __device__ __forceinline__ void tmem_st32(unsigned taddr, const float* v) {
 // blocks of a cluster share a row tile, the first takes the first half of its key tiles and the second the rest,
 // and at the end the second hands its sum, reference and output to the first through distributed shared memory.
 // The row tile with the most keys decides how long the kernel runs, and its chain of tiles is halved this way.
+template <int HD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 2)
 paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const int* block_table, int max_blocks,
                          const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_seg,
                          int n_head, int n_kv_head, int ps, float scale_log2e, int window, int* error) {
+  constexpr int HALVES = HD / 64, Q_BYTES = HALVES * Q_HALF_BYTES, KV_BYTES = HALVES * KV_HALF_BYTES;
   extern __shared__ __align__(1024) unsigned char base[];   // no byte to spare for rounding the address up: checked below
   unsigned char* sQ = base;                                   // 2 halves of the head dim
   unsigned char* sK = sQ + Q_BYTES;                           // one tile: Q K^T runs two tiles ahead, so the next keys have time
@@ -251,8 +253,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 0 && lane == 0) {
       bar_expect(q_full, Q_BYTES);
       const int qrow = r_begin + tile * BM;
-      tma_2d(sQ, &map_q, h * HD, qrow, q_full);
-      tma_2d(sQ + Q_HALF_BYTES, &map_q, h * HD + 64, qrow, q_full);
+#pragma unroll
+      for (int hh = 0; hh < HALVES; ++hh) tma_2d(sQ + hh * Q_HALF_BYTES, &map_q, h * HD + hh * 64, qrow, q_full);
     }
     const int piece = min(ps, BN), pieces_per_tile = BN / piece, piece_shift = 31 - __clz(piece);
     // copies tile j's keys (kv = 0) or values (kv = 1) into their stage; false when the block has given up
@@ -271,15 +273,15 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           atomicExch(error, 11);
         }
         stop = *abort_flag;
-        if (!stop) bar_expect(full, (unsigned)n_valid * piece * 128u * 2u);
+        if (!stop) bar_expect(full, (unsigned)n_valid * piece * 128u * HALVES);
       }
       stop = __shfl_sync(0xffffffffu, stop, 0);
       if (stop) return false;
       if (mine) {
         const int grow = (page * n_kv_head + hk) * ps + j0 % ps;   // row of the run's first key in the [rows, HD] view
         unsigned char* d = (kv ? sV : sK) + s * KV_BYTES + p0 * 128;
-        tma_2d(d, kv ? &map_v : &map_k, 0, grow, full);
-        tma_2d(d + KV_HALF_BYTES, kv ? &map_v : &map_k, 64, grow, full);
+#pragma unroll
+        for (int hh = 0; hh < HALVES; ++hh) tma_2d(d + hh * KV_HALF_BYTES, kv ? &map_v : &map_k, hh * 64, grow, full);
       }
       __syncwarp();
       return true;
@@ -418,7 +420,7 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           *reinterpret_cast<uint4*>(vrow + c * 16) = make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(vrow + KV_HALF_BYTES + c * 16) = make_uint4(0, 0, 0, 0);
+          if (HALVES > 1) *reinterpret_cast<uint4*>(vrow + KV_HALF_BYTES + c * 16) = make_uint4(0, 0, 0, 0);
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P must be visible to the tensor cores' reads
@@ -537,15 +539,15 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols,
 
 using namespace cbis;
 
-// q: [total_rows, q_ld] bfloat16 with head h in columns h*128..; kc/vc: [num_pages, n_kv_head, ps, 128].
-// Takes head size 128 and page sizes 8, 16, 32, 64, 128; refuses anything else.
+// q: [total_rows, q_ld] bfloat16 with head h in columns h*hd..; kc/vc: [num_pages, n_kv_head, ps, hd].
+// Takes head sizes 64 and 128 and page sizes 8, 16, 32, 64, 128; refuses anything else.
 CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, const void* kc, const void* vc,
                                        int num_pages, const int* block_table, int max_blocks, const int* cu_rows,
                                        const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
                                        int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
                                        int window, int* error, void* stream) {
   if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
-  if (hd != 128 || ps < 8 || ps > 128 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
+  if ((hd != 128 && hd != 64) || ps < 8 || ps > 128 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
     return CBIS_ERR_BAD_SIZE;
   if (q_ld % 8 || out_ld % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
       ((uintptr_t)out & 15) || error == nullptr)
@@ -558,8 +560,8 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   if (st != CBIS_OK) return st;
   st = tc5::make_map(&map_v, vc, cache_rows, hd, hd, ps < tc5::BN ? ps : tc5::BN);
   if (st != CBIS_OK) return st;
-  const size_t smem = tc5::SMEM_BYTES;
-  auto kern = tc5::paged_prefill_tc5_kernel;
+  const size_t smem = tc5::smem_bytes(hd);
+  auto kern = hd == 128 ? tc5::paged_prefill_tc5_kernel<128> : tc5::paged_prefill_tc5_kernel<64>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
@@ -573,12 +575,12 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
 
 // How many blocks of the kernel above an SM holds at a time (it is sized for two); negative: a CUDA error.
 CBIS_EXPORT int cbis_paged_prefill_tc5_blocks_per_sm() {
-  auto kern = tc5::paged_prefill_tc5_kernel;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc5::SMEM_BYTES);
+  auto kern = tc5::paged_prefill_tc5_kernel<128>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc5::smem_bytes(128));
   if (e != cudaSuccess) return -(int)e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return -(int)e;
   int n = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tc5::THREADS, tc5::SMEM_BYTES);
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tc5::THREADS, tc5::smem_bytes(128));
   return e == cudaSuccess ? n : -(int)e;
 }

@@ -7,8 +7,8 @@ keep the same contract: the query at position p sees the keys of its own request
 
 * bfloat16, head size a multiple of 8, decoding rows: the split-KV decode kernel, which also
   stores the current token's key and value;
-* bfloat16, head size 128, page size a power of two, longer segments: the TMA + tcgen05 kernel,
-  after the cache-write kernel; head size 64: the tiled mma.sync kernel;
+* bfloat16, head size 64 or 128, page size a power of two, longer segments: the TMA + tcgen05 kernel,
+  after the cache-write kernel (with CBIS_TCGEN05=0: the tiled mma.sync kernel);
 * everything else: the general kernel, after the cache-write kernel.
 """
 from __future__ import annotations
@@ -40,7 +40,7 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
         if mixer.own_kv:
             ops.kv_write(qkv[r], k_off, v_off, cache.k, cache.v, view.slot_mapping[r], mixer.n_kv_head, hd, ps)
         tiled = qkv.dtype == torch.bfloat16 and ps & (ps - 1) == 0 and first_general == nd
-        if tiled and hd == 128 and 8 <= ps <= 128 and ops.USE_TCGEN05:
+        if tiled and hd in (64, 128) and 8 <= ps <= 128 and ops.USE_TCGEN05:
             # TMA + tcgen05: q and out keep their full row numbering, the kernel finds its rows through cu_rows
             ops.paged_prefill_tc5(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                   ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,

@@ -410,10 +410,10 @@ def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out
 def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
                       n_head, n_kv_head, head_dim, page_size, scale, window=0):
     """The same attention as ``paged_prefill_bf16`` on the tcgen05 tensor cores (TMA operands, S and the output in
-    tensor memory).  Head size 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering."""
+    tensor memory).  Head size 64 or 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering."""
     _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
-    if head_dim != 128:
-        raise KernelError(f"tcgen05 prefill attention: head_dim={head_dim} is not 128")
+    if head_dim not in (64, 128):
+        raise KernelError(f"tcgen05 prefill attention: head_dim={head_dim} is neither 64 nor 128")
     if page_size & (page_size - 1) or not 8 <= page_size <= 128:
         raise KernelError(f"tcgen05 prefill attention: page_size={page_size} is not a power of two in 8..128")
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16

@@ -457,10 +457,10 @@ def test_gemm_tcgen05(ops, M, N, K, out_dtype):
 
 @pytest.mark.parametrize("n_head,n_kv_head,ps,window", [(2, 2, 16, 0), (4, 2, 16, 0), (3, 1, 64, 0), (2, 2, 8, 0),
                                                         (2, 2, 16, 100), (1, 1, 32, 37), (2, 1, 128, 0)])
-def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window):
-    """The TMA + tcgen05 form (head size 128): the same cases as the mma.sync form, in a cache whose unused
+@pytest.mark.parametrize("hd", [128, 64])
+def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window, hd):
+    """The TMA + tcgen05 form (head sizes 128 and 64): the same cases as the mma.sync form, in a cache whose unused
     slots hold NaN (what an earlier owner of a page may have left must not reach another request)."""
-    hd = 128
     seg_ctx, seg_rows = [200, 333, 64, 70, 1, 130, 600], [200, 77, 64, 3, 1, 65, 257]
     c = paged_case(ops, torch.bfloat16, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed=ps + window)
     S = len(seg_ctx)
