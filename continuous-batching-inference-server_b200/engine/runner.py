@@ -105,6 +105,7 @@ class ModelRunner:
         self._dev = torch.zeros(off, dtype=torch.int32, device=self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = None    # event after the last host->device copy of the packed buffer
+        self._stream_obj = None
         # decode-only steps replay a captured CUDA graph unless a part reads device values on the host
         self.use_graphs = all(getattr(part, "capturable", True)
                               for layer in model.layers for _, part in layer.parts()) \
@@ -171,8 +172,16 @@ class ModelRunner:
         self._dev.copy_(self._host, non_blocking=True)
         if self._copied is None:
             self._copied = torch.cuda.Event()
-        self._copied.record()
+        self._copied.record(self._current_stream())
         return info
+
+    def _current_stream(self):
+        """torch.cuda.current_stream() costs 5 us of Python layers; the stream object is kept and only looked up
+        again when the raw handle of the current stream differs from it."""
+        raw = ops.raw_stream_handle()
+        if self._stream_obj is None or raw is None or self._stream_obj.cuda_stream != raw:
+            self._stream_obj = torch.cuda.current_stream()
+        return self._stream_obj
 
     def validate(self, entries: Sequence[StepEntry], reserved_ahead: bool = False) -> None:
         """Raises StepError if the step does not fit the cache's state or the engine's limits (it is packed

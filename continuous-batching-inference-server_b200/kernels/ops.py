@@ -74,6 +74,13 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def raw_stream_handle():
+    """The current stream's raw handle (an int), or None where torch does not offer the fast call."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
+    return None
+
+
 def _need_cuda(*ts):
     for t in ts:
         if t is not None and not t.is_cuda:
