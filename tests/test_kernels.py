@@ -438,7 +438,7 @@ def test_gemm_few_rows_tcgen05(ops, M, N, K, ksplit, out_dtype):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 136), (1000, 512, 2048), (77, 5001, 96), (2048, 768, 320),
-                                   (257, 520, 72), (2304, 8200, 128)])
+                                   (257, 520, 72), (2304, 8200, 128), (300, 40, 64), (129, 17, 8), (4096, 264, 40)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gemm_tcgen05(ops, M, N, K, out_dtype):
     """The TMA + tcgen05 product with its fused epilogue: sizes that are no multiple of its tiles (128x256x64 on
