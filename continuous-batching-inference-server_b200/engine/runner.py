@@ -11,6 +11,7 @@ table per REQUEST and token slots; only wanted rows reach the head; logits stay 
 from __future__ import annotations
 
 import os
+import time
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
@@ -118,6 +119,7 @@ class ModelRunner:
         self.shape_graphs = os.environ.get("CBIS_SHAPE_GRAPHS", "1") != "0"
         self.max_shape_graphs = 24
         self.shape_graph_after = int(os.environ.get("CBIS_SHAPE_GRAPH_AFTER", "8"))
+        self.shape_graph_min_host_s = 1e-3
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.shape_captures = self.shape_replays = 0
@@ -235,20 +237,32 @@ class ModelRunner:
         if self.use_graphs and decode_only:
             out = self._decode_step_graph(entries, native)
             return out if borrow else out.clone()
+        shape = None
         if self.use_graphs and self.shape_graphs and entries:
-            out = self._shape_step_graph(entries, native)
+            shape = self._step_shape(entries, native)
+            out = self._shape_step_graph(entries, shape)
             if out is not None:
                 return out if borrow else out.clone()
         ctx = self.build_context(entries)
-        return self.model.forward(ctx)
+        t0 = time.perf_counter()
+        out = self.model.forward(ctx)
+        if shape is not None:      # what issuing this shape's launches costs the host: decides whether a graph pays
+            seen = self._shape_seen.get(shape)
+            if seen is not None:
+                seen[1] = time.perf_counter() - t0
+        return out
 
-    def _shape_step_graph(self, entries, native: bool):
-        """Replays the graph of this step's shape, captures it if the shape has been seen often enough, or returns
-        None (the caller then runs the step launch by launch)."""
+    @staticmethod
+    def _step_shape(entries, native: bool) -> tuple:
         if native:
-            shape = tuple((e.n_tokens, 1 if e.sample else 0) for e in entries)
-        else:
-            shape = tuple((len(e.tokens), len(e.want)) for e in entries)
+            return tuple((e.n_tokens, 1 if e.sample else 0) for e in entries)
+        return tuple((len(e.tokens), len(e.want)) for e in entries)
+
+    def _shape_step_graph(self, entries, shape: tuple):
+        """Replays the graph of this step's shape, captures it if the shape has come often enough and issuing its
+        launches one by one costs the host a millisecond or more (a capture stalls the engine for tens of
+        milliseconds: for a small model that is a hundred steps, and its steps cost the host little anyway), or
+        returns None (the caller then runs the step launch by launch)."""
         have = self._shape_graphs.get(shape)
         if have is not None:
             self._shape_graphs.move_to_end(shape)
@@ -258,11 +272,11 @@ class ModelRunner:
             self.graph_replays += 1
             self.shape_replays += 1
             return logits
-        seen = self._shape_seen.get(shape, 0) + 1
         if len(self._shape_seen) > 4096:
             self._shape_seen.clear()
-        self._shape_seen[shape] = seen
-        if seen < self.shape_graph_after:                # capturing costs as much as twenty runs: not for a passing shape
+        seen = self._shape_seen.setdefault(shape, [0, 0.0])      # [times seen, host seconds of the last launch-by-launch run]
+        seen[0] += 1
+        if seen[0] < self.shape_graph_after or seen[1] < self.shape_graph_min_host_s:
             return None
         ctx = self.build_context(entries, fixed_shapes=True)
         self.model.forward(ctx)                           # warm-up outside the capture (writes the same cache values)

@@ -152,7 +152,7 @@ def test_repeated_step_shapes_replay_a_graph_and_give_the_same_logits(tiny):
 
     def run(after):
         eng = cb.Engine(folder, dtype="bfloat16", page_size=page, num_pages=64, max_num_seqs=2, max_batched_tokens=64)
-        eng.runner.shape_graph_after = after
+        eng.runner.shape_graph_after, eng.runner.shape_graph_min_host_s = after, 0.0
         outs = []
         for req in range(2):
             slot = eng.open_request(req)
