@@ -59,8 +59,11 @@ __global__ void kv_write_vec_kernel(const TT* qkv, int ld, int k_off, int v_off,
 // One warp per (row, query head).  The query at position p sees keys max(0, p-window+1)..p
 // (window 0: all keys 0..p; the loop bound is the causal mask, kernels/attention.cu:67-68,78).
 // Online softmax with running max m, normaliser l and accumulator acc as in
-// kernels/attention.cu:74-95, four keys at a time.  Lane i owns head dims i, i+32, ...
-template <typename TT, int NPER>
+// kernels/attention.cu:74-95, G keys at a time (the loads of a group are all in flight together: with four
+// a short context was one round trip to memory per four keys, 36 us for 36 keys).  Lane i owns head dims
+// i, i+32, ...  A group starts at kstart + a multiple of G, whatever the step brought: the logits do not depend
+// on how a request was cut.
+template <typename TT, int NPER, int G>
 __global__ void paged_attention_generic_kernel(
     const TT* q, int q_ld, const TT* kc, const TT* vc,
     const int* block_table, int max_blocks, const int* row_seq,
@@ -92,11 +95,11 @@ __global__ void paged_attention_generic_kernel(
   }
   float m = -INFINITY, l = 0.f;
 
-  for (int j0 = kstart; j0 < kend; j0 += 4) {
-    float s[4];
-    const TT* vptr[4];
+  for (int j0 = kstart; j0 < kend; j0 += G) {
+    float s[G];
+    const TT* vptr[G];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < G; ++u) {
       const int j = j0 + u;
       float part = 0.f;
       vptr[u] = nullptr;
@@ -114,13 +117,15 @@ __global__ void paged_attention_generic_kernel(
       s[u] = part;
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) s[u] = (j0 + u < kend) ? warp_sum(s[u]) * scale : -INFINITY;
-    const float m_new = fmaxf(fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3])), m);
+    for (int u = 0; u < G; ++u) s[u] = (j0 + u < kend) ? warp_sum(s[u]) * scale : -INFINITY;
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < G; ++u) m_new = fmaxf(m_new, s[u]);
     const float corr = expf(m - m_new);  // first group: exp(-inf) = 0
-    float p[4];
+    float p[G];
     float psum = 0.f;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < G; ++u) {
       p[u] = (j0 + u < kend) ? expf(s[u] - m_new) : 0.f;
       psum += p[u];
     }
@@ -131,7 +136,7 @@ __global__ void paged_attention_generic_kernel(
       float a = acc[i] * corr;
       if (dim < hd) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < G; ++u)
           if (vptr[u]) a = fmaf(p[u], to_f32(vptr[u][dim]), a);
       }
       acc[i] = a;
@@ -186,7 +191,7 @@ static int launch_generic(const void* q, int q_ld, const void* kc, const void* v
   const int blocks = (int)((total + warps - 1) / warps);
   cudaError_t e;
 #define CBIS_LAUNCH(NPER)                                                                                            \
-  e = launch_pdl(paged_attention_generic_kernel<TT, NPER>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
+  e = launch_pdl(paged_attention_generic_kernel<TT, NPER, (NPER <= 2 ? 16 : (NPER <= 4 ? 8 : 4))>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
                  (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, out_ld, n_rows, \
                  n_head, n_kv_head, hd, ps, scale, window)
   if (hd <= 32) CBIS_LAUNCH(1);
