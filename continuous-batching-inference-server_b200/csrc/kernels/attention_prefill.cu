@@ -32,6 +32,10 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+__device__ __forceinline__ void ldmatrix_x2(uint32_t* r, const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(s));
+}
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -139,11 +143,16 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
     for (int nt = 0; nt < PF_BN / 8; ++nt) {
       s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < KS; ks += 2) {
+      for (int ks = 0; ks + 1 < KS; ks += 2) {
         uint32_t b[4];
         ldmatrix_x4(b, tk + (size_t)(nt * 8 + (lane & 7)) * PITCH + ks * 16 + (lane >> 3) * 8);
         mma_pf(s[nt], qf[ks], b[0], b[1]);
         mma_pf(s[nt], qf[ks + 1], b[2], b[3]);
+      }
+      if constexpr (KS & 1) {   // a head size that is an odd multiple of 16: the last 16 dims on their own
+        uint32_t b[2];
+        ldmatrix_x2(b, tk + (size_t)(nt * 8 + (lane & 7)) * PITCH + (KS - 1) * 16 + ((lane >> 3) & 1) * 8);
+        mma_pf(s[nt], qf[KS - 1], b[0], b[1]);
       }
     }
     // scale (into the base-2 domain), mask, running max
@@ -225,14 +234,14 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
 using namespace cbis;
 
 // Attention of the segments seg0 .. seg0+n_seg-1 of a step (each a run of rows, cu_rows) over their pages.
-// Takes head sizes 64 and 128 and page sizes that are powers of two; refuses anything else.
+// Takes head sizes 16, 32, ... 128 and page sizes that are powers of two; refuses anything else.
 CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc, const void* vc,
                                         const int* block_table, int max_blocks, const int* cu_rows,
                                         const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
                                         int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
                                         int window, void* stream) {
   if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
-  if ((hd != 64 && hd != 128) || ps <= 0 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
+  if (hd < 16 || hd > 128 || hd % 16 || ps <= 0 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
     return CBIS_ERR_BAD_SIZE;
   if (q_ld % 8 || out_ld % 2 || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)out & 3))
     return CBIS_ERR_ALIGNMENT;
@@ -242,20 +251,20 @@ CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc,
   const float scale_log2e = scale * 1.4426950408889634f;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  if (hd == 128) {
-    auto kern = paged_prefill_bf16_kernel<128>;
-    const size_t smem = (size_t)4 * PF_BN * (128 + 8) * sizeof(__nv_bfloat16);
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(kern, grid, dim3(PF_WARPS * 32), smem, st, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc,
-                   (const __nv_bfloat16*)vc, block_table, max_blocks, cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0,
-                   n_head, n_kv_head, ps_shift, scale_log2e, window);
-  } else {
-    auto kern = paged_prefill_bf16_kernel<64>;
-    const size_t smem = (size_t)4 * PF_BN * (64 + 8) * sizeof(__nv_bfloat16);
-    e = launch_pdl(kern, grid, dim3(PF_WARPS * 32), smem, st, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc,
-                   (const __nv_bfloat16*)vc, block_table, max_blocks, cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0,
-                   n_head, n_kv_head, ps_shift, scale_log2e, window);
+  e = cudaErrorInvalidValue;
+#define CBIS_PF(HD_)                                                                                                  \
+  if (hd == HD_) {                                                                                                    \
+    auto kern = paged_prefill_bf16_kernel<HD_>;                                                                       \
+    const size_t smem = (size_t)4 * PF_BN * (HD_ + 8) * sizeof(__nv_bfloat16);                                        \
+    if (smem > 48 * 1024) {                                                                                           \
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                         \
+      if (e != cudaSuccess) return (int)e;                                                                            \
+    }                                                                                                                 \
+    e = launch_pdl(kern, grid, dim3(PF_WARPS * 32), smem, st, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, \
+                   (const __nv_bfloat16*)vc, block_table, max_blocks, cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, \
+                   n_head, n_kv_head, ps_shift, scale_log2e, window);                                                 \
   }
+  CBIS_PF(16) CBIS_PF(32) CBIS_PF(48) CBIS_PF(64) CBIS_PF(80) CBIS_PF(96) CBIS_PF(112) CBIS_PF(128)
+#undef CBIS_PF
   return (int)e;
 }

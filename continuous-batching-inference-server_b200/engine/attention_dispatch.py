@@ -8,7 +8,8 @@ keep the same contract: the query at position p sees the keys of its own request
 * bfloat16, head size a multiple of 8, decoding rows: the split-KV decode kernel, which also
   stores the current token's key and value;
 * bfloat16, head size 64 or 128, page size a power of two, longer segments: the TMA + tcgen05 kernel,
-  after the cache-write kernel (with CBIS_TCGEN05=0: the tiled mma.sync kernel);
+  after the cache-write kernel; other head sizes in steps of 16 up to 128 (and these two with
+  CBIS_TCGEN05=0): the tiled mma.sync kernel;
 * everything else: the general kernel, after the cache-write kernel.
 """
 from __future__ import annotations
@@ -46,7 +47,7 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
                                   ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                   mixer.scale, mixer.window)
             return
-        if tiled and hd in (64, 128):
+        if tiled and hd % 16 == 0 and 16 <= hd <= 128:
             ops.paged_prefill_bf16(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                    ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                    mixer.scale, mixer.window)

@@ -398,10 +398,10 @@ def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq,
 def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
                        n_head, n_kv_head, head_dim, page_size, scale, window=0):
     """Attention of the segments seg0..seg0+n_seg-1 (runs of rows given by ``cu_rows``, first positions
-    ``seg_start``) over their pages, on the tensor cores.  Head sizes 64 and 128, page sizes 2^k."""
+    ``seg_start``) over their pages, on the tensor cores.  Head sizes 16, 32, ... 128, page sizes 2^k."""
     _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
-    if head_dim not in (64, 128):
-        raise KernelError(f"prefill attention: head_dim={head_dim} is not 64 or 128 (the general kernel takes it)")
+    if head_dim % 16 or not 16 <= head_dim <= 128:
+        raise KernelError(f"prefill attention: head_dim={head_dim} is no multiple of 16 up to 128 (the general kernel takes it)")
     if page_size & (page_size - 1):
         raise KernelError(f"prefill attention: page_size={page_size} is not a power of two (the general kernel takes it)")
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16

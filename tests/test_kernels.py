@@ -371,7 +371,9 @@ def test_bias_act_out_rounds_once(ops):
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [(2, 2, 128, 16, 0), (4, 2, 64, 16, 0), (3, 1, 128, 64, 0),
-                                                           (2, 2, 64, 8, 0), (2, 2, 128, 16, 100), (1, 1, 64, 32, 37)])
+                                                           (2, 2, 64, 8, 0), (2, 2, 128, 16, 100), (1, 1, 64, 32, 37),
+                                                           (8, 8, 32, 16, 0), (2, 1, 16, 8, 0), (3, 3, 48, 16, 21),
+                                                           (2, 2, 80, 16, 0), (2, 1, 96, 32, 0), (1, 1, 112, 16, 0)])
 def test_prefill_attention_tensor_cores(ops, n_head, n_kv_head, hd, ps, window):
     """Segments of 1..200 rows at the end of contexts of up to 333 keys: first portions, later portions,
     rows that are not a multiple of the 64-row tile, contexts that end inside a page and inside a key tile."""
