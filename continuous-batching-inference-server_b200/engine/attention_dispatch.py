@@ -10,6 +10,8 @@ keep the same contract: the query at position p sees the keys of its own request
 * bfloat16, head size 64 or 128, page size a power of two, longer segments: the TMA + tcgen05 kernel,
   after the cache-write kernel; other head sizes in steps of 16 up to 128 (and these two with
   CBIS_TCGEN05=0): the tiled mma.sync kernel;
+* 32-bit, head size in steps of 16 up to 128, longer segments: the tiled 32-bit kernel (decoding rows: the general
+  kernel);
 * everything else: the general kernel, after the cache-write kernel.
 """
 from __future__ import annotations
@@ -51,6 +53,23 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
             ops.paged_prefill_bf16(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                    ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                    mixer.scale, mixer.window)
+            return
+        if qkv.dtype == torch.float32 and hd % 16 == 0 and 16 <= hd <= 128 and ops.USE_TILED_F32:
+            # 32-bit: decoding rows through the general kernel, the longer segments 64 rows to a block
+            if nd > 0:
+                d = slice(0, nd)
+                ops.paged_attention_generic(qkv[d, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[d],
+                                            ctx.positions[d], out[d], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
+                                            mixer.window)
+            if ctx.n_segments > nd:
+                limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+                chunks = ops.prefill_f32_chunks(-(-ctx.max_seg_rows // 64), mixer.n_head, ctx.n_segments - nd, limit)
+                partial = None
+                if chunks[0] > 1:
+                    partial, _ = ctx.decode_scratch((T - nd) * mixer.n_head * chunks[0] * (hd + 4), 1)
+                ops.paged_prefill_f32(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
+                                      ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
+                                      mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
         ops.paged_attention_generic(qkv[r, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[r],
                                     ctx.positions[r], out[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,

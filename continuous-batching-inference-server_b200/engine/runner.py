@@ -152,9 +152,13 @@ class ModelRunner:
         if n_floats > self._scratch.numel() or n_counters > self._counters.numel():
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("kernel scratch would have to grow during graph capture")
+            # captured graphs keep the addresses they were recorded with: what is outgrown stays allocated
+            self._outgrown = getattr(self, "_outgrown", [])
             if n_floats > self._scratch.numel():
-                self._scratch = torch.empty(n_floats, dtype=torch.float32, device=self.device)
+                self._outgrown.append(self._scratch)
+                self._scratch = torch.empty(n_floats + n_floats // 2, dtype=torch.float32, device=self.device)
             if n_counters > self._counters.numel():
+                self._outgrown.append(self._counters)
                 self._counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
         return self._scratch, self._counters
 

@@ -211,6 +211,7 @@ def gemm_few_rows(x, w_nk, bias, act, out, ksplit=0):
 
 _tc_error = {}
 USE_TCGEN05 = __import__("os").environ.get("CBIS_TCGEN05", "1") != "0"
+USE_TILED_F32 = __import__("os").environ.get("CBIS_TILED_F32", "1") != "0"   # 0: the general kernel for 32-bit prompts
 USE_FEW_ROWS = USE_TCGEN05 and __import__("os").environ.get("CBIS_FEW_ROWS", "1") != "0"
 
 
@@ -412,6 +413,47 @@ def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out
         c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim), c_int(page_size), c_float(scale),
         c_int(window), _stream())
     _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+
+
+def prefill_f32_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int):
+    """(n_chunks, chunk_keys) for the 32-bit prefill attention: no cut (1, 0) when (row tile, head, segment) alone
+    give four blocks to each of the 148 SMs; else chunks of a power of two of keys, at least 256, that do."""
+    base = max(1, row_tiles * n_head * n_seg)
+    want = -(-4 * 148 // base)
+    if want <= 1 or max_context <= 256:
+        return 1, 0
+    chunk = 256
+    while chunk * want < max_context:
+        chunk *= 2
+    n = -(-max_context // chunk)
+    return (n, chunk) if n > 1 else (1, 0)
+
+
+def paged_prefill_f32(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
+                      n_head, n_kv_head, head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None,
+                      positions=None, row0=0, n_rows=0):
+    """The same attention as ``paged_prefill_bf16`` in true 32-bit (no tensor cores): a block takes 64 rows of one
+    head and brings keys and values through shared memory once.  Head sizes 16, 32, ... 128, any page size;
+    ``q`` and ``out`` in full row numbering.  ``chunks`` = (n, keys) from ``prefill_f32_chunks`` cuts the keys n
+    ways (every context of the step below n * keys); ``partial`` then holds ``n_rows * n_head * n * (head_dim + 4)``
+    floats, ``positions`` the position of every row, ``row0`` and ``n_rows`` name the rows of these segments."""
+    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, partial, positions)
+    if head_dim % 16 or not 16 <= head_dim <= 128:
+        raise KernelError(f"32-bit prefill attention: head_dim={head_dim} is no multiple of 16 up to 128 (the general kernel takes it)")
+    assert q.dtype == torch.float32 and k_cache.dtype == torch.float32 and out.dtype == torch.float32
+    assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous() and k_cache.is_contiguous()
+    n_chunks, chunk_keys = chunks
+    if n_chunks > 1:
+        assert partial.dtype == torch.float32 and partial.numel() >= n_rows * n_head * n_chunks * (head_dim + 4)
+        assert positions.dtype == torch.int32 and positions.numel() >= row0 + n_rows
+    st = kernels().cbis_paged_prefill_f32(
+        _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(cu_rows), _ptr(seg_start), _ptr(out), c_int(out.stride(0)), c_int(seg0), c_int(n_seg),
+        c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim), c_int(page_size), c_float(scale),
+        c_int(window), c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _ptr(positions), c_int(row0), c_int(n_rows),
+        _stream())
+    _check(st, "paged_prefill_f32", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size} "
+                                    f"chunks={n_chunks}x{chunk_keys}")
 
 
 def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,

@@ -395,6 +395,61 @@ def test_prefill_attention_tensor_cores(ops, n_head, n_kv_head, hd, ps, window):
     assert torch.isnan(out2[:r2].float()).all() and torch.equal(out2[r2:], out[r2:])
 
 
+@pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [(2, 2, 128, 16, 0), (4, 2, 64, 16, 0), (3, 1, 32, 64, 0),
+                                                           (8, 8, 32, 16, 0), (2, 1, 16, 3, 0), (3, 3, 48, 16, 21),
+                                                           (2, 2, 80, 5, 100), (2, 1, 96, 32, 0), (1, 1, 112, 16, 37)])
+def test_prefill_attention_32_bit_tiled(ops, n_head, n_kv_head, hd, ps, window):
+    """The 32-bit tiled form (64 rows to a block, keys through shared memory in tiles of 32): the cases of the
+    tensor-core form, page sizes that are no power of two, in a cache whose unused slots hold NaN; it agrees with
+    the general kernel (one warp per row) to 32-bit rounding."""
+    seg_ctx, seg_rows = [200, 333, 64, 70, 1, 130, 600], [200, 77, 64, 3, 1, 65, 257]
+    c = paged_case(ops, torch.float32, n_head, n_kv_head, hd, ps, window, seg_ctx, seg_rows, seed=hd + ps + window)
+    S = len(seg_ctx)
+    cu = torch.tensor([0] + list(np.cumsum(seg_rows)), dtype=torch.int32)
+    start = torch.tensor([cx - n for cx, n in zip(seg_ctx, seg_rows)], dtype=torch.int32)
+    out = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_f32(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out, 0, S, max(seg_rows),
+                          n_head, n_kv_head, hd, ps, c["scale"], window)
+    bound = 2e-6 * max(1.0, c["ref"].abs().max().item())
+    assert (out.double().cpu() - c["ref"]).abs().max().item() < bound
+    general = torch.empty_like(out)
+    ops.paged_attention_generic(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(c["row_seq"]), dev(c["positions"]),
+                                general, n_head, n_kv_head, hd, ps, c["scale"], window)
+    assert (out - general).abs().max().item() < bound
+    # the keys cut into chunks (by absolute index) and merged by the second kernel: the same to rounding
+    T = len(c["positions"])
+    for n_chunks, chunk_keys in [(3, 256), (10, 64), (20, 32)]:
+        partial = torch.full((T * n_head * n_chunks * (hd + 4),), float("nan"), device="cuda")
+        cut = torch.full_like(c["q"], float("nan")).cuda()
+        ops.paged_prefill_f32(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), cut, 0, S, max(seg_rows),
+                              n_head, n_kv_head, hd, ps, c["scale"], window, (n_chunks, chunk_keys), partial,
+                              dev(c["positions"]), 0, T)
+        assert (cut - out).abs().max().item() < bound, (n_chunks, chunk_keys)
+    r2 = int(cu[2])
+    partial = torch.full(((T - r2) * n_head * 5 * (hd + 4),), float("nan"), device="cuda")
+    cut = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_f32(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), cut, 2, S - 2, max(seg_rows[2:]),
+                          n_head, n_kv_head, hd, ps, c["scale"], window, (5, 128), partial, dev(c["positions"]), r2, T - r2)
+    assert torch.isnan(cut[:r2]).all() and (cut[r2:] - out[r2:]).abs().max().item() < bound
+    # only the segments from the third on: the rows before stay untouched
+    out2 = torch.full_like(c["q"], float("nan")).cuda()
+    ops.paged_prefill_f32(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 2, S - 2, max(seg_rows[2:]),
+                          n_head, n_kv_head, hd, ps, c["scale"], window)
+    assert torch.isnan(out2[:r2]).all() and torch.equal(out2[r2:], out[r2:])
+    with pytest.raises(ops.KernelError, match="head_dim=24"):
+        ops.paged_prefill_f32(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 0, S, max(seg_rows),
+                              n_head, n_kv_head, 24, ps, c["scale"], window)
+
+
+def test_prefill_32_bit_chunks_fill_the_gpu_and_cover_the_context(ops):
+    assert ops.prefill_f32_chunks(40, 16, 1, 2048) == (1, 0)              # enough blocks without a cut
+    assert ops.prefill_f32_chunks(1, 2, 1, 200) == (1, 0)                 # too short to cut
+    for tiles, heads, segs, limit in [(8, 8, 1, 32768), (1, 1, 1, 5000), (2, 3, 2, 257), (8, 8, 1, 700)]:
+        n, keys = ops.prefill_f32_chunks(tiles, heads, segs, limit)
+        assert n > 1 and keys % 32 == 0 and keys >= 256 and keys & (keys - 1) == 0
+        assert (n - 1) * keys < limit <= n * keys
+
+
 def test_prefill_attention_finds_a_far_key_and_respects_the_diagonal(ops):
     hd, ps, T = 128, 16, 300
     g = torch.Generator().manual_seed(4)
