@@ -6,8 +6,7 @@
 //
 // Cache of one layer: K and V each [num_pages][n_kv_head][page_size][head_dim]; the
 // reference keeps [page][page_size][head][head_dim] (kernels/attention.cu:14,80).
-#include "common.cuh"
-#include <math.h>
+#include "attention_merge.cuh"
 
 namespace cbis {
 
@@ -68,23 +67,30 @@ __global__ void paged_attention_generic_kernel(
     const TT* q, int q_ld, const TT* kc, const TT* vc,
     const int* block_table, int max_blocks, const int* row_seq,
     const int* positions, TT* __restrict__ out, int out_ld, int n_rows, int n_head, int n_kv_head,
-    int hd, int ps, float scale, int window) {
+    int hd, int ps, float scale, int window, int n_chunks, int chunk_keys, float* partial) {
   pdl_trigger();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= n_rows * n_head) return;
+  const int wc = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wc >= n_rows * n_head * n_chunks) return;
+  const int w = wc / n_chunks, chunk = wc % n_chunks;
   const int row = w / n_head, h = w % n_head;
   const int hk = h / (n_head / n_kv_head);
   const int pos = positions[row];
   const int seq = row_seq[row];
   if (seq < 0) {  // a padding row of a fixed-size batch
-    for (int dim = lane; dim < hd; dim += 32) from_f32(out[(size_t)row * out_ld + h * hd + dim], 0.f);
+    if (chunk == 0)
+      for (int dim = lane; dim < hd; dim += 32) from_f32(out[(size_t)row * out_ld + h * hd + dim], 0.f);
     return;
   }
   const int* bt = block_table + (size_t)seq * max_blocks;
-  const int kend = pos + 1;
-  const int kstart = window > 0 ? max(0, kend - window) : 0;
+  int kend = pos + 1;
+  int kstart = window > 0 ? max(0, kend - window) : 0;
+  if (n_chunks > 1) {   // this warp's share of the keys: chunks by absolute index, merged by a second kernel
+    kstart = max(kstart, chunk * chunk_keys);
+    kend = min(kend, (chunk + 1) * chunk_keys);
+    if (kstart >= kend) return;
+  }
 
   float qv[NPER], acc[NPER];
 #pragma unroll
@@ -143,6 +149,19 @@ __global__ void paged_attention_generic_kernel(
     }
     m = m_new;
   }
+  if (n_chunks > 1) {
+    float* dst = partial + ((size_t)w * n_chunks + chunk) * (hd + 4);
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) {
+      const int dim = lane + 32 * i;
+      if (dim < hd) dst[dim] = acc[i];
+    }
+    if (lane == 0) {
+      dst[hd] = m;
+      dst[hd + 1] = l;
+    }
+    return;
+  }
   const float inv = 1.f / l;
 #pragma unroll
   for (int i = 0; i < NPER; ++i) {
@@ -185,36 +204,45 @@ template <typename TT>
 static int launch_generic(const void* q, int q_ld, const void* kc, const void* vc, const int* block_table,
                           int max_blocks, const int* row_seq, const int* positions, void* out, int out_ld,
                           int n_rows, int n_head, int n_kv_head, int hd, int ps, float scale, int window,
-                          cudaStream_t st) {
+                          int n_chunks, int chunk_keys, float* partial, cudaStream_t st) {
   const int warps = 4;
-  const long long total = (long long)n_rows * n_head;
+  const long long total = (long long)n_rows * n_head * n_chunks;
   const int blocks = (int)((total + warps - 1) / warps);
   cudaError_t e;
 #define CBIS_LAUNCH(NPER)                                                                                            \
   e = launch_pdl(paged_attention_generic_kernel<TT, NPER, (NPER <= 2 ? 16 : (NPER <= 4 ? 8 : 4))>, dim3(blocks), dim3(warps * 32), 0, st, (const TT*)q, q_ld, \
                  (const TT*)kc, (const TT*)vc, block_table, max_blocks, row_seq, positions, (TT*)out, out_ld, n_rows, \
-                 n_head, n_kv_head, hd, ps, scale, window)
+                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial)
   if (hd <= 32) CBIS_LAUNCH(1);
   else if (hd <= 64) CBIS_LAUNCH(2);
   else if (hd <= 128) CBIS_LAUNCH(4);
   else CBIS_LAUNCH(8);
 #undef CBIS_LAUNCH
+  if (e == cudaSuccess && n_chunks > 1)
+    e = launch_pdl(prefill_merge_kernel<TT, false>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, row_seq,
+                   (TT*)out, out_ld, 0, n_head, hd, window, n_chunks, chunk_keys);
   return (int)e;
 }
 
+// With n_chunks > 1 (head sizes that are a multiple of 4, 16-byte aligned rows of out) every (row, head) is cut into
+// chunks of chunk_keys keys over as many warps: partial holds n_rows * n_head * n_chunks * (hd + 4) floats and a
+// second kernel merges the chunks.
 CBIS_EXPORT int cbis_paged_attention_generic(const void* q, int q_ld, const void* kc, const void* vc,
                                              const int* block_table, int max_blocks, const int* row_seq,
                                              const int* positions, void* out, int out_ld, int n_rows, int n_head,
                                              int n_kv_head, int hd, int ps, float scale, int window, int dtype,
-                                             void* stream) {
+                                             int n_chunks, int chunk_keys, float* partial, void* stream) {
   if (n_rows <= 0) return CBIS_OK;
   if (hd <= 0 || hd > 256 || ps <= 0 || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head) return CBIS_ERR_BAD_SIZE;
+  if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || !partial || hd % 4 || out_ld % 4 || ((uintptr_t)partial & 15) ||
+                                        ((uintptr_t)out & 15))))
+    return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == CBIS_F32)
     return launch_generic<float>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld, n_rows,
-                                 n_head, n_kv_head, hd, ps, scale, window, st);
+                                 n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, st);
   if (dtype == CBIS_BF16)
     return launch_generic<__nv_bfloat16>(q, q_ld, kc, vc, block_table, max_blocks, row_seq, positions, out, out_ld,
-                                         n_rows, n_head, n_kv_head, hd, ps, scale, window, st);
+                                         n_rows, n_head, n_kv_head, hd, ps, scale, window, n_chunks, chunk_keys, partial, st);
   return CBIS_ERR_BAD_DTYPE;
 }

@@ -9,7 +9,7 @@
 // tiles in flight); Q*K^T and P*V run on the tensor cores (mma.sync m16n8k16, bf16 in, 32-bit
 // accumulate; ldmatrix from rows padded by 16 bytes), and the softmax is the online form with
 // running max and sum per row in 32-bit, P rounded to bf16 only as the operand of P*V.
-#include "common.cuh"
+#include "attention_merge.cuh"
 #include <math.h>
 
 namespace cbis {
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3)
 paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
                           const int* block_table, int max_blocks, const int* cu_rows, const int* seg_start,
                           __nv_bfloat16* out, int out_ld, int seg0, int n_head, int n_kv_head, int ps_shift,
-                          float scale_log2e, int window) {
+                          float scale_log2e, int window, int n_chunks, int chunk_keys, float* partial, int row0) {
   constexpr int PITCH = HD + 8;  // elements per shared-memory row: 16 bytes of padding keep ldmatrix conflict-free
   constexpr int KS = HD / 16;    // k-steps of Q*K^T
   constexpr int DT = HD / 8;     // 8-wide column tiles of the output
@@ -71,7 +71,8 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   pdl_trigger();
   pdl_wait();
   // late row tiles have the most keys to walk: they are given out first, the short ones fill the end
-  const int seg = seg0 + blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+  const int seg = seg0 + blockIdx.z, h = blockIdx.y;
+  const int chunk = blockIdx.x % n_chunks, tile = gridDim.x / n_chunks - 1 - blockIdx.x / n_chunks;
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * PF_BM >= n_rows) return;
   const int hk = h / (n_head / n_kv_head);
@@ -80,8 +81,13 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   const int g = lane >> 2, t = lane & 3;
   const int pos0 = seg_start[seg] + tile * PF_BM;           // position of the tile's first row
   const int rows_here = min(PF_BM, n_rows - tile * PF_BM);
-  const int kend = pos0 + rows_here;                        // keys 0 .. kend-1 can matter to this tile
-  const int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int kend = pos0 + rows_here;                              // keys 0 .. kend-1 can matter to this tile
+  int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  if (n_chunks > 1) {   // this block's share of the keys (chunks by absolute index, whole key tiles)
+    kbegin = max(kbegin, chunk * chunk_keys);
+    kend = min(kend, (chunk + 1) * chunk_keys);
+    if (kbegin >= kend) return;
+  }
   const int* bt = block_table + (size_t)seg * max_blocks;
 
   // this thread's two rows: g and g + 8 of the warp's 16
@@ -219,6 +225,18 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (n_chunks > 1) {   // unnormalised sums, maximum (base-2 domain) and denominator for the merge kernel
+    float* d0 = partial + (((size_t)(r_begin + tile * PF_BM + lr0 - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
+    float* d1 = partial + (((size_t)(r_begin + tile * PF_BM + lr1 - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+      if (lr0 < rows_here) *reinterpret_cast<float2*>(d0 + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
+      if (lr1 < rows_here) *reinterpret_cast<float2*>(d1 + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
+    }
+    if (t == 0 && lr0 < rows_here) *reinterpret_cast<float2*>(d0 + HD) = make_float2(m0, l0);
+    if (t == 0 && lr1 < rows_here) *reinterpret_cast<float2*>(d1 + HD) = make_float2(m1, l1);
+    return;
+  }
   const float i0 = 1.f / l0, i1 = 1.f / l1;
   __nv_bfloat16* o0 = out + (size_t)(r_begin + tile * PF_BM + lr0) * out_ld + h * HD;
   __nv_bfloat16* o1 = out + (size_t)(r_begin + tile * PF_BM + lr1) * out_ld + h * HD;
@@ -234,20 +252,27 @@ paged_prefill_bf16_kernel(const __nv_bfloat16* q, int q_ld, const __nv_bfloat16*
 using namespace cbis;
 
 // Attention of the segments seg0 .. seg0+n_seg-1 of a step (each a run of rows, cu_rows) over their pages.
-// Takes head sizes 16, 32, ... 128 and page sizes that are powers of two; refuses anything else.
+// Takes head sizes 16, 32, ... 128 and page sizes that are powers of two; refuses anything else.  With
+// n_chunks > 1 the keys are cut into chunks of chunk_keys (a multiple of 64) over more blocks: partial then holds
+// n_rows * n_head * n_chunks * (hd + 4) floats for the rows row0 .. row0+n_rows-1 (those of the segments),
+// positions the position of every row of the step, and a second kernel merges the chunks of these rows.
 CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc, const void* vc,
                                         const int* block_table, int max_blocks, const int* cu_rows,
                                         const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
                                         int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
-                                        int window, void* stream) {
+                                        int window, int n_chunks, int chunk_keys, float* partial, const int* positions,
+                                        int row0, int n_rows, void* stream) {
   if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
+  if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || chunk_keys % PF_BN || !partial || !positions || n_rows <= 0 ||
+                                        ((uintptr_t)partial & 15) || out_ld % 4 || ((uintptr_t)out & 7))))
+    return CBIS_ERR_BAD_SIZE;
   if (hd < 16 || hd > 128 || hd % 16 || ps <= 0 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
     return CBIS_ERR_BAD_SIZE;
   if (q_ld % 8 || out_ld % 2 || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) || ((uintptr_t)out & 3))
     return CBIS_ERR_ALIGNMENT;
   int ps_shift = 0;
   while ((1 << ps_shift) < ps) ++ps_shift;
-  dim3 grid((max_seg_rows + PF_BM - 1) / PF_BM, n_head, n_seg);
+  dim3 grid(((max_seg_rows + PF_BM - 1) / PF_BM) * n_chunks, n_head, n_seg);
   const float scale_log2e = scale * 1.4426950408889634f;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
@@ -262,9 +287,12 @@ CBIS_EXPORT int cbis_paged_prefill_bf16(const void* q, int q_ld, const void* kc,
     }                                                                                                                 \
     e = launch_pdl(kern, grid, dim3(PF_WARPS * 32), smem, st, (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kc, \
                    (const __nv_bfloat16*)vc, block_table, max_blocks, cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, \
-                   n_head, n_kv_head, ps_shift, scale_log2e, window);                                                 \
+                   n_head, n_kv_head, ps_shift, scale_log2e, window, n_chunks, chunk_keys, partial, row0);            \
   }
   CBIS_PF(16) CBIS_PF(32) CBIS_PF(48) CBIS_PF(64) CBIS_PF(80) CBIS_PF(96) CBIS_PF(112) CBIS_PF(128)
 #undef CBIS_PF
+  if (e == cudaSuccess && n_chunks > 1)
+    e = launch_pdl(prefill_merge_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions,
+                   (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window, n_chunks, chunk_keys);
   return (int)e;
 }

@@ -14,8 +14,7 @@
 // key indices, so a key's chunk does not depend on how the prompt was cut), a block takes (row tile, head, chunk)
 // and leaves its unnormalised sum, maximum and denominator in scratch memory, and a second kernel merges the
 // chunks of every row.
-#include "common.cuh"
-#include <math.h>
+#include "attention_merge.cuh"
 
 namespace cbis {
 
@@ -159,39 +158,6 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
     *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
 }
 
-// Merges the chunks of every (row, head): out = sum_c exp(m_c - M) o_c / sum_c exp(m_c - M) l_c over the chunks
-// that hold keys of the row's range.  grid: rows from row0 on; a thread takes 4 head dims of one head at a time.
-__global__ void __launch_bounds__(128)
-prefill_f32_merge_kernel(const float* partial, const int* positions, float* out, int out_ld, int row0, int n_head, int hd,
-                         int window, int n_chunks, int chunk_keys) {
-  pdl_trigger();
-  pdl_wait();
-  const int row = row0 + blockIdx.x;
-  const int p = positions[row];
-  const int c_lo = (window > 0 ? max(0, p - window + 1) : 0) / chunk_keys, c_hi = p / chunk_keys;
-  const int units = n_head * (hd / 4);
-  for (int u = threadIdx.x; u < units; u += blockDim.x) {
-    const int h = u / (hd / 4), d = (u % (hd / 4)) * 4;
-    const float* src = partial + ((size_t)blockIdx.x * n_head + h) * n_chunks * (hd + 4);
-    float mx = -INFINITY;
-    for (int c = c_lo; c <= c_hi; ++c) mx = fmaxf(mx, src[(size_t)c * (hd + 4) + hd]);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float l = 0.f;
-    for (int c = c_lo; c <= c_hi; ++c) {
-      const float* s = src + (size_t)c * (hd + 4);
-      const float w = expf(s[hd] - mx);   // a chunk without a visible key has maximum -inf: weight 0
-      const float4 o = *reinterpret_cast<const float4*>(s + d);
-      acc.x = fmaf(w, o.x, acc.x);
-      acc.y = fmaf(w, o.y, acc.y);
-      acc.z = fmaf(w, o.z, acc.z);
-      acc.w = fmaf(w, o.w, acc.w);
-      l = fmaf(w, s[hd + 1], l);
-    }
-    const float inv = 1.f / l;
-    *reinterpret_cast<float4*>(out + (size_t)row * out_ld + h * hd + d) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-  }
-}
-
 }  // namespace cbis
 
 using namespace cbis;
@@ -230,7 +196,7 @@ CBIS_EXPORT int cbis_paged_prefill_f32(const float* q, int q_ld, const float* kc
   CBIS_PF32(16) CBIS_PF32(32) CBIS_PF32(48) CBIS_PF32(64) CBIS_PF32(80) CBIS_PF32(96) CBIS_PF32(112) CBIS_PF32(128)
 #undef CBIS_PF32
   if (e == cudaSuccess && n_chunks > 1)
-    e = launch_pdl(prefill_f32_merge_kernel, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, out, out_ld, row0,
+    e = launch_pdl(prefill_merge_kernel<float, false>, dim3(n_rows), dim3(128), 0, st, (const float*)partial, positions, (const int*)nullptr, out, out_ld, row0,
                    n_head, hd, window, n_chunks, chunk_keys);
   return (int)e;
 }

@@ -21,6 +21,27 @@ import torch
 from ..kernels import ops
 
 
+def _key_chunks(ctx, mixer, nd, T, hd):
+    """Few rows behind a long context give the tiled kernels too few blocks: the keys are then cut into chunks over
+    more blocks, whose partial results (in the step's scratch memory) a second kernel merges."""
+    limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+    chunks = ops.prefill_key_chunks(-(-ctx.max_seg_rows // 64), mixer.n_head, ctx.n_segments - nd, limit)
+    partial = None
+    if chunks[0] > 1:
+        partial, _ = ctx.decode_scratch((T - nd) * mixer.n_head * chunks[0] * (hd + 4), 1)
+    return chunks, partial
+
+
+def _general_chunks(ctx, mixer, rows, hd):
+    """The general kernel gives a warp to every (row, head): a few rows behind a long context are cut the same way."""
+    limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+    chunks = ops.generic_key_chunks(rows, mixer.n_head, limit, hd)
+    partial = None
+    if chunks[0] > 1:
+        partial, _ = ctx.decode_scratch(rows * mixer.n_head * chunks[0] * (hd + 4), 1)
+    return chunks, partial
+
+
 def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
     nd = ctx.n_decode
     T = ctx.n_rows
@@ -50,27 +71,26 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
                                   mixer.scale, mixer.window)
             return
         if tiled and hd % 16 == 0 and 16 <= hd <= 128:
+            chunks, partial = _key_chunks(ctx, mixer, nd, T, hd)
             ops.paged_prefill_bf16(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                    ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
-                                   mixer.scale, mixer.window)
+                                   mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
         if qkv.dtype == torch.float32 and hd % 16 == 0 and 16 <= hd <= 128 and ops.USE_TILED_F32:
             # 32-bit: decoding rows through the general kernel, the longer segments 64 rows to a block
             if nd > 0:
                 d = slice(0, nd)
+                chunks, partial = _general_chunks(ctx, mixer, nd, hd)
                 ops.paged_attention_generic(qkv[d, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[d],
                                             ctx.positions[d], out[d], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
-                                            mixer.window)
+                                            mixer.window, chunks, partial)
             if ctx.n_segments > nd:
-                limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
-                chunks = ops.prefill_f32_chunks(-(-ctx.max_seg_rows // 64), mixer.n_head, ctx.n_segments - nd, limit)
-                partial = None
-                if chunks[0] > 1:
-                    partial, _ = ctx.decode_scratch((T - nd) * mixer.n_head * chunks[0] * (hd + 4), 1)
+                chunks, partial = _key_chunks(ctx, mixer, nd, T, hd)
                 ops.paged_prefill_f32(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                       ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
                                       mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
+        chunks, partial = _general_chunks(ctx, mixer, T - first_general, hd)
         ops.paged_attention_generic(qkv[r, :mixer.d_q], cache.k, cache.v, view.block_table, ctx.row_seq[r],
                                     ctx.positions[r], out[r], mixer.n_head, mixer.n_kv_head, hd, ps, mixer.scale,
-                                    mixer.window)
+                                    mixer.window, chunks, partial)

@@ -342,10 +342,26 @@ def kv_write(qkv, k_off, v_off, k_cache, v_cache, slot_mapping, n_kv_head, head_
     _check(st, "kv_write", f"T={T} kv_heads={n_kv_head} head_dim={head_dim} page={page_size}")
 
 
+def generic_key_chunks(rows: int, n_head: int, max_context: int, head_dim: int):
+    """(n_chunks, chunk_keys) for the general attention kernel (a warp per row and head): no cut (1, 0) when rows and
+    heads alone give 16 warps to each of the 148 SMs, or the head size is no multiple of 4; else chunks of a power
+    of two of keys, at least 256, that do."""
+    want = -(-16 * 148 // max(1, rows * n_head))
+    if want <= 1 or max_context <= 256 or head_dim % 4:
+        return 1, 0
+    chunk = 256
+    while chunk * want < max_context:
+        chunk *= 2
+    n = -(-max_context // chunk)
+    return (n, chunk) if n > 1 else (1, 0)
+
+
 def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions, out, n_head, n_kv_head,
-                            head_dim, page_size, scale, window=0):
-    """Attention of every row over its request's pages: keys max(0,p-window+1)..p for the query at p."""
-    _need_cuda(q, k_cache, v_cache, block_table, row_seq, positions, out)
+                            head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None):
+    """Attention of every row over its request's pages: keys max(0,p-window+1)..p for the query at p.
+    ``chunks`` = (n, keys) from ``generic_key_chunks`` cuts every row's keys n ways over as many warps (every
+    context below n * keys); ``partial`` then holds ``rows * n_head * n * (head_dim + 4)`` floats."""
+    _need_cuda(q, k_cache, v_cache, block_table, row_seq, positions, out, partial)
     T = q.shape[0]
     if head_dim > 256:
         raise KernelError(f"attention: head_dim={head_dim} is above the kernel's limit of 256")
@@ -353,11 +369,18 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, row_seq, positions
         raise KernelError(f"attention: n_head={n_head} is not a multiple of n_kv_head={n_kv_head}")
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.dtype == torch.int32
     assert block_table.is_contiguous() and row_seq.dtype == torch.int32 and positions.dtype == torch.int32
+    n_chunks, chunk_keys = chunks
+    if n_chunks > 1:
+        assert partial.dtype == torch.float32 and partial.numel() >= T * n_head * n_chunks * (head_dim + 4)
+        if out.stride(0) % 4 or out.data_ptr() % 16:
+            n_chunks, chunk_keys = 1, 0
     st = kernels().cbis_paged_attention_generic(
         _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(row_seq), _ptr(positions), _ptr(out), c_int(out.stride(0)), c_int(T), c_int(n_head), c_int(n_kv_head),
-        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(dtype_code(q.dtype)), _stream())
-    _check(st, "paged_attention_generic", f"T={T} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(dtype_code(q.dtype)),
+        c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _stream())
+    _check(st, "paged_attention_generic", f"T={T} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size} "
+                                          f"chunks={n_chunks}x{chunk_keys}")
 
 
 def decode_splits(rows: int, n_head: int, max_context: int) -> int:
@@ -397,27 +420,38 @@ def paged_decode_bf16(qkv, k_off, v_off, k_cache, v_cache, block_table, row_seq,
 
 
 def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
-                       n_head, n_kv_head, head_dim, page_size, scale, window=0):
+                       n_head, n_kv_head, head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None,
+                       positions=None, row0=0, n_rows=0):
     """Attention of the segments seg0..seg0+n_seg-1 (runs of rows given by ``cu_rows``, first positions
-    ``seg_start``) over their pages, on the tensor cores.  Head sizes 16, 32, ... 128, page sizes 2^k."""
-    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
+    ``seg_start``) over their pages, on the tensor cores.  Head sizes 16, 32, ... 128, page sizes 2^k.
+    ``chunks`` = (n, keys) from ``prefill_key_chunks`` cuts the keys n ways over more blocks (every context of the
+    step below n * keys); ``partial`` then holds ``n_rows * n_head * n * (head_dim + 4)`` floats, ``positions`` the
+    position of every row, ``row0`` and ``n_rows`` name the rows of these segments."""
+    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, partial, positions)
     if head_dim % 16 or not 16 <= head_dim <= 128:
         raise KernelError(f"prefill attention: head_dim={head_dim} is no multiple of 16 up to 128 (the general kernel takes it)")
     if page_size & (page_size - 1):
         raise KernelError(f"prefill attention: page_size={page_size} is not a power of two (the general kernel takes it)")
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous()
+    n_chunks, chunk_keys = chunks
+    if n_chunks > 1:
+        assert partial.dtype == torch.float32 and partial.numel() >= n_rows * n_head * n_chunks * (head_dim + 4)
+        assert positions.dtype == torch.int32 and positions.numel() >= row0 + n_rows
     st = kernels().cbis_paged_prefill_bf16(
         _ptr(q), c_int(q.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(cu_rows), _ptr(seg_start), _ptr(out), c_int(out.stride(0)), c_int(seg0), c_int(n_seg),
         c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head), c_int(head_dim), c_int(page_size), c_float(scale),
-        c_int(window), _stream())
-    _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size}")
+        c_int(window), c_int(n_chunks), c_int(chunk_keys), _ptr(partial), _ptr(positions), c_int(row0), c_int(n_rows),
+        _stream())
+    _check(st, "paged_prefill_bf16", f"segments={n_seg} heads={n_head}/{n_kv_head} head_dim={head_dim} page={page_size} "
+                                     f"chunks={n_chunks}x{chunk_keys}")
 
 
-def prefill_f32_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int):
-    """(n_chunks, chunk_keys) for the 32-bit prefill attention: no cut (1, 0) when (row tile, head, segment) alone
-    give four blocks to each of the 148 SMs; else chunks of a power of two of keys, at least 256, that do."""
+def prefill_key_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int):
+    """(n_chunks, chunk_keys) for the tiled prefill attention kernels (64-row tiles): no cut (1, 0) when (row tile,
+    head, segment) alone give four blocks to each of the 148 SMs; else chunks of a power of two of keys, at least
+    256, that do."""
     base = max(1, row_tiles * n_head * n_seg)
     want = -(-4 * 148 // base)
     if want <= 1 or max_context <= 256:
@@ -429,12 +463,15 @@ def prefill_f32_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int
     return (n, chunk) if n > 1 else (1, 0)
 
 
+prefill_f32_chunks = prefill_key_chunks
+
+
 def paged_prefill_f32(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
                       n_head, n_kv_head, head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None,
                       positions=None, row0=0, n_rows=0):
     """The same attention as ``paged_prefill_bf16`` in true 32-bit (no tensor cores): a block takes 64 rows of one
     head and brings keys and values through shared memory once.  Head sizes 16, 32, ... 128, any page size;
-    ``q`` and ``out`` in full row numbering.  ``chunks`` = (n, keys) from ``prefill_f32_chunks`` cuts the keys n
+    ``q`` and ``out`` in full row numbering.  ``chunks`` = (n, keys) from ``prefill_key_chunks`` cuts the keys n
     ways (every context of the step below n * keys); ``partial`` then holds ``n_rows * n_head * n * (head_dim + 4)``
     floats, ``positions`` the position of every row, ``row0`` and ``n_rows`` name the rows of these segments."""
     _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, partial, positions)

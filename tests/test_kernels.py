@@ -188,6 +188,23 @@ def test_kv_write_and_generic_attention(ops, dtype, n_head, n_kv_head, hd, ps, w
                                 out, n_head, n_kv_head, hd, ps, c["scale"], window)
     tol = 2e-6 if dtype == torch.float32 else 1e-2
     assert (out.double().cpu() - c["ref"]).abs().max() < tol * max(1.0, c["ref"].abs().max().item())
+    if hd % 4 == 0:   # every row's keys cut into chunks over more warps, merged by the second kernel
+        T = len(c["positions"])
+        for n_chunks, chunk_keys in [(2, 128), (9, 16), (33, 4)]:
+            partial = torch.full((T * n_head * n_chunks * (hd + 4),), float("nan"), device="cuda")
+            cut = torch.full_like(c["q"], float("nan")).cuda()
+            ops.paged_attention_generic(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(c["row_seq"]), dev(c["positions"]),
+                                        cut, n_head, n_kv_head, hd, ps, c["scale"], window, (n_chunks, chunk_keys), partial)
+            assert (cut.double().cpu() - c["ref"]).abs().max() < tol * max(1.0, c["ref"].abs().max().item())
+        # a padding row (request -1) is left zero by both kernels
+        seq = c["row_seq"].clone(); seq[0] = -1
+        partial = torch.full((T * n_head * 2 * (hd + 4),), float("nan"), device="cuda")
+        ops.paged_attention_generic(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(seq), dev(c["positions"]),
+                                    cut, n_head, n_kv_head, hd, ps, c["scale"], window, (2, 128), partial)
+        assert cut[0].abs().max().item() == 0 and not torch.isnan(cut.float()).any()
+    assert ops.generic_key_chunks(512, 16, 2048, 128) == (1, 0) and ops.generic_key_chunks(1, 8, 32768, 30) == (1, 0)
+    n, keys = ops.generic_key_chunks(1, 8, 32768, 32)
+    assert n > 1 and (n - 1) * keys < 32768 <= n * keys and keys >= 256
 
 
 def test_attention_refuses_sizes_it_does_not_take(ops):
@@ -393,6 +410,17 @@ def test_prefill_attention_tensor_cores(ops, n_head, n_kv_head, hd, ps, window):
                            n_head, n_kv_head, hd, ps, c["scale"], window)
     r2 = int(cu[2])
     assert torch.isnan(out2[:r2].float()).all() and torch.equal(out2[r2:], out[r2:])
+    # the keys cut into chunks over more blocks and merged by the second kernel: the same to rounding
+    T = len(c["positions"])
+    for n_chunks, chunk_keys, s0 in [(2, 256, 0), (6, 64, 0), (3, 128, 2)]:
+        r0 = int(cu[s0])
+        partial = torch.full(((T - r0) * n_head * n_chunks * (hd + 4),), float("nan"), device="cuda")
+        cut = torch.full_like(c["q"], float("nan")).cuda()
+        ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), cut, s0, S - s0,
+                               max(seg_rows[s0:]), n_head, n_kv_head, hd, ps, c["scale"], window, (n_chunks, chunk_keys),
+                               partial, dev(c["positions"]), r0, T - r0)
+        assert torch.isnan(cut[:r0].float()).all()
+        assert (cut[r0:].float() - out[r0:].float()).abs().max().item() < 1.5e-2 * max(1.0, c["ref"].abs().max().item())
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,hd,ps,window", [(2, 2, 128, 16, 0), (4, 2, 64, 16, 0), (3, 1, 32, 64, 0),
@@ -441,11 +469,11 @@ def test_prefill_attention_32_bit_tiled(ops, n_head, n_kv_head, hd, ps, window):
                               n_head, n_kv_head, 24, ps, c["scale"], window)
 
 
-def test_prefill_32_bit_chunks_fill_the_gpu_and_cover_the_context(ops):
-    assert ops.prefill_f32_chunks(40, 16, 1, 2048) == (1, 0)              # enough blocks without a cut
-    assert ops.prefill_f32_chunks(1, 2, 1, 200) == (1, 0)                 # too short to cut
+def test_prefill_key_chunks_fill_the_gpu_and_cover_the_context(ops):
+    assert ops.prefill_key_chunks(40, 16, 1, 2048) == (1, 0)              # enough blocks without a cut
+    assert ops.prefill_key_chunks(1, 2, 1, 200) == (1, 0)                 # too short to cut
     for tiles, heads, segs, limit in [(8, 8, 1, 32768), (1, 1, 1, 5000), (2, 3, 2, 257), (8, 8, 1, 700)]:
-        n, keys = ops.prefill_f32_chunks(tiles, heads, segs, limit)
+        n, keys = ops.prefill_key_chunks(tiles, heads, segs, limit)
         assert n > 1 and keys % 32 == 0 and keys >= 256 and keys & (keys - 1) == 0
         assert (n - 1) * keys < limit <= n * keys
 
