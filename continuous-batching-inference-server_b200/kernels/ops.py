@@ -152,7 +152,7 @@ def linear_f32(x, w, bias, act, out, w_is_nk=False):
     _check(st, "linear_f32", f"M={M} N={N} K={K}")
 
 
-SMALL_M = 16      # rows up to which the weight-streaming kernel takes a bfloat16 product (it can take 64)
+SMALL_M = int(__import__("os").environ.get("CBIS_SMALL_M", "16"))      # rows up to which the weight-streaming kernel takes a bfloat16 product (it can take 64; measured at batch 32 and 64 of the 1.3B sizes: the library product is 27-33 % faster per step there)
 
 
 _next_weight = {}      # data_ptr of a weight -> weak reference to the weight used after it
