@@ -26,7 +26,7 @@
 //
 // Every wait on an mbarrier is bounded; when a limit runs out the block sets *error, stops, frees its
 // tensor memory and returns (its output rows are then invalid, and the host raises).
-#include "common.cuh"
+#include "attention_merge.cuh"
 
 #include <cuda.h>
 #include <math.h>
@@ -165,7 +165,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 2)
 paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const int* block_table, int max_blocks,
                          const int* cu_rows, const int* seg_start, __nv_bfloat16* out, int out_ld, int seg0, int n_seg,
-                         int n_head, int n_kv_head, int ps, float scale_log2e, int window, int* error) {
+                         int n_head, int n_kv_head, int ps, float scale_log2e, int window, int n_chunks, int chunk_keys,
+                         float* partial, int row0, int* error) {
   constexpr int HALVES = HD / 64, Q_BYTES = HALVES * Q_HALF_BYTES, KV_BYTES = HALVES * KV_HALF_BYTES;
   extern __shared__ __align__(1024) unsigned char base[];   // no byte to spare for rounding the address up: checked below
   unsigned char* sQ = base;                                   // 2 halves of the head dim
@@ -185,8 +186,8 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   // first, and an SM's second block is a light one
   unsigned rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  const int pair = (int)blockIdx.x >> 1;
-  const int per_rank = n_head * n_seg, n_row_tiles = (gridDim.x >> 1) / per_rank;
+  const int chunk = ((int)blockIdx.x >> 1) % n_chunks, pair = ((int)blockIdx.x >> 1) / n_chunks;
+  const int per_rank = n_head * n_seg, n_row_tiles = (int)(gridDim.x >> 1) / n_chunks / per_rank;
   const int tile = n_row_tiles - 1 - pair / per_rank, seg = seg0 + (pair % per_rank) / n_head, h = pair % n_head;
   const int r_begin = cu_rows[seg], n_rows = cu_rows[seg + 1] - r_begin;
   if (tile * BM >= n_rows) return;
@@ -197,8 +198,14 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int hk = h / (n_head / n_kv_head);
   const int pos0 = seg_start[seg] + tile * BM;
   const int rows_here = min(BM, n_rows - tile * BM);
-  const int kend = pos0 + rows_here;
-  const int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int kend = pos0 + rows_here;
+  int kbegin = window > 0 ? max(0, pos0 - window + 1) : 0;
+  if (n_chunks > 1) {   // few rows behind a long context: this cluster takes one chunk of the keys (whole key tiles,
+                        // by absolute index) and leaves an unnormalised partial result for the merge kernel
+    kbegin = max(kbegin, chunk * chunk_keys);
+    kend = min(kend, (chunk + 1) * chunk_keys);
+    if (kbegin >= kend) return;   // both blocks of the cluster alike, before any barrier or allocation
+  }
   const int kt_all = kbegin / BN, n_all = (kend - 1) / BN - kt_all + 1, n_first = (n_all + 1) / 2;
   // this block's key tiles: the first takes n_first of them, the second the rest (none, if there is only one)
   const int kt_first = kt_all + (rank ? n_first : 0), n_tiles = rank ? n_all - n_first : n_first;
@@ -467,10 +474,14 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const float m1 = xml[r], l1 = xml[BM + r];
       const float mm = fmaxf(m, m1);
       const float f0 = m == -INFINITY ? 0.f : exp2f(m - mm), f1 = (m1 == -INFINITY || l1 == 0.f) ? 0.f : exp2f(m1 - mm);
-      const float inv = 1.f / (l * f0 + l1 * f1);
+      // with the keys cut into chunks the sum stays unnormalised (relative to the reference mm): the merge kernel divides
+      const float inv = n_chunks > 1 ? 1.f : 1.f / (l * f0 + l1 * f1);
       const float g0 = f0 * inv, g1 = f1 * inv;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       __nv_bfloat16* dst = out + (size_t)(r_begin + tile * BM + r) * out_ld + h * HD;
+      float* pdst = n_chunks > 1 ? partial + (((size_t)(r_begin + tile * BM + r - row0) * n_head + h) * n_chunks + chunk) * (HD + 4)
+                                 : nullptr;
+      if (pdst && r < rows_here) *reinterpret_cast<float2*>(pdst + HD) = make_float2(mm, l * f0 + l1 * f1);
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
         float o[32];
@@ -480,10 +491,16 @@ paged_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           for (int i = 0; i < 32; i += 4) {
             float4 o1 = make_float4(0.f, 0.f, 0.f, 0.f);
             if (f1 != 0.f) o1 = *reinterpret_cast<const float4*>(xo + (((c0 + i) >> 2) * BM + r) * 4);
-            o[i] = o[i] * g0 + o1.x * g1;
-            o[i + 1] = o[i + 1] * g0 + o1.y * g1;
-            o[i + 2] = o[i + 2] * g0 + o1.z * g1;
-            o[i + 3] = o[i + 3] * g0 + o1.w * g1;
+            o[i] = (f0 != 0.f ? o[i] * g0 : 0.f) + o1.x * g1;
+            o[i + 1] = (f0 != 0.f ? o[i + 1] * g0 : 0.f) + o1.y * g1;
+            o[i + 2] = (f0 != 0.f ? o[i + 2] * g0 : 0.f) + o1.z * g1;
+            o[i + 3] = (f0 != 0.f ? o[i + 3] * g0 : 0.f) + o1.w * g1;
+          }
+          if (pdst) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(pdst + c0 + i) = make_float4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+            continue;
           }
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -540,13 +557,20 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols,
 using namespace cbis;
 
 // q: [total_rows, q_ld] bfloat16 with head h in columns h*hd..; kc/vc: [num_pages, n_kv_head, ps, hd].
+// With n_chunks > 1 the keys are cut into chunks of chunk_keys (a multiple of 64) over as many clusters: partial holds
+// n_rows * n_head * n_chunks * (hd + 4) floats for the rows row0 .. row0+n_rows-1 (those of the segments), positions the
+// position of every row of the step, and a second kernel merges the chunks of these rows.
 // Takes head sizes 64 and 128 and page sizes 8, 16, 32, 64, 128; refuses anything else.
 CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, const void* kc, const void* vc,
                                        int num_pages, const int* block_table, int max_blocks, const int* cu_rows,
                                        const int* seg_start, void* out, int out_ld, int seg0, int n_seg,
                                        int max_seg_rows, int n_head, int n_kv_head, int hd, int ps, float scale,
-                                       int window, int* error, void* stream) {
+                                       int window, int n_chunks, int chunk_keys, float* partial, const int* positions,
+                                       int row0, int n_rows, int* error, void* stream) {
   if (n_seg <= 0 || max_seg_rows <= 0) return CBIS_OK;
+  if (n_chunks < 1 || (n_chunks > 1 && (chunk_keys <= 0 || chunk_keys % tc5::BN || !partial || !positions || n_rows <= 0 ||
+                                        ((uintptr_t)partial & 15))))
+    return CBIS_ERR_BAD_SIZE;
   if ((hd != 128 && hd != 64) || ps < 8 || ps > 128 || (ps & (ps - 1)) || n_head <= 0 || n_kv_head <= 0 || n_head % n_kv_head)
     return CBIS_ERR_BAD_SIZE;
   if (q_ld % 8 || out_ld % 8 || ((uintptr_t)q & 15) || ((uintptr_t)kc & 15) || ((uintptr_t)vc & 15) ||
@@ -566,10 +590,14 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   if (e != cudaSuccess) return (int)e;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
-  dim3 grid(2u * (unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg);
+  dim3 grid(2u * (unsigned)((max_seg_rows + tc5::BM - 1) / tc5::BM) * n_head * n_seg * n_chunks);
   e = launch_pdl(kern, grid, dim3(tc5::THREADS), smem, (cudaStream_t)stream, map_q, map_k, map_v, block_table, max_blocks,
                  cu_rows, seg_start, (__nv_bfloat16*)out, out_ld, seg0, n_seg, n_head, n_kv_head, ps,
-                 scale * 1.4426950408889634f, window, error);
+                 scale * 1.4426950408889634f, window, n_chunks, chunk_keys, partial, row0, error);
+  if (e == cudaSuccess && n_chunks > 1)
+    e = launch_pdl(prefill_merge_kernel<__nv_bfloat16, true>, dim3(n_rows), dim3(128), 0, (cudaStream_t)stream,
+                   (const float*)partial, positions, (const int*)nullptr, (__nv_bfloat16*)out, out_ld, row0, n_head, hd, window,
+                   n_chunks, chunk_keys);
   return (int)e;
 }
 

@@ -21,11 +21,12 @@ import torch
 from ..kernels import ops
 
 
-def _key_chunks(ctx, mixer, nd, T, hd):
+def _key_chunks(ctx, mixer, nd, T, hd, row_tile=64, blocks_per_tile=1, blocks_per_sm=8, min_chunk=256):
     """Few rows behind a long context give the tiled kernels too few blocks: the keys are then cut into chunks over
     more blocks, whose partial results (in the step's scratch memory) a second kernel merges."""
     limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
-    chunks = ops.prefill_key_chunks(-(-ctx.max_seg_rows // 64), mixer.n_head, ctx.n_segments - nd, limit)
+    chunks = ops.prefill_key_chunks(-(-ctx.max_seg_rows // row_tile), mixer.n_head, ctx.n_segments - nd, limit,
+                                    blocks_per_tile, blocks_per_sm, min_chunk)
     partial = None
     if chunks[0] > 1:
         partial, _ = ctx.decode_scratch((T - nd) * mixer.n_head * chunks[0] * (hd + 4), 1)
@@ -66,9 +67,10 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
         tiled = qkv.dtype == torch.bfloat16 and ps & (ps - 1) == 0 and first_general == nd
         if tiled and hd in (64, 128) and 8 <= ps <= 128 and ops.USE_TCGEN05:
             # TMA + tcgen05: q and out keep their full row numbering, the kernel finds its rows through cu_rows
+            chunks, partial = _key_chunks(ctx, mixer, nd, T, hd, row_tile=128, blocks_per_tile=2, blocks_per_sm=2, min_chunk=8192)
             ops.paged_prefill_tc5(qkv, cache.k, cache.v, view.block_table, ctx.cu_rows, ctx.seg_start, out, nd,
                                   ctx.n_segments - nd, ctx.max_seg_rows, mixer.n_head, mixer.n_kv_head, hd, ps,
-                                  mixer.scale, mixer.window)
+                                  mixer.scale, mixer.window, chunks, partial, ctx.positions, nd, T - nd)
             return
         if tiled and hd % 16 == 0 and 16 <= hd <= 128:
             chunks, partial = _key_chunks(ctx, mixer, nd, T, hd)

@@ -6,6 +6,7 @@ launch streams from HBM, as in a real step) or launch by launch for profilers.
     python -m cbis_b200.kernels.microbench --op gemm_tc --rows 2048 --n 8192 --k 2048
     python -m cbis_b200.kernels.microbench --op layernorm --rows 8 --k 2048
     python -m cbis_b200.kernels.microbench --op sample --rows 8 --n 50257
+    python -m cbis_b200.kernels.microbench --op prefill_attn --rows 512 --ctx 32768 --heads 8 --head-dim 32 [--dtype float32]
 
 ``--no-graph`` launches the kernels directly (a profiler then sees ordinary launches).
 """
@@ -43,7 +44,9 @@ def timed(fn, use_graph=True, reps=20):
 def main():
     from cbis_b200.kernels import ops
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["decode_attn", "gemm", "gemm_tc", "layernorm", "sample"])
+    ap.add_argument("--op", required=True, choices=["decode_attn", "prefill_attn", "gemm", "gemm_tc", "layernorm", "sample"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="prefill_attn: the path")
+    ap.add_argument("--chunks", type=int, default=-1, help="prefill_attn: key chunks (-1: the engine's own choice, 1: none)")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--n", type=int, default=6144)
     ap.add_argument("--k", type=int, default=2048)
@@ -118,6 +121,52 @@ def main():
             for l in range(L):
                 ops.sample(lg, None, None, out)
         print(f"sample rows={M} vocab={a.n}: {timed(fn, not a.no_graph, a.reps) / L:.2f} us")
+    elif a.op == "prefill_attn":
+        # the last `rows` tokens of one request of `ctx` tokens (a portion of a prompt behind ctx - rows cached tokens)
+        H, hd, ps, ctx = a.heads, a.head_dim, a.page_size, a.ctx
+        dt = torch.float32 if a.dtype == "float32" else torch.bfloat16
+        L = min(L, 4)
+        nblk = -(-ctx // ps)
+        kc = torch.randn(L, nblk, H, ps, hd, device=dev, dtype=dt)
+        vc = torch.randn_like(kc)
+        bt_ = torch.randperm(nblk, device=dev).int().view(1, nblk).contiguous()
+        q = torch.randn(M, H * hd, device=dev, dtype=dt)
+        out = torch.empty_like(q)
+        cu = torch.tensor([0, M], dtype=torch.int32, device=dev)
+        start = torch.tensor([ctx - M], dtype=torch.int32, device=dev)
+        pos = torch.arange(ctx - M, ctx, dtype=torch.int32, device=dev)
+        chunks = ops.prefill_key_chunks(-(-M // 64), H, 1, ctx)
+        if a.chunks == 1:
+            chunks = (1, 0)
+        elif a.chunks > 1:
+            keys = 64
+            while keys * a.chunks < ctx:
+                keys *= 2
+            chunks = (-(-ctx // keys), keys)
+        partial = torch.empty(max(1, M * H * chunks[0] * (hd + 4)), device=dev)
+        fl = 4.0 * H * hd * (M * (ctx - M) + M * (M + 1) / 2)
+        forms = []
+        if dt == torch.float32:
+            forms.append(("32-bit tiled", lambda l: ops.paged_prefill_f32(q, kc[l], vc[l], bt_, cu, start, out, 0, 1, M, H, H, hd, ps,
+                                                                         hd ** -0.5, 0, chunks, partial, pos, 0, M)))
+        else:
+            forms.append(("mma.sync tiled", lambda l: ops.paged_prefill_bf16(q, kc[l], vc[l], bt_, cu, start, out, 0, 1, M, H, H, hd,
+                                                                            ps, hd ** -0.5, 0, chunks, partial, pos, 0, M)))
+            if hd in (64, 128) and 8 <= ps <= 128:
+                ch5 = ops.prefill_key_chunks(-(-M // 128), H, 1, ctx, 2, 2, 8192) if a.chunks < 0 else chunks
+                part5 = torch.empty(max(1, M * H * ch5[0] * (hd + 4)), device=dev)
+                forms.append((f"tcgen05 (key chunks {ch5[0]} x {ch5[1]})",
+                              lambda l: ops.paged_prefill_tc5(q, kc[l], vc[l], bt_, cu, start, out, 0, 1, M, H, H, hd, ps,
+                                                              hd ** -0.5, 0, ch5, part5, pos, 0, M)))
+        print(f"prefill_attn {a.dtype} rows={M} ctx={ctx} heads={H} head_dim={hd} page={ps}: {fl / 1e9:.2f} GFLOP, "
+              f"key chunks {chunks[0]} x {chunks[1]}")
+        for name, form in forms:
+            def fn():
+                for l in range(L):
+                    form(l)
+            t = timed(fn, not a.no_graph, a.reps) / L
+            print(f"   {name}: {t:.1f} us ({fl / t / 1e6:.1f} TFLOP/s)")
+        print(f"   error flag {ops.tcgen05_error_flag(dev).item()}")
     else:
         H, hd, ps, ctx = a.heads, a.head_dim, a.page_size, a.ctx
         nblk = -(-ctx // ps)

@@ -448,22 +448,22 @@ def paged_prefill_bf16(q, k_cache, v_cache, block_table, cu_rows, seg_start, out
                                      f"chunks={n_chunks}x{chunk_keys}")
 
 
-def prefill_key_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int):
-    """(n_chunks, chunk_keys) for the tiled prefill attention kernels (64-row tiles): no cut (1, 0) when (row tile,
-    head, segment) alone give four blocks to each of the 148 SMs; else chunks of a power of two of keys, at least
-    256, that do."""
-    base = max(1, row_tiles * n_head * n_seg)
-    want = -(-4 * 148 // base)
-    if want <= 1 or max_context <= 256:
+def prefill_key_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int, blocks_per_tile: int = 1,
+                       blocks_per_sm: int = 8, min_chunk: int = 256):
+    """(n_chunks, chunk_keys) for the tiled prefill attention kernels: no cut (1, 0) when (row tile, head, segment)
+    alone give ``blocks_per_sm`` blocks to each of the 148 SMs; else chunks of a power of two of keys, at least
+    ``min_chunk``, that do.  The tcgen05 kernel has two blocks per row tile and two per SM, and a block of it costs
+    some 8 us before its first tile: it is cut only into chunks of 8,192 keys or more (measured at 512 rows, 16 heads
+    of 128: 2,048 keys 32 us whole, 42 us in two chunks; 32,768 keys 385 us whole, 230 us in two, 291 us in eight)."""
+    base = max(1, row_tiles * n_head * n_seg * blocks_per_tile)
+    want = -(-blocks_per_sm * 148 // base)
+    if want <= 1 or max_context <= min_chunk:
         return 1, 0
-    chunk = 256
+    chunk = min_chunk
     while chunk * want < max_context:
         chunk *= 2
     n = -(-max_context // chunk)
     return (n, chunk) if n > 1 else (1, 0)
-
-
-prefill_f32_chunks = prefill_key_chunks
 
 
 def paged_prefill_f32(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
@@ -494,22 +494,30 @@ def paged_prefill_f32(q, k_cache, v_cache, block_table, cu_rows, seg_start, out,
 
 
 def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, seg0, n_seg, max_seg_rows,
-                      n_head, n_kv_head, head_dim, page_size, scale, window=0):
+                      n_head, n_kv_head, head_dim, page_size, scale, window=0, chunks=(1, 0), partial=None,
+                      positions=None, row0=0, n_rows=0):
     """The same attention as ``paged_prefill_bf16`` on the tcgen05 tensor cores (TMA operands, S and the output in
-    tensor memory).  Head size 64 or 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering."""
-    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out)
+    tensor memory).  Head size 64 or 128, page sizes 8..128 (powers of two); ``q`` and ``out`` in full row numbering.
+    ``chunks``, ``partial``, ``positions``, ``row0``, ``n_rows`` as for ``paged_prefill_bf16`` (chunks from
+    ``prefill_key_chunks`` with two blocks per 128-row tile, two per SM and chunks of at least 8,192 keys)."""
+    _need_cuda(q, k_cache, v_cache, block_table, cu_rows, seg_start, out, partial, positions)
     if head_dim not in (64, 128):
         raise KernelError(f"tcgen05 prefill attention: head_dim={head_dim} is neither 64 nor 128")
     if page_size & (page_size - 1) or not 8 <= page_size <= 128:
         raise KernelError(f"tcgen05 prefill attention: page_size={page_size} is not a power of two in 8..128")
     assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and block_table.is_contiguous() and k_cache.is_contiguous()
+    n_chunks, chunk_keys = chunks
+    if n_chunks > 1:
+        assert partial.dtype == torch.float32 and partial.numel() >= n_rows * n_head * n_chunks * (head_dim + 4)
+        assert positions.dtype == torch.int32 and positions.numel() >= row0 + n_rows
     st = kernels().cbis_paged_prefill_tc5(
         _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
         _ptr(block_table), c_int(block_table.shape[1]), _ptr(cu_rows), _ptr(seg_start), _ptr(out),
         c_int(out.stride(0)), c_int(seg0), c_int(n_seg), c_int(max_seg_rows), c_int(n_head), c_int(n_kv_head),
-        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), _ptr(tcgen05_error_flag(q.device)), _stream())
-    _check(st, "paged_prefill_tc5", f"segments={n_seg} heads={n_head}/{n_kv_head} page={page_size}")
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(n_chunks), c_int(chunk_keys),
+        _ptr(partial), _ptr(positions), c_int(row0), c_int(n_rows), _ptr(tcgen05_error_flag(q.device)), _stream())
+    _check(st, "paged_prefill_tc5", f"segments={n_seg} heads={n_head}/{n_kv_head} page={page_size} chunks={n_chunks}x{chunk_keys}")
 
 
 def paged_prefill_tc5_blocks_per_sm():

@@ -470,7 +470,9 @@ def test_prefill_attention_32_bit_tiled(ops, n_head, n_kv_head, hd, ps, window):
 
 
 def test_prefill_key_chunks_fill_the_gpu_and_cover_the_context(ops):
-    assert ops.prefill_key_chunks(40, 16, 1, 2048) == (1, 0)              # enough blocks without a cut
+    assert ops.prefill_key_chunks(80, 16, 1, 2048) == (1, 0)              # enough blocks without a cut
+    assert ops.prefill_key_chunks(16, 16, 1, 2048, 2, 2) == (1, 0)        # the tcgen05 kernel: two blocks a tile, two an SM
+    assert ops.prefill_key_chunks(4, 16, 1, 2048, 2, 2, 8192) == (1, 0) and ops.prefill_key_chunks(4, 16, 1, 32768, 2, 2, 8192) == (2, 16384)
     assert ops.prefill_key_chunks(1, 2, 1, 200) == (1, 0)                 # too short to cut
     for tiles, heads, segs, limit in [(8, 8, 1, 32768), (1, 1, 1, 5000), (2, 3, 2, 257), (8, 8, 1, 700)]:
         n, keys = ops.prefill_key_chunks(tiles, heads, segs, limit)
@@ -557,6 +559,18 @@ def test_prefill_attention_tcgen05(ops, n_head, n_kv_head, ps, window, hd):
     assert ops.tcgen05_error_flag("cuda").item() == 0
     err = (out.double().cpu() - c["ref"]).abs().max().item()
     assert err < 1.5e-2 * max(1.0, c["ref"].abs().max().item()), err
+    # the keys cut into chunks over more clusters and merged by the second kernel: the same to rounding
+    T = len(c["positions"])
+    for n_chunks, chunk_keys, s0 in [(3, 256, 0), (10, 64, 0), (5, 128, 2)]:
+        r0 = int(cu[s0])
+        partial = torch.full(((T - r0) * n_head * n_chunks * (hd + 4),), float("nan"), device="cuda")
+        cut = torch.full_like(c["q"], float("nan")).cuda()
+        ops.paged_prefill_tc5(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), cut, s0, S - s0,
+                              max(seg_rows[s0:]), n_head, n_kv_head, hd, ps, c["scale"], window, (n_chunks, chunk_keys),
+                              partial, dev(c["positions"]), r0, T - r0)
+        assert ops.tcgen05_error_flag("cuda").item() == 0
+        assert torch.isnan(cut[:r0].float()).all()
+        assert (cut[r0:].float() - out[r0:].float()).abs().max().item() < 1.5e-2 * max(1.0, c["ref"].abs().max().item())
     # agrees with the mma.sync form to rounding
     out2 = torch.empty_like(out)
     ops.paged_prefill_bf16(dev(c["q"]), c["kc"], c["vc"], dev(c["bt"]), dev(cu), dev(start), out2, 0, S, max(seg_rows),
