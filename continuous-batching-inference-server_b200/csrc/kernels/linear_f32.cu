@@ -74,6 +74,102 @@ linear_f32_kernel(const float* A, const float* __restrict__ W, const float* __re
   }
 }
 
+// More than 16 rows with W stored [N, K] (both operands contiguous along k, 16-byte aligned): tiles of BM x BN
+// outputs, k in pieces of 32 that arrive by 16-byte cp.async in two buffers (the next piece is on its way while
+// this one is multiplied), operands kept [row][k] in shared memory so that the copy is straight and a thread reads
+// four k of a row at once.  A thread owns the outputs (ty + 16 i, tx + 16 j) and walks k from left to right with
+// one fused multiply-add per element: the order of the kernels above and below, hence the same bits.  The tile
+// shrinks (64x64, 32x64, 32x32) until the grid fills the SMs: a 512 x 256 x 1024 product had 8 blocks of the
+// 128 x 128 kernel above and took 190 us.
+__device__ __forceinline__ void cp_async16_f32(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;   // 0 bytes read: the 16 bytes in shared memory are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+
+template <int BM, int BN>
+__global__ void __launch_bounds__(256)
+linear_f32_nk_kernel(const float* A, const float* __restrict__ W, const float* __restrict__ bias, float* __restrict__ C,
+                     int M, int N, int K, int act, int lda, int ldc) {
+  constexpr int BK = 32, PITCH = BK + 4, TM = BM / 16, TN = BN / 16;
+  __shared__ __align__(16) float As[2][BM][PITCH];
+  __shared__ __align__(16) float Ws[2][BN][PITCH];
+  pdl_trigger();
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  auto load_w = [&](int k0, int stage) {
+    for (int i = tid; i < BN * (BK / 4); i += 256) {
+      const int r = i / (BK / 4), c = (i % (BK / 4)) * 4;
+      const bool valid = n0 + r < N && k0 + c < K;
+      cp_async16_f32(&Ws[stage][r][c], valid ? W + (size_t)(n0 + r) * K + k0 + c : W, valid);
+    }
+  };
+  auto load_a = [&](int k0, int stage) {
+    for (int i = tid; i < BM * (BK / 4); i += 256) {
+      const int r = i / (BK / 4), c = (i % (BK / 4)) * 4;
+      const bool valid = m0 + r < M && k0 + c < K;
+      cp_async16_f32(&As[stage][r][c], valid ? A + (size_t)(m0 + r) * lda + k0 + c : A, valid);
+    }
+  };
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+  load_w(0, 0);   // the weights do not come from the kernel before
+  pdl_wait();
+  load_a(0, 0);
+  asm volatile("cp.async.commit_group;\n" ::);
+  const int n_kt = (K + BK - 1) / BK;
+  for (int kt = 0; kt < n_kt; ++kt) {
+    const int stage = kt & 1;
+    if (kt + 1 < n_kt) {
+      load_w((kt + 1) * BK, stage ^ 1);
+      load_a((kt + 1) * BK, stage ^ 1);
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+    const int kc = min(BK, K - kt * BK);   // a multiple of 4; the sum stops at K (0 * 0 could still flip the sign of a zero)
+#pragma unroll 2
+    for (int kk = 0; kk < kc; kk += 4) {
+      float4 a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = *reinterpret_cast<const float4*>(&As[stage][ty + 16 * i][kk]);
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = *reinterpret_cast<const float4*>(&Ws[stage][tx + 16 * j][kk]);
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          float v = acc[i][j];
+          v = fmaf(a[i].x, b[j].x, v);
+          v = fmaf(a[i].y, b[j].y, v);
+          v = fmaf(a[i].z, b[j].z, v);
+          v = fmaf(a[i].w, b[j].w, v);
+          acc[i][j] = v;
+        }
+    }
+    __syncthreads();   // this buffer is free for the piece after the next
+  }
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + ty + 16 * i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (bias) v += bias[n];
+      C[(size_t)m * ldc + n] = activate(v, act);
+    }
+  }
+}
+
 // Up to 16 rows (decoding) with W stored [N, K]: the tiled kernel above would run N / 64 blocks that walk K in
 // steps of 16 with two barriers each: 62 us for a 16 x 768 x 256 product.  Here a block takes 16 output columns
 // and a thread owns ONE output (lane m of a half-warp: row m; the half-warp: one column).  K comes in pieces of
@@ -138,11 +234,23 @@ linear_f32_few_rows_kernel(const float* A, const float* __restrict__ W, const fl
 using namespace cbis;
 
 // lda / ldc: row strides of A and C in elements (>= K, >= N).
+// variant: 0 the launcher's choice; 1 never the cp.async kernel (the older tiled kernels: all give the same bits).
 CBIS_EXPORT int cbis_linear_f32(const float* A, const float* W, const float* bias, float* C, int M, int N, int K,
-                                int w_is_nk, int act, int lda, int ldc, void* stream) {
+                                int w_is_nk, int act, int lda, int ldc, int variant, void* stream) {
   if (M <= 0 || N <= 0) return CBIS_OK;
   if (K <= 0 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
+  if (variant != 1 && w_is_nk && M > 16 && K % 4 == 0 && lda % 4 == 0 && !(((uintptr_t)A | (uintptr_t)W) & 15)) {
+    const long long b64 = (long long)((M + 63) / 64) * ((N + 63) / 64), b32 = (long long)((M + 31) / 32) * ((N + 63) / 64);
+    if (b64 >= 2 * 148)
+      return (int)launch_pdl(linear_f32_nk_kernel<64, 64>, dim3((N + 63) / 64, (M + 63) / 64), dim3(256), 0, st, A, W, bias, C,
+                             M, N, K, act, lda, ldc);
+    if (b32 >= 148)
+      return (int)launch_pdl(linear_f32_nk_kernel<32, 64>, dim3((N + 63) / 64, (M + 31) / 32), dim3(256), 0, st, A, W, bias, C,
+                             M, N, K, act, lda, ldc);
+    return (int)launch_pdl(linear_f32_nk_kernel<32, 32>, dim3((N + 31) / 32, (M + 31) / 32), dim3(256), 0, st, A, W, bias, C,
+                           M, N, K, act, lda, ldc);
+  }
   if (M > 256) {
     dim3 grid((N + 127) / 128, (M + 127) / 128);
     return (int)launch_pdl(linear_f32_kernel<128, 128, 8, 8, 8>, grid, dim3(256), 0, st, A, W, bias, C, M, N, K, w_is_nk,

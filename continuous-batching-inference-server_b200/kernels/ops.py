@@ -138,8 +138,9 @@ def bias_act_out(src, bias, act, dst):
     _check(st, "bias_act_out", f"M={M} N={N}")
 
 
-def linear_f32(x, w, bias, act, out, w_is_nk=False):
-    """out = act(x @ W + bias) on the FP32 units; W is [K,N], or [N,K] with ``w_is_nk``."""
+def linear_f32(x, w, bias, act, out, w_is_nk=False, variant=0):
+    """out = act(x @ W + bias) on the FP32 units; W is [K,N], or [N,K] with ``w_is_nk``.  ``variant`` 1 keeps the
+    cp.async kernel out (all kernels sum along k in the same order and give the same bits)."""
     _need_cuda(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0] if w_is_nk else w.shape[1]
@@ -148,7 +149,7 @@ def linear_f32(x, w, bias, act, out, w_is_nk=False):
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] >= M and out.shape[1] == N
     st = kernels().cbis_linear_f32(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), c_int(M), c_int(N), c_int(K),
                                    c_int(1 if w_is_nk else 0), c_int(ACT[act]), c_int(x.stride(0)),
-                                   c_int(out.stride(0)), _stream())
+                                   c_int(out.stride(0)), c_int(variant), _stream())
     _check(st, "linear_f32", f"M={M} N={N} K={K}")
 
 

@@ -123,6 +123,25 @@ def test_linear_f32(ops, M, N, K):
     assert torch.equal(big[:, N:].cpu(), torch.zeros(M, 5))
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 256, 1024), (70, 100, 64), (300, 513, 300), (33, 40, 36), (2048, 768, 256), (17, 1000, 8)])
+def test_linear_f32_kernels_give_the_same_bits(ops, M, N, K):
+    """Every 32-bit product kernel sums along k in the same order: the cp.async kernel (its three tile sizes), the older
+    tiled kernels and the few-rows kernel agree bit for bit, so a token's logits do not depend on which step shape
+    (and therefore which kernel) computed them."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x, w, b = dev(torch.randn(M, K, generator=g)), dev(torch.randn(N, K, generator=g)), dev(torch.randn(N, generator=g))
+    new, old = torch.full((M, N), float("nan"), device="cuda"), torch.full((M, N), float("nan"), device="cuda")
+    ops.linear_f32(x, w, b, "gelu_erf", new, w_is_nk=True)
+    ops.linear_f32(x, w, b, "gelu_erf", old, w_is_nk=True, variant=1)
+    assert torch.equal(new, old)
+    lo = min(5, M - 16)
+    few = torch.empty(16, N, device="cuda")
+    ops.linear_f32(x[lo:lo + 16], w, b, "gelu_erf", few, w_is_nk=True)    # 16 rows: the few-rows kernel
+    assert torch.equal(few, new[lo:lo + 16])
+    ref = plain_gpt.gelu(x.double() @ w.double().t() + b.double(), "gelu")
+    assert (new.double() - ref).abs().max().item() < 2e-6 * max(1.0, ref.abs().max().item()) * math.sqrt(K)
+
+
 def test_linear_f32_is_true_32_bit(ops):
     # a product that TF32 (10-bit mantissa) would get wrong by ~1e-3 relative
     g = torch.Generator().manual_seed(1)
