@@ -24,7 +24,7 @@ from ..kernels import ops
 def _key_chunks(ctx, mixer, nd, T, hd, row_tile=64, blocks_per_tile=1, blocks_per_sm=8, min_chunk=256):
     """Few rows behind a long context give the tiled kernels too few blocks: the keys are then cut into chunks over
     more blocks, whose partial results (in the step's scratch memory) a second kernel merges."""
-    limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+    limit = ctx.ctx_limit
     chunks = ops.prefill_key_chunks(-(-ctx.max_seg_rows // row_tile), mixer.n_head, ctx.n_segments - nd, limit,
                                     blocks_per_tile, blocks_per_sm, min_chunk)
     partial = None
@@ -35,7 +35,7 @@ def _key_chunks(ctx, mixer, nd, T, hd, row_tile=64, blocks_per_tile=1, blocks_pe
 
 def _general_chunks(ctx, mixer, rows, hd):
     """The general kernel gives a warp to every (row, head): a few rows behind a long context are cut the same way."""
-    limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+    limit = ctx.ctx_limit
     chunks = ops.generic_key_chunks(rows, mixer.n_head, limit, hd)
     partial = None
     if chunks[0] > 1:
@@ -51,7 +51,7 @@ def run_attention(ctx, mixer, qkv, cache, view, out) -> None:
     fast_decode = qkv.dtype == torch.bfloat16 and hd % 8 == 0 and hd <= 256 and nd > 0
     first_general = nd if fast_decode else 0
     if fast_decode:
-        limit = ctx.max_positions if ctx.fixed_shapes else ctx.max_ctx
+        limit = ctx.ctx_limit
         nsplit = ops.decode_splits(nd, mixer.n_head, limit)
         scratch = counters = None
         if nsplit > 1:

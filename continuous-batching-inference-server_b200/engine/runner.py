@@ -71,6 +71,8 @@ class StepContext:
         self.runner = None
         self.fixed_shapes = False              # the step is being captured for replay: no size may depend on this batch
         self.max_positions = 0
+        self.ctx_limit = 0                     # no request of the step is longer: the step's own maximum, or, in a step
+                                               # captured for replay, the bound of the graph's context class
 
     def layer_cache(self, li: int):
         return self.pool.layer_cache.get(li)
@@ -111,7 +113,7 @@ class ModelRunner:
         self.use_graphs = all(getattr(part, "capturable", True)
                               for layer in model.layers for _, part in layer.parts()) \
             and getattr(model.position, "capturable", True) and getattr(model.final_norm, "capturable", True)
-        self._graphs: Dict[int, tuple] = {}      # rows of a decode-only step -> (graph, context, logits)
+        self._graphs: Dict[tuple, tuple] = {}    # (rows of a decode-only step, context class) -> (graph, logits)
         # Steps with prompt portions: a step's SHAPE (tokens and wanted rows per entry, in order) fixes every launch
         # of it; what differs between two steps of one shape (tokens, positions, block tables, wanted rows) is in
         # the packed buffer on the device.  A shape seen for the eighth time is captured (that costs about 60 ms) and
@@ -195,7 +197,7 @@ class ModelRunner:
         self._pack(entries, 0, False, reserved_ahead)
 
     def build_context(self, entries, pad_rows: int = 0, all_logits: bool = False,
-                      reserved_ahead: bool = False, fixed_shapes: bool = False) -> StepContext:
+                      reserved_ahead: bool = False, fixed_shapes: bool = False, ctx_limit: int = 0) -> StepContext:
         """Packs the step into the host buffer, copies it over, returns the views.
 
         ``pad_rows`` > 0 (decode-only steps): the step is laid out for exactly that many rows and
@@ -214,6 +216,7 @@ class ModelRunner:
         ctx.logit_rows = self._dev_view("logit_rows", R)
         ctx.host_seg_rows, ctx.host_seg_ctx = list(info.seg_rows), list(info.seg_ctx)
         ctx.max_seg_rows, ctx.max_ctx = info.max_seg_rows, info.max_ctx
+        ctx.ctx_limit = (ctx_limit or ctx.max_positions) if ctx.fixed_shapes else info.max_ctx
         for g in range(self._n_groups):
             mb = pool.max_blocks(g)
             ctx.groups.append(GroupView(self._dev_view(f"block_table{g}", S * mb).view(S, mb),
@@ -295,13 +298,19 @@ class ModelRunner:
 
     def _decode_step_graph(self, entries, native: bool) -> torch.Tensor:
         rows = self._bucket(len(entries))
-        have = self._graphs.get(rows)
+        info = self._pack(entries, rows, True, False)     # the captured kernels read the same buffer: no views needed
+        # a graph holds for a number of rows and a class of context lengths (256, 1024, 4096, ... up to the model's
+        # positions): kernels that split a request's keys over blocks size the split for the class's bound, so short
+        # requests of a model with many positions are not cut into pieces that are mostly empty
+        limit = 256
+        while limit < info.max_ctx:
+            limit *= 4
+        limit = min(limit, self.model.spec.max_positions)
+        have = self._graphs.get((rows, limit))
         if have is None:
-            ctx = self.build_context(entries, pad_rows=rows, all_logits=True)
+            ctx = self.build_context(entries, pad_rows=rows, all_logits=True, ctx_limit=limit)
             self.model.forward(ctx)                       # warm-up outside the capture (writes the same cache values)
-            have = self._graphs[rows] = capture_graph(lambda: self.model.forward(ctx))
-        else:
-            self._pack(entries, rows, True, False)        # the captured kernels read the same buffer: no views needed
+            have = self._graphs[(rows, limit)] = capture_graph(lambda: self.model.forward(ctx))
         graph, logits = have
         graph.replay()
         self.graph_replays += 1

@@ -212,6 +212,7 @@ def gemm_few_rows(x, w_nk, bias, act, out, ksplit=0):
 
 _tc_error = {}
 USE_TCGEN05 = __import__("os").environ.get("CBIS_TCGEN05", "1") != "0"
+USE_KEY_CHUNKS = __import__("os").environ.get("CBIS_KEY_CHUNKS", "1") != "0"   # 0: attention kernels never cut the keys over more blocks
 USE_TILED_F32 = __import__("os").environ.get("CBIS_TILED_F32", "1") != "0"   # 0: the general kernel for 32-bit prompts
 USE_FEW_ROWS = USE_TCGEN05 and __import__("os").environ.get("CBIS_FEW_ROWS", "1") != "0"
 
@@ -348,7 +349,7 @@ def generic_key_chunks(rows: int, n_head: int, max_context: int, head_dim: int):
     heads alone give 16 warps to each of the 148 SMs, or the head size is no multiple of 4; else chunks of a power
     of two of keys, at least 256, that do."""
     want = -(-16 * 148 // max(1, rows * n_head))
-    if want <= 1 or max_context <= 256 or head_dim % 4:
+    if want <= 1 or max_context <= 256 or head_dim % 4 or not USE_KEY_CHUNKS:
         return 1, 0
     chunk = 256
     while chunk * want < max_context:
@@ -458,7 +459,7 @@ def prefill_key_chunks(row_tiles: int, n_head: int, n_seg: int, max_context: int
     of 128: 2,048 keys 32 us whole, 42 us in two chunks; 32,768 keys 385 us whole, 230 us in two, 291 us in eight)."""
     base = max(1, row_tiles * n_head * n_seg * blocks_per_tile)
     want = -(-blocks_per_sm * 148 // base)
-    if want <= 1 or max_context <= min_chunk:
+    if want <= 1 or max_context <= min_chunk or not USE_KEY_CHUNKS:
         return 1, 0
     chunk = min_chunk
     while chunk * want < max_context:
