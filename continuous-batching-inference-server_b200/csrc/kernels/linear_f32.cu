@@ -92,8 +92,9 @@ __global__ void __launch_bounds__(256)
 linear_f32_nk_kernel(const float* A, const float* __restrict__ W, const float* __restrict__ bias, float* __restrict__ C,
                      int M, int N, int K, int act, int lda, int ldc) {
   constexpr int BK = 32, PITCH = BK + 4, TM = BM / 16, TN = BN / 16;
-  __shared__ __align__(16) float As[2][BM][PITCH];
-  __shared__ __align__(16) float Ws[2][BN][PITCH];
+  extern __shared__ __align__(16) float nk_smem[];
+  float (*As)[BM][PITCH] = reinterpret_cast<float (*)[BM][PITCH]>(nk_smem);                      // [2][BM][PITCH]
+  float (*Ws)[BN][PITCH] = reinterpret_cast<float (*)[BN][PITCH]>(nk_smem + 2 * BM * PITCH);     // [2][BN][PITCH]
   pdl_trigger();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -241,15 +242,24 @@ CBIS_EXPORT int cbis_linear_f32(const float* A, const float* W, const float* bia
   if (K <= 0 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
   cudaStream_t st = (cudaStream_t)stream;
   if (variant != 1 && w_is_nk && M > 16 && K % 4 == 0 && lda % 4 == 0 && !(((uintptr_t)A | (uintptr_t)W) & 15)) {
-    const long long b64 = (long long)((M + 63) / 64) * ((N + 63) / 64), b32 = (long long)((M + 31) / 32) * ((N + 63) / 64);
-    if (b64 >= 2 * 148)
-      return (int)launch_pdl(linear_f32_nk_kernel<64, 64>, dim3((N + 63) / 64, (M + 63) / 64), dim3(256), 0, st, A, W, bias, C,
-                             M, N, K, act, lda, ldc);
-    if (b32 >= 148)
-      return (int)launch_pdl(linear_f32_nk_kernel<32, 64>, dim3((N + 63) / 64, (M + 31) / 32), dim3(256), 0, st, A, W, bias, C,
-                             M, N, K, act, lda, ldc);
-    return (int)launch_pdl(linear_f32_nk_kernel<32, 32>, dim3((N + 31) / 32, (M + 31) / 32), dim3(256), 0, st, A, W, bias, C,
-                           M, N, K, act, lda, ldc);
+    // (a 128 x 128 tile, 8 x 8 outputs a thread, was measured too: 198 registers, one block per SM, no faster than 64 x 64)
+    const long long b64 = (long long)((M + 63) / 64) * ((N + 63) / 64),
+                    b32 = (long long)((M + 31) / 32) * ((N + 63) / 64);
+#define CBIS_NK(BM_, BN_)                                                                                              \
+  {                                                                                                                    \
+    auto kern = linear_f32_nk_kernel<BM_, BN_>;                                                                        \
+    const size_t smem = (size_t)2 * (BM_ + BN_) * 36 * sizeof(float);                                                  \
+    if (smem > 48 * 1024) {                                                                                            \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
+      if (e != cudaSuccess) return (int)e;                                                                             \
+    }                                                                                                                  \
+    return (int)launch_pdl(kern, dim3((N + BN_ - 1) / BN_, (M + BM_ - 1) / BM_), dim3(256), smem, st, A, W, bias, C, M, N, K, \
+                           act, lda, ldc);                                                                             \
+  }
+    if (b64 >= 2 * 148) CBIS_NK(64, 64)
+    if (b32 >= 148) CBIS_NK(32, 64)
+    CBIS_NK(32, 32)
+#undef CBIS_NK
   }
   if (M > 256) {
     dim3 grid((N + 127) / 128, (M + 127) / 128);

@@ -4,6 +4,7 @@ launch streams from HBM, as in a real step) or launch by launch for profilers.
     python -m cbis_b200.kernels.microbench --op decode_attn --rows 8 --ctx 1536 --layers 24
     python -m cbis_b200.kernels.microbench --op gemm --rows 8 --n 6144 --k 2048
     python -m cbis_b200.kernels.microbench --op gemm_tc --rows 2048 --n 8192 --k 2048
+    python -m cbis_b200.kernels.microbench --op gemm_f32 --rows 512 --n 256 --k 1024
     python -m cbis_b200.kernels.microbench --op layernorm --rows 8 --k 2048
     python -m cbis_b200.kernels.microbench --op sample --rows 8 --n 50257
     python -m cbis_b200.kernels.microbench --op prefill_attn --rows 512 --ctx 32768 --heads 8 --head-dim 32 [--dtype float32]
@@ -44,7 +45,7 @@ def timed(fn, use_graph=True, reps=20):
 def main():
     from cbis_b200.kernels import ops
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["decode_attn", "prefill_attn", "gemm", "gemm_tc", "layernorm", "sample"])
+    ap.add_argument("--op", required=True, choices=["decode_attn", "prefill_attn", "gemm", "gemm_tc", "gemm_f32", "layernorm", "sample"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="prefill_attn: the path")
     ap.add_argument("--chunks", type=int, default=-1, help="prefill_attn: key chunks (-1: the engine's own choice, 1: none)")
     ap.add_argument("--rows", type=int, default=8)
@@ -103,6 +104,18 @@ def main():
         tl = timed(lib, not a.no_graph, a.reps) / len(W)
         print(f"gemm_tc M={M} N={a.n} K={a.k}: tcgen05 with bias+{a.act} {t:.1f} us ({fl / t / 1e6:.0f} TFLOP/s)  "
               f"library, no epilogue {tl:.1f} us ({fl / tl / 1e6:.0f} TFLOP/s)  error flag {ops.tcgen05_error_flag(dev).item()}")
+    elif a.op == "gemm_f32":
+        x = torch.randn(M, a.k, device=dev)
+        W = [torch.randn(a.n, a.k, device=dev) * 0.02 for _ in range(min(L, 4))]
+        bias = torch.randn(a.n, device=dev)
+        out = torch.empty(M, a.n, device=dev)
+        fl = 2.0 * M * a.n * a.k
+        for name, variant in (("cp.async kernel", 0), ("older tiled kernels", 1)):
+            def fn():
+                for w in W:
+                    ops.linear_f32(x, w, bias, a.act if a.act != "none" else None, out, w_is_nk=True, variant=variant)
+            t = timed(fn, not a.no_graph, a.reps) / len(W)
+            print(f"gemm_f32 M={M} N={a.n} K={a.k} {name}: {t:.1f} us ({fl / t / 1e6:.1f} TFLOP/s)")
     elif a.op == "layernorm":
         x = torch.randn(M, a.k, device=dev)
         delta = torch.randn(M, a.k, device=dev)

@@ -123,7 +123,8 @@ def test_linear_f32(ops, M, N, K):
     assert torch.equal(big[:, N:].cpu(), torch.zeros(M, 5))
 
 
-@pytest.mark.parametrize("M,N,K", [(512, 256, 1024), (70, 100, 64), (300, 513, 300), (33, 40, 36), (2048, 768, 256), (17, 1000, 8)])
+@pytest.mark.parametrize("M,N,K", [(512, 256, 1024), (70, 100, 64), (300, 513, 300), (33, 40, 36), (2048, 768, 256), (17, 1000, 8),
+                                   (2000, 2500, 68)])
 def test_linear_f32_kernels_give_the_same_bits(ops, M, N, K):
     """Every 32-bit product kernel sums along k in the same order: the cp.async kernel (its three tile sizes), the older
     tiled kernels and the few-rows kernel agree bit for bit, so a token's logits do not depend on which step shape
