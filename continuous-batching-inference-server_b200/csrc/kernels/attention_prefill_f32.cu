@@ -6,7 +6,9 @@
 // tiles of 32 keys gathered page by page through the block table.  Four threads share a query row: each computes
 // 8 of the tile's 32 scores (fused multiply-adds over the head dim, 16 bytes of Q and K per load), the four
 // combine maximum and sum with two shuffles, P goes through shared memory, and each thread accumulates its
-// quarter of the head dims of P V.  Everything is 32-bit arithmetic; the softmax is the online form with running
+// quarter of the head dims of P V.  A thread does this for two rows at once, 32 apart: with one row a thread the
+// kernel ran at 85 % of the shared-memory load rate and a quarter of the FFMA rate, and every key and value it
+// loads now serves two rows.  Everything is 32-bit arithmetic; the softmax is the online form with running
 // maximum and sum per row (kernels/attention.cu:74-95).
 //
 // A long context with few rows (a 512-token portion behind 30,000 cached tokens, 8 heads) gives too few blocks
@@ -18,7 +20,8 @@
 
 namespace cbis {
 
-constexpr int F_BM = 64, F_BN = 32, F_THREADS = 256;
+constexpr int F_BM = 64, F_BN = 32, F_THREADS = 128;
+constexpr int P_PITCH = F_BN + 4;   // floats per row of P: the four threads of eight rows store to 32 different banks
 
 // grid: (row tiles of the longest segment, heads, segments from seg0 on).  HD4: head dims per thread in P V (hd / 4).
 template <int HD>
@@ -32,7 +35,7 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
   float* sQ = smem_f;                       // [F_BM][PITCH]
   float* sK = sQ + F_BM * PITCH;            // [F_BN][PITCH]
   float* sV = sK + F_BN * PITCH;            // [F_BN][PITCH]
-  float* sP = sV + F_BN * PITCH;            // [F_BM][F_BN + 1]
+  float* sP = sV + F_BN * PITCH;            // [F_BM][P_PITCH]
   pdl_trigger();
   pdl_wait();
   // late row tiles have the most keys to walk: they are given out first
@@ -52,8 +55,11 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
   }
   const int* bt = block_table + (size_t)seg * max_blocks;
   const int tid = threadIdx.x;
-  const int r = tid >> 2, part = tid & 3;   // this thread's row of the tile and its place among the row's four threads
-  const int p = pos0 + r;                   // the row's position
+  // a thread has TWO rows of the tile, r0 and r0 + 32 (the keys and values it loads from shared memory serve both:
+  // the kernel is bound by those loads), and is one of the four threads of each
+  const int r0 = tid >> 2, part = tid & 3;
+  const int rr2[2] = {r0, r0 + F_BM / 2};
+  const int p2[2] = {pos0 + r0, pos0 + r0 + F_BM / 2};   // the rows' positions
 
   for (int i = tid; i < F_BM * (HD / 4); i += F_THREADS) {
     const int rr = i / (HD / 4), c = (i % (HD / 4)) * 4;
@@ -61,10 +67,12 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
     if (rr < rows_here) v = *reinterpret_cast<const float4*>(q + (size_t)(r_begin + tile * F_BM + rr) * q_ld + h * HD + c);
     *reinterpret_cast<float4*>(sQ + rr * PITCH + c) = v;
   }
-  float o[D4];
+  float o[2][D4];
 #pragma unroll
-  for (int d = 0; d < D4; ++d) o[d] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  for (int w = 0; w < 2; ++w)
+#pragma unroll
+    for (int d = 0; d < D4; ++d) o[w][d] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   const int kt_first = kbegin / F_BN, kt_last = (kend - 1) / F_BN;
   for (int kt = kt_first; kt <= kt_last; ++kt) {
@@ -83,79 +91,98 @@ paged_prefill_f32_kernel(const float* q, int q_ld, const float* kc, const float*
       *reinterpret_cast<float4*>(sV + rr * PITCH + c) = vv;
     }
     __syncthreads();
-    // scores of keys part, part + 4, ... (8 of the 32)
-    float s[F_BN / 4];
+    // scores of keys part, part + 4, ... (8 of the 32), for both rows
+    float s[2][F_BN / 4];
 #pragma unroll
-    for (int u = 0; u < F_BN / 4; ++u) s[u] = 0.f;
-    const float* qrow = sQ + r * PITCH;
-#pragma unroll 4
+    for (int w = 0; w < 2; ++w)
+#pragma unroll
+      for (int u = 0; u < F_BN / 4; ++u) s[w][u] = 0.f;
+#pragma unroll 2
     for (int c = 0; c < HD; c += 4) {
-      const float4 qv = *reinterpret_cast<const float4*>(qrow + c);
+      const float4 qa = *reinterpret_cast<const float4*>(sQ + rr2[0] * PITCH + c);
+      const float4 qb = *reinterpret_cast<const float4*>(sQ + rr2[1] * PITCH + c);
 #pragma unroll
       for (int u = 0; u < F_BN / 4; ++u) {
         const float4 kv = *reinterpret_cast<const float4*>(sK + (part + 4 * u) * PITCH + c);
-        s[u] = fmaf(qv.x, kv.x, s[u]);
-        s[u] = fmaf(qv.y, kv.y, s[u]);
-        s[u] = fmaf(qv.z, kv.z, s[u]);
-        s[u] = fmaf(qv.w, kv.w, s[u]);
+        s[0][u] = fmaf(qa.x, kv.x, s[0][u]);
+        s[0][u] = fmaf(qa.y, kv.y, s[0][u]);
+        s[0][u] = fmaf(qa.z, kv.z, s[0][u]);
+        s[0][u] = fmaf(qa.w, kv.w, s[0][u]);
+        s[1][u] = fmaf(qb.x, kv.x, s[1][u]);
+        s[1][u] = fmaf(qb.y, kv.y, s[1][u]);
+        s[1][u] = fmaf(qb.z, kv.z, s[1][u]);
+        s[1][u] = fmaf(qb.w, kv.w, s[1][u]);
       }
     }
-    float mx = -INFINITY;
+    float corr[2];
 #pragma unroll
-    for (int u = 0; u < F_BN / 4; ++u) {
-      const int j = j0 + part + 4 * u;
-      const bool seen = j <= p && j < kend && (window == 0 || j >= p - window + 1);
-      s[u] = seen ? s[u] * scale : -INFINITY;
-      mx = fmaxf(mx, s[u]);
+    for (int w = 0; w < 2; ++w) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int u = 0; u < F_BN / 4; ++u) {
+        const int j = j0 + part + 4 * u;
+        const bool seen = j <= p2[w] && j < kend && (window == 0 || j >= p2[w] - window + 1);
+        s[w][u] = seen ? s[w][u] * scale : -INFINITY;
+        mx = fmaxf(mx, s[w][u]);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[w], mx);
+      const float base = m_new == -INFINITY ? 0.f : m_new;   // a row with no key in range yet
+      corr[w] = expf(m[w] - base);
+      float psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < F_BN / 4; ++u) {
+        const float e = expf(s[w][u] - base);
+        psum += e;
+        sP[rr2[w] * P_PITCH + part + 4 * u] = e;
+      }
+      psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+      psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+      l[w] = l[w] * corr[w] + psum;
+      m[w] = m_new;
+#pragma unroll
+      for (int d = 0; d < D4; ++d) o[w][d] *= corr[w];
     }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m, mx);
-    const float base = m_new == -INFINITY ? 0.f : m_new;   // a row with no key in range yet
-    const float corr = expf(m - base);
-    float psum = 0.f;
-#pragma unroll
-    for (int u = 0; u < F_BN / 4; ++u) {
-      const float e = expf(s[u] - base);
-      psum += e;
-      sP[r * (F_BN + 1) + part + 4 * u] = e;
-    }
-    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-    l = l * corr + psum;
-    m = m_new;
-    __syncwarp();   // the four threads of a row are neighbours in one warp: P of the row is complete
-#pragma unroll
-    for (int d = 0; d < D4; ++d) o[d] *= corr;
-    const float* prow = sP + r * (F_BN + 1);
+    __syncwarp();   // the four threads of a row are neighbours in one warp: P of both rows is complete
+    const float* pa = sP + rr2[0] * P_PITCH;
+    const float* pb = sP + rr2[1] * P_PITCH;
 #pragma unroll 4
     for (int j = 0; j < F_BN; ++j) {
-      const float pj = prow[j];
+      const float p0 = pa[j], p1 = pb[j];
       const float* vrow = sV + j * PITCH + part * D4;
 #pragma unroll
       for (int d = 0; d < D4; d += 4) {
         const float4 vv = *reinterpret_cast<const float4*>(vrow + d);
-        o[d] = fmaf(pj, vv.x, o[d]);
-        o[d + 1] = fmaf(pj, vv.y, o[d + 1]);
-        o[d + 2] = fmaf(pj, vv.z, o[d + 2]);
-        o[d + 3] = fmaf(pj, vv.w, o[d + 3]);
+        o[0][d] = fmaf(p0, vv.x, o[0][d]);
+        o[0][d + 1] = fmaf(p0, vv.y, o[0][d + 1]);
+        o[0][d + 2] = fmaf(p0, vv.z, o[0][d + 2]);
+        o[0][d + 3] = fmaf(p0, vv.w, o[0][d + 3]);
+        o[1][d] = fmaf(p1, vv.x, o[1][d]);
+        o[1][d + 1] = fmaf(p1, vv.y, o[1][d + 1]);
+        o[1][d + 2] = fmaf(p1, vv.z, o[1][d + 2]);
+        o[1][d + 3] = fmaf(p1, vv.w, o[1][d + 3]);
       }
     }
   }
-  if (r >= rows_here) return;
-  if (n_chunks > 1) {
-    float* dst = partial + (((size_t)(r_begin + tile * F_BM + r - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const int r = rr2[w];
+    if (r >= rows_here) continue;
+    if (n_chunks > 1) {
+      float* dst = partial + (((size_t)(r_begin + tile * F_BM + r - row0) * n_head + h) * n_chunks + chunk) * (HD + 4);
+#pragma unroll
+      for (int d = 0; d < D4; d += 4)
+        *reinterpret_cast<float4*>(dst + part * D4 + d) = make_float4(o[w][d], o[w][d + 1], o[w][d + 2], o[w][d + 3]);
+      if (part == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(m[w], l[w]);
+      continue;
+    }
+    const float inv = 1.f / l[w];
+    float* dst = out + (size_t)(r_begin + tile * F_BM + r) * out_ld + h * HD + part * D4;
 #pragma unroll
     for (int d = 0; d < D4; d += 4)
-      *reinterpret_cast<float4*>(dst + part * D4 + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
-    if (part == 0) *reinterpret_cast<float2*>(dst + HD) = make_float2(m, l);
-    return;
+      *reinterpret_cast<float4*>(dst + d) = make_float4(o[w][d] * inv, o[w][d + 1] * inv, o[w][d + 2] * inv, o[w][d + 3] * inv);
   }
-  const float inv = 1.f / l;
-  float* dst = out + (size_t)(r_begin + tile * F_BM + r) * out_ld + h * HD + part * D4;
-#pragma unroll
-  for (int d = 0; d < D4; d += 4)
-    *reinterpret_cast<float4*>(dst + d) = make_float4(o[d] * inv, o[d + 1] * inv, o[d + 2] * inv, o[d + 3] * inv);
 }
 
 }  // namespace cbis
@@ -185,7 +212,7 @@ CBIS_EXPORT int cbis_paged_prefill_f32(const float* q, int q_ld, const float* kc
 #define CBIS_PF32(HD_)                                                                                               \
   if (hd == HD_) {                                                                                                   \
     auto kern = paged_prefill_f32_kernel<HD_>;                                                                       \
-    const size_t smem = ((size_t)(F_BM + 2 * F_BN) * (HD_ + 4) + (size_t)F_BM * (F_BN + 1)) * sizeof(float);          \
+    const size_t smem = ((size_t)(F_BM + 2 * F_BN) * (HD_ + 4) + (size_t)F_BM * P_PITCH) * sizeof(float);            \
     if (smem > 48 * 1024) {                                                                                          \
       e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                        \
       if (e != cudaSuccess) return (int)e;                                                                           \
