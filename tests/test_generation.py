@@ -78,6 +78,24 @@ def test_long_decoding_to_the_last_position(folder_a):
     assert out == plain_gpt.generate(cfg, w, prompt, len(out))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_the_context_classes_of_the_decode_graphs(tmp_path, dtype):
+    """Decode-only steps replay a graph captured for a class of context lengths (256, 1024, ... up to the model's
+    positions), for which the attention kernels size their split of the keys.  Requests decode across the bounds 256
+    and 1024 side by side and a short one goes on alone: every token is the plain implementation's, and all three
+    classes were captured."""
+    import cbis_b200 as cb
+    cfgd = dict(tc.TINY_B, n_positions=1300)
+    folder = str(tmp_path / "long_b")
+    cb.write_model_folder(folder, cb.config_from_dict(cfgd), seed=5, scheme=cb.InitScheme(*tc.INIT_B))
+    eng = cb.Engine(folder, dtype=dtype, page_size=8, max_tokens=2700, max_num_seqs=3, max_batched_tokens=512)
+    prompts = prompts_for(cfgd, [250, 1015, 10], seed=9)
+    outs = eng.generate(prompts, [cb.SamplingParams(max_new_tokens=n) for n in (16, 16, 40)])   # the short one ends alone
+    check_against_plain(folder, prompts, outs, 0.0, 0, 0, exact=dtype == "float32")
+    if eng.runner.use_graphs:
+        assert {limit for _, limit in eng.runner._graphs} == {256, 1024, 1300}
+
+
 def test_first_tokens_of_a_sequence(tiny):
     import cbis_b200 as cb
     folder, cfg, page = tiny
