@@ -1,8 +1,8 @@
 """Device memory of the cache: pages per group of layers, fixed-size state per request slot.
 
-Layers whose mixers need the same kind of cache (same key/value heads, head size and
+Layers whose mixers need the same kind of cache (the same named arrays per token and the same
 window) form a group; a group has one pool of pages and one block table per request,
-and every layer of the group has its own K and V arrays indexed by the same page ids
+and every layer of the group has its own arrays (attention: K and V) indexed by the same page ids
 (the reference has this one implicit group: ``k_base(l)``/``v_base(l)`` share the page id,
 include/paged_kv_cache.hpp:38-39; and allocates 2 L separate buffers,
 src/paged_kv_cache.cpp:8-14 - here a group is one allocation).  The host bookkeeping
@@ -11,7 +11,7 @@ src/paged_kv_cache.cpp:8-14 - here a group is one allocation).  The host bookkee
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -21,11 +21,19 @@ from ..parts import CacheNeed
 
 @dataclass
 class LayerCache:
+    """The pages of one layer: per declared array a tensor ``[num_pages, heads, page_size, width]``."""
     group: int
-    k: torch.Tensor          # [num_pages, n_kv_head, page_size, head_dim]
-    v: torch.Tensor
+    arrays: Dict[str, torch.Tensor]
     page_size: int
     window: int
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.arrays["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.arrays["v"]
 
 
 @dataclass
@@ -34,10 +42,10 @@ class CacheGroup:
     layers: List[int]
     page_size: int
     num_pages: int
-    storage: Optional[torch.Tensor] = None   # [n_layers, 2, num_pages, n_kv_head, page_size, head_dim]
+    storage: Optional[torch.Tensor] = None   # one flat allocation: [layer][array][page][head][token][width]
 
     def bytes_per_page(self, itemsize: int) -> int:
-        return len(self.layers) * 2 * self.need.n_kv_head * self.page_size * self.need.head_dim * itemsize
+        return len(self.layers) * self.need.elements_per_token() * self.page_size * itemsize
 
 
 def cache_groups_of(model, page_size: int) -> List[CacheGroup]:
@@ -76,12 +84,19 @@ class CachePool:
             num_pages = min(num_pages, max_requests * (-(-model.spec.max_positions // page_size)))
         self.layer_cache: Dict[int, LayerCache] = {}
         specs = []
+        align = 256 // itemsize                      # every array starts on a 256-byte boundary (TMA wants 16)
         for gi, g in enumerate(self.groups):
             g.num_pages = int(num_pages)
-            g.storage = torch.zeros((len(g.layers), 2, g.num_pages, g.need.n_kv_head, page_size, g.need.head_dim),
-                                    dtype=self.dtype, device=self.device)
-            for j, li in enumerate(g.layers):
-                self.layer_cache[li] = LayerCache(gi, g.storage[j, 0], g.storage[j, 1], page_size, g.need.window)
+            sizes = [(-(-g.num_pages * a.heads * page_size * a.width // align) * align) for a in g.need.arrays]
+            g.storage = torch.zeros(len(g.layers) * sum(sizes), dtype=self.dtype, device=self.device)
+            at = 0
+            for li in g.layers:
+                arrays = {}
+                for a, size in zip(g.need.arrays, sizes):
+                    n = g.num_pages * a.heads * page_size * a.width
+                    arrays[a.name] = g.storage[at:at + n].view(g.num_pages, a.heads, page_size, a.width)
+                    at += size
+                self.layer_cache[li] = LayerCache(gi, arrays, page_size, g.need.window)
             specs.append(host().GroupSpec(page_size, g.num_pages, g.need.window))
         if not specs:  # a model without any cache still needs request slots
             specs.append(host().GroupSpec(page_size, 0, 0))
@@ -108,4 +123,15 @@ class CachePool:
 
     def bytes_per_token(self) -> int:
         itemsize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.layers) * 2 * g.need.n_kv_head * g.need.head_dim * itemsize for g in self.groups)
+        return sum(len(g.layers) * g.need.elements_per_token() * itemsize for g in self.groups)
+
+    def poison_pages(self, group: int, pages: Sequence[int]) -> None:
+        """Fills the given pages of every array of every layer of ``group`` with NaN (a debugging aid: a
+        kernel that reads a page its request no longer holds, or a token slot beyond a request's length
+        inside a page that was used before, then shows up as NaN logits)."""
+        if not pages or group >= len(self.groups):
+            return
+        idx = torch.tensor(sorted(set(int(p) for p in pages)), dtype=torch.long, device=self.device)
+        for li in self.groups[group].layers:
+            for t in self.layer_cache[li].arrays.values():
+                t.index_fill_(0, idx, float("nan"))

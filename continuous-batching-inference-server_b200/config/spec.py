@@ -10,7 +10,7 @@ twice, and a layer may read another layer's cache (``cache_source``).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Dict, List, Optional, Tuple, Union
 
 
 @dataclass(frozen=True)
@@ -43,17 +43,34 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class ModelSpec:
+    """``token_embedding`` and ``head`` are parts like the others: a ``PartSpec`` of the embedding
+    registry (built in: "token_table" with ``tensor`` and ``multiplier``) and of the head registry
+    (built in: "linear" with ``tensor`` (None: tied to the embedding's table), ``bias`` (a tensor
+    name or None), ``logit_scale`` and ``soft_cap``).  As a shorthand a tensor name stands for a
+    plain token table, and a tensor name or None for a plain linear head.  ``final_norm`` may be
+    ``PartSpec("none", {"width": w})`` for a model that has none."""
     width: int
     vocab_size: int
     max_positions: int
-    token_embedding: str                    # tensor name of the token table
+    token_embedding: Union[str, PartSpec]   # the input: token rows (PartSpec of the embedding registry)
     position: PartSpec                      # position encoding at the input (or "none")
     layers: Tuple[LayerSpec, ...]
     schedule: Tuple[int, ...]               # layer indices in running order
     final_norm: PartSpec
     final_norm_prefix: str
-    head: Optional[str]                     # tensor name of an untied head, None = tied to the token table
+    head: Union[None, str, PartSpec]        # the output: logits from the last norm's rows (PartSpec of the head registry)
     ignored_tensors: Tuple[str, ...] = ()   # regular expressions of tensors a checkpoint may carry unused
+
+    def embedding_spec(self) -> PartSpec:
+        if isinstance(self.token_embedding, PartSpec):
+            return self.token_embedding
+        return PartSpec("token_table", {"vocab_size": self.vocab_size, "width": self.width,
+                                        "tensor": self.token_embedding})
+
+    def head_spec(self) -> PartSpec:
+        if isinstance(self.head, PartSpec):
+            return self.head
+        return PartSpec("linear", {"vocab_size": self.vocab_size, "width": self.width, "tensor": self.head})
 
 
 class ConfigError(ValueError):

@@ -49,6 +49,8 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def("block_table", &CacheManager::block_table)
       .def("table_len", &CacheManager::table_len)
       .def("token_slot", &CacheManager::token_slot)
+      .def("record_freed", &CacheManager::record_freed)
+      .def("take_freed", &CacheManager::take_freed)
       .def("check", &CacheManager::check);
 
   py::class_<SchedulerLimits>(m, "SchedulerLimits")

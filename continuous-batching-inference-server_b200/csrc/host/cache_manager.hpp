@@ -49,6 +49,11 @@ class CacheManager {
   int window(int g) const { return groups_.at(g).window; }
   int free_pages(int g) const { return (int)free_.at(g).size(); }
   int free_slots() const { return (int)free_slots_.size(); }
+  int largest_page() const {
+    int m = 1;
+    for (const GroupSpec& s : groups_) m = s.page_size > m ? s.page_size : m;
+    return m;
+  }
 
   // Takes a state slot for a new request; -1 if none is free.  The slot index also addresses
   // the request's fixed-size state.
@@ -174,6 +179,21 @@ class CacheManager {
     free_slots_.push_back(slot);
   }
 
+  // Debugging aid: with recording on, every page that is given back is also noted, and take_freed hands the
+  // notes of a group over (and forgets them), so that the owner of the device memory can overwrite those
+  // pages before the next step runs.  A page may be noted and already belong to a new request: that request
+  // writes its tokens in the step that follows, after the overwrite.
+  void record_freed(bool on) {
+    record_freed_ = on;
+    freed_.assign(groups_.size(), {});
+  }
+  std::vector<int> take_freed(int g) {
+    if (!record_freed_) return {};
+    std::vector<int> out;
+    out.swap(freed_.at(g));
+    return out;
+  }
+
   // Logical page -> physical page of the request in group g; -1 where a page was given back.
   const std::vector<int>& block_table(int slot, int g) const { return get(slot).tables.at(g); }
   // Number of logical pages of the request in group g (cheap: lets a caller keep a copy of the table
@@ -242,9 +262,12 @@ class CacheManager {
     if (owner_[g][p] != slot) throw std::logic_error("cache manager: page freed by a request that does not hold it");
     owner_[g][p] = -1;
     free_[g].push_back(p);
+    if (record_freed_) freed_[g].push_back(p);
   }
 
   std::vector<GroupSpec> groups_;
+  bool record_freed_ = false;
+  std::vector<std::vector<int>> freed_;  // per group: pages given back since the last take_freed (if recorded)
   std::vector<std::vector<int>> free_;   // per group, LIFO
   std::vector<std::vector<int>> owner_;  // per group: page -> slot or -1
   std::vector<Slot> slots_;

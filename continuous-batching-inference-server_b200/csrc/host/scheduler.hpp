@@ -14,7 +14,11 @@
 //     and goes to the FRONT of the waiting queue, to be recomputed later; sampling is keyed
 //     by (request, output index), so it continues as it would have;
 //   * waiting requests are admitted FIFO while a slot, budget and pages for their first
-//     portion are there; a request that could never fit is refused when it is added.
+//     portion are there; a request that could never fit is refused when it is added;
+//   * a step that preempted admits nobody, and a request that was preempted before comes back
+//     only when everything it holds so far, plus a page, fits beside the running requests:
+//     otherwise the pages it just gave up would let it in again at once, to be recomputed and
+//     thrown out again every few steps.
 #pragma once
 #include <algorithm>
 #include <cstdint>
@@ -106,6 +110,7 @@ class Scheduler {
     // them, and it has been launched (work on the device runs in launch order).
     for (int64_t id : running_) cache_->release_out_of_window(reqs_.at(id).slot);
     // (1) running requests, oldest first
+    const long preemptions_before = preemptions_;
     for (size_t i = 0; i < running_.size() && budget > 0;) {
       Req& r = reqs_.at(running_[i]);
       const int remaining = (int)r.tokens.size() - r.computed;
@@ -130,10 +135,14 @@ class Scheduler {
       ++i;
     }
     // (2) admissions, FIFO
-    while (!waiting_.empty() && budget > 0 && (int)running_.size() < lim_.max_num_seqs && cache_->free_slots() > 0) {
+    while (preemptions_ == preemptions_before && !waiting_.empty() && budget > 0 &&
+           (int)running_.size() < lim_.max_num_seqs && cache_->free_slots() > 0) {
       Req& r = reqs_.at(waiting_.front());
       const int remaining = (int)r.tokens.size();
       int n = std::min({remaining, lim_.prefill_chunk, budget});
+      // preempted before: room for all it knows and a page more (one token more per group rounds up to that)
+      if (r.times_preempted > 0 && !running_.empty() && !cache_->fits_fresh(remaining + cache_->largest_page()))
+        break;
       if (!cache_->fits_fresh(n)) {
         if (!running_.empty()) break;  // wait until running requests give pages back
         // nothing is running, so every page is free: take what fits (add() made sure it can finish)
@@ -204,6 +213,7 @@ class Scheduler {
     int computed = 0;         // tokens whose keys/values are in the cache
     int slot = -1;
     bool admitted_now = false;
+    int times_preempted = 0;
   };
 
   void emit(Req& r, int n, std::vector<PlannedEntry>* plan) {
@@ -225,6 +235,7 @@ class Scheduler {
     r.slot = -1;
     r.computed = 0;
     r.admitted_now = false;
+    ++r.times_preempted;
     running_.erase(std::remove(running_.begin(), running_.end(), id), running_.end());
     waiting_.push_front(id);
     ++preemptions_;

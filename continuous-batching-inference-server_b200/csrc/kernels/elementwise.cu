@@ -4,12 +4,12 @@
 
 namespace cbis {
 
-// x[r,:] = wte[tok[r],:] + wpe[pos[r],:]   (reference: kernels/elementwise.cu:7-17)
+// x[r,:] = wte[tok[r],:] * tok_scale + wpe[pos[r],:]   (reference: kernels/elementwise.cu:7-17, no scale there)
 // A token or position outside its table sets *err (1 = token, 2 = position) and gives a zero row.
 template <typename TT>
 __global__ void embed_pos_add_kernel(const int* tokens, const int* positions,
                                      const TT* __restrict__ wte, const TT* __restrict__ wpe,
-                                     float* __restrict__ out, int d, int vocab, int n_pos, int* err) {
+                                     float* __restrict__ out, int d, int vocab, int n_pos, float tok_scale, int* err) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -27,7 +27,7 @@ __global__ void embed_pos_add_kernel(const int* tokens, const int* positions,
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float v = 0.f;
     if (tok_ok && pos_ok) {
-      v = to_f32(trow[c]);
+      v = to_f32(trow[c]) * tok_scale;
       if (prow) v += to_f32(prow[c]);
     }
     orow[c] = v;
@@ -37,7 +37,7 @@ __global__ void embed_pos_add_kernel(const int* tokens, const int* positions,
 // One block per output row r; src row s = rows ? rows[r] : r.
 //   v = x[s,:] (+ delta[s,:]) (+ delta_bias[:])           32-bit
 //   if rows == nullptr and (delta or bias): x[s,:] = v      the residual stream moves on
-//   out[r,:] = (v - mean) * rsqrt(var + eps) * gamma + beta
+//   out[r,:] = (v - mean) * rsqrt(var + eps) * gamma + beta      (gamma == nullptr: out[r,:] = v, no norm)
 // var is the centred, biased variance (the reference uses E[x^2]-mean^2, kernels/elementwise.cu:50).
 // The row is staged in shared memory (d floats), so x is read once.
 template <typename TD, typename TO>
@@ -75,7 +75,7 @@ __global__ void add_layernorm_kernel(float* __restrict__ x, const TD* delta,
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     const float v = row[c];
     if (write_x) xrow[c] = v;
-    from_f32(orow[c], (v - mean) * inv * gamma[c] + beta[c]);
+    from_f32(orow[c], gamma ? (v - mean) * inv * gamma[c] + (beta ? beta[c] : 0.f) : v);
   }
 }
 
@@ -117,8 +117,8 @@ add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ de
     const int c = threadIdx.x + i * 128;
     gm[i] = bt[i] = db[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < nvec) {
-      gm[i] = *reinterpret_cast<const float4*>(gamma + 4 * c);
-      bt[i] = *reinterpret_cast<const float4*>(beta + 4 * c);
+      if (gamma) gm[i] = *reinterpret_cast<const float4*>(gamma + 4 * c);
+      if (beta) bt[i] = *reinterpret_cast<const float4*>(beta + 4 * c);
       if (delta_bias) db[i] = *reinterpret_cast<const float4*>(delta_bias + 4 * c);
     }
   }
@@ -161,11 +161,13 @@ add_layernorm_reg_kernel(float* x, const TD* delta, const float* __restrict__ de
     const int c = threadIdx.x + i * 128;
     if (c < nvec) {
       if (write_x) *reinterpret_cast<float4*>(xrow + 4 * c) = v[i];
-      float4 y;
-      y.x = (v[i].x - mean) * inv * gm[i].x + bt[i].x;
-      y.y = (v[i].y - mean) * inv * gm[i].y + bt[i].y;
-      y.z = (v[i].z - mean) * inv * gm[i].z + bt[i].z;
-      y.w = (v[i].w - mean) * inv * gm[i].w + bt[i].w;
+      float4 y = v[i];
+      if (gamma) {
+        y.x = (v[i].x - mean) * inv * gm[i].x + bt[i].x;
+        y.y = (v[i].y - mean) * inv * gm[i].y + bt[i].y;
+        y.z = (v[i].z - mean) * inv * gm[i].z + bt[i].z;
+        y.w = (v[i].w - mean) * inv * gm[i].w + bt[i].w;
+      }
       store4(orow + 4 * c, y);
     }
   }
@@ -197,23 +199,45 @@ __global__ void bias_act_out_kernel(const float* src, const float* __restrict__ 
   }
 }
 
+// x = cap > 0 ? cap * tanh(x * scale / cap) : x * scale, in place (logits of a head with a scale or a soft cap).
+__global__ void scale_soft_cap_kernel(float* x, float scale, float cap, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = x[i] * scale;
+    x[i] = cap > 0.f ? cap * tanhf(v * inv_cap) : v;
+  }
+}
+
 }  // namespace cbis
 
 using namespace cbis;
 
+// The widest row the norm kernel takes (it is staged in shared memory beyond 8,192 columns).
+CBIS_EXPORT int cbis_norm_max_width() { return (200 * 1024) / (int)sizeof(float) - 33; }
+
+CBIS_EXPORT int cbis_scale_soft_cap(float* x, float scale, float cap, int M, int N, void* stream) {
+  if (M <= 0 || N <= 0) return CBIS_OK;
+  const size_t total = (size_t)M * N;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (int)launch_pdl(scale_soft_cap_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, x, scale, cap, total);
+}
+
 CBIS_EXPORT int cbis_embed_pos_add(const int* tokens, const int* positions, const void* wte, const void* wpe,
-                                   float* out, int T, int d, int vocab, int n_pos, int table_dtype, int* err,
-                                   void* stream) {
+                                   float* out, int T, int d, int vocab, int n_pos, int table_dtype, float tok_scale,
+                                   int* err, void* stream) {
   if (T <= 0) return CBIS_OK;
   if (d <= 0) return CBIS_ERR_BAD_SIZE;
   const int threads = d >= 1024 ? 256 : (d >= 256 ? 128 : 64);
   cudaStream_t st = (cudaStream_t)stream;
   if (table_dtype == CBIS_F32)
     return (int)launch_after(false, embed_pos_add_kernel<float>, dim3(T), dim3(threads), 0, st, tokens, positions,
-                           (const float*)wte, (const float*)wpe, out, d, vocab, n_pos, err);
+                           (const float*)wte, (const float*)wpe, out, d, vocab, n_pos, tok_scale, err);
   if (table_dtype == CBIS_BF16)
     return (int)launch_after(false, embed_pos_add_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, st, tokens, positions,
-                           (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d, vocab, n_pos, err);
+                           (const __nv_bfloat16*)wte, (const __nv_bfloat16*)wpe, out, d, vocab, n_pos, tok_scale, err);
   return CBIS_ERR_BAD_DTYPE;
 }
 

@@ -34,9 +34,9 @@ __device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Waits for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, unsigned limit = TC_SPIN_LIMIT) {
   const unsigned a = smem_u32(bar);
-  for (unsigned it = 0; it < TC_SPIN_LIMIT; ++it) {
+  for (unsigned it = 0; it < limit; ++it) {
     unsigned ok;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
@@ -158,7 +158,10 @@ template <typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                    int* error) {
+                    int* error, unsigned spin_limit, int starve) {
+  // spin_limit: tries of every wait before it gives up (TC_SPIN_LIMIT in service).  starve != 0 (tests of the
+  // give-up path only): the loading thread requests nothing, so the waits for operands wait for a signal that
+  // nothing sends, run out, and the block reports, frees its tensor memory and returns with no copy in flight.
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // stages first (each tile 1024-byte aligned for the swizzle), then the barriers
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -166,7 +169,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   unsigned long long* empty = full + TC_STAGES;
   unsigned long long* acc_full = empty + TC_STAGES;    // [2]
   unsigned long long* acc_empty = acc_full + 2;         // [2]
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+  unsigned long long* drained = acc_empty + 2;          // [1]: the products issued before a give-up have finished
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(drained + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -183,6 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       mbar_init(&acc_full[b2], 1);
       mbar_init(&acc_empty[b2], TC_EPI_WARPS);   // one arrival per epilogue warp
     }
+    mbar_init(drained, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -204,11 +209,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       unsigned it = 0;  // k-tiles loaded so far, over all tiles of this block
-      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag && !starve; tile += gridDim.x) {
         const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * TC_BN;
         for (int kt = 0; kt < n_kt; ++kt, ++it) {
           const unsigned s = it % TC_STAGES, round = it / TC_STAGES;
-          if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1)) {
+          if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, spin_limit)) {
             *abort_flag = 1;
             atomicExch(error, 1);
             break;
@@ -220,6 +225,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           tma_load_2d(sa + TC_A_BYTES, &map_w, kt * TC_BK, n0, &full[s]);
         }
       }
+      if (*abort_flag) {
+        // a give-up somewhere in the block: the copies this thread requested last may still be on their way into
+        // shared memory; the block must not leave before they have landed (waits with the full limit)
+        for (unsigned j = it > (unsigned)TC_STAGES ? it - TC_STAGES : 0; j < it; ++j)
+          if (!mbar_wait(&full[j % TC_STAGES], (j / TC_STAGES) & 1)) atomicExch(error, 5);
+      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -227,7 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       unsigned it = 0, local = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x, ++local) {
         const unsigned buf = local & 1, use = local >> 1;
-        if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {   // the epilogue has read this accumulator
+        if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1, spin_limit)) {   // the epilogue has read this accumulator
           *abort_flag = 4;
           atomicExch(error, 4);
           break;
@@ -237,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         for (int kt = 0; kt < n_kt; ++kt, ++it) {
           const unsigned s = it % TC_STAGES, round = it / TC_STAGES;
-          if (!mbar_wait(&full[s], round & 1)) {
+          if (!mbar_wait(&full[s], round & 1, spin_limit)) {
             *abort_flag = 2;
             atomicExch(error, 2);
             ok = false;
@@ -255,6 +266,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!ok) break;
         umma_commit(&acc_full[buf]);  // arrives when every product issued so far has finished
       }
+      if (*abort_flag) {
+        // products issued before the give-up may still run: tensor memory is freed only after they have finished
+        umma_commit(drained);
+        if (!mbar_wait(drained, 0)) atomicExch(error, 6);
+      }
     }
   } else {
     // epilogue: a warp can read the 32 lanes of the quarter of tensor memory given by its index % 4; the
@@ -268,7 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * TC_BN;
       const unsigned buf = local & 1, use = local >> 1;
       const int row = m0 + quarter * 32 + lane;
-      if (!mbar_wait(&acc_full[buf], use & 1)) {
+      if (!mbar_wait(&acc_full[buf], use & 1, spin_limit)) {
         atomicExch(error, 3);
         break;
       }
@@ -591,16 +607,30 @@ using namespace cbis;
 
 // A [M, lda] and W [N, K] bfloat16 (K contiguous, lda and K multiples of 8, 16-byte aligned), bias [N] float or
 // null, C [M, ldc] bfloat16 or float.  error: int on the device, set non-zero if a wait inside the kernel ran out.
+// spin_limit (0: the service limit) and starve are for the single-block form (M <= 128) and exist for the test
+// of the give-up path: see the kernel.  With starve the result is not computed and *error becomes non-zero.
+CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
+                                          int M, int N, int K, int act, int out_dtype, int* error, void* stream,
+                                          unsigned spin_limit, int starve);
+
 CBIS_EXPORT int cbis_gemm_tcgen05_bf16(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
                                        int M, int N, int K, int act, int out_dtype, int* error, void* stream) {
+  return cbis_gemm_tcgen05_bf16_ex(A, lda, W, bias, C, ldc, M, N, K, act, out_dtype, error, stream, 0, 0);
+}
+
+CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
+                                          int M, int N, int K, int act, int out_dtype, int* error, void* stream,
+                                          unsigned spin_limit, int starve) {
   if (M <= 0 || N <= 0) return CBIS_OK;
+  if (spin_limit == 0) spin_limit = TC_SPIN_LIMIT;
+  if (starve && M > TC_BM) return CBIS_ERR_BAD_SIZE;     // only the single-block form can be starved
   if (K <= 0 || K % 8 || lda % 8 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || error == nullptr) return CBIS_ERR_ALIGNMENT;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   CUtensorMap map_a, map_w;
   cudaError_t e;
-  if (pair_enabled() && M > TC_BM) {
+  if (pair_enabled() && M > TC_BM && !starve) {
     // pairs of blocks on 256 x 256 tiles: every block loads boxes of 128 rows of A and of W
     // the tile's width: the multiple of 16 for which the pairs' rounds over the tiles take the least time (a last
     // round that only a few pairs work in costs as much as a full one)
@@ -653,13 +683,13 @@ CBIS_EXPORT int cbis_gemm_tcgen05_bf16(const void* A, int lda, const void* W, co
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(kern, grid, dim3(TC_THREADS), smem, (cudaStream_t)stream, map_a, map_w, bias, (__nv_bfloat16*)C, ldc,
-                   M, N, K, act, error);
+                   M, N, K, act, error, spin_limit, starve);
   } else if (out_dtype == CBIS_F32) {
     auto kern = gemm_tcgen05_kernel<float>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(kern, grid, dim3(TC_THREADS), smem, (cudaStream_t)stream, map_a, map_w, bias, (float*)C, ldc, M, N, K,
-                   act, error);
+                   act, error, spin_limit, starve);
   } else {
     return CBIS_ERR_BAD_DTYPE;
   }

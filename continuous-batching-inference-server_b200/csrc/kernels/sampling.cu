@@ -98,9 +98,10 @@ __global__ void sample_kernel(const float* logits, int ld, const float* temperat
 using namespace cbis;
 
 // Chunks a row of V entries is cut into, and the scratch this needs: chunks*R floats, chunks*R ints, R counters.
+#define CBIS_SAMPLE_MAX_CHUNKS 64
 CBIS_EXPORT int cbis_sample_chunks(int V) {
   int c = (V + 4095) / 4096;
-  return c < 1 ? 1 : (c > 64 ? 64 : c);
+  return c < 1 ? 1 : (c > CBIS_SAMPLE_MAX_CHUNKS ? CBIS_SAMPLE_MAX_CHUNKS : c);
 }
 
 // logits [R, ld >= V] 32-bit; temperature[R] (<= 0: greedy) and keys[R] may be null (greedy).
@@ -126,7 +127,7 @@ CBIS_EXPORT int cbis_sample(const float* logits, int ld, const float* temperatur
 
 namespace {
 
-constexpr int NA_MAX_CHUNKS = 64;  // cbis_sample_chunks() never returns more
+constexpr int NA_MAX_CHUNKS = CBIS_SAMPLE_MAX_CHUNKS;  // the bound that cbis_sample_chunks() itself clamps to
 constexpr int NA_WORDS = CBIS_SAMPLE_NO_ALLOC_MAX_ROWS * NA_MAX_CHUNKS * 2 + CBIS_SAMPLE_NO_ALLOC_MAX_ROWS;
 
 // chunk maxima (floats), their indices (ints), one counter per row: 33,024 words = 132,096 bytes.
@@ -171,6 +172,7 @@ CBIS_EXPORT int cbis_sample_no_alloc(const float* logits, int ld, const float* t
   cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)R * sizeof(unsigned int), (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   const int chunks = cbis_sample_chunks(V);
+  if (chunks > NA_MAX_CHUNKS) return CBIS_ERR_TOO_LARGE;   // the fixed array is laid out for NA_MAX_CHUNKS per row
   const int threads = V >= 1024 ? 256 : 64;
   dim3 grid(chunks, R);
   return (int)launch_after(false, sample_kernel, grid, dim3(threads), 0, (cudaStream_t)stream, logits, ld, temperature,

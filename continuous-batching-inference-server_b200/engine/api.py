@@ -36,12 +36,15 @@ class Engine:
     def __init__(self, model: Union[str, Model], *, dtype="bfloat16", page_size: int = 16,
                  num_pages: Optional[int] = None, max_tokens: Optional[int] = None, max_num_seqs: int = 16,
                  max_batched_tokens: int = 512, prefill_chunk: Optional[int] = None,
-                 memory_fraction: float = 0.85, device: str = "cuda"):
+                 memory_fraction: float = 0.85, device: str = "cuda", poison_freed_pages: Optional[bool] = None):
         """``model``: a folder with config.json and model.safetensors, or a loaded ``Model``.
         Engine options in the reference's terms: ``page_size`` = kPageSize (include/config.hpp:20),
         ``num_pages`` = kMaxPages, ``max_num_seqs`` = kMaxSlots, ``max_batched_tokens`` =
         kMaxTotalRows (src/server_demo.cpp:27-29).  ``prefill_chunk`` cuts prompts into portions
-        (src/bench_tiering.cpp:78 uses 512); default: the token budget."""
+        (src/bench_tiering.cpp:78 uses 512); default: the token budget.  ``poison_freed_pages`` (default:
+        the environment's CBIS_POISON_FREED_PAGES=1) is a debugging mode: every page that a request gives back
+        is filled with NaN before the next step runs, so a read of a page that is no longer held, or of a
+        token slot beyond a request's length in a page that was used before, shows as NaN logits."""
         if not torch.cuda.is_available():
             raise RuntimeError("the engine needs a CUDA device (sm_100a); there is no CPU path")
         self.model = load_model(model, dtype, device) if isinstance(model, str) else model
@@ -53,6 +56,12 @@ class Engine:
                            prefill_chunk=prefill_chunk or max_batched_tokens,
                            max_positions=self.model.spec.max_positions)
         self.scheduler = host().Scheduler(self.pool.manager, host().SchedulerLimits(**self.limits))
+        if poison_freed_pages is None:
+            poison_freed_pages = os.environ.get("CBIS_POISON_FREED_PAGES", "0") == "1"
+        self.poison_freed_pages = bool(poison_freed_pages)
+        self.pages_poisoned = 0
+        if self.poison_freed_pages:
+            self.pool.manager.record_freed(True)
         self._params: Dict[int, SamplingParams] = {}
         self._next_id = 0
         self.steps = 0
@@ -62,9 +71,12 @@ class Engine:
     # ---- construction from random weights --------------------------------------
     @classmethod
     def from_random(cls, config, seed: int = 1234, *, init: InitScheme = InitScheme(), dtype="bfloat16",
-                    weight_dtype: Optional[torch.dtype] = None, device: str = "cuda", **options) -> "Engine":
+                    weight_dtype: Optional[torch.dtype] = None, device: str = "cuda", draw_on: Optional[str] = None,
+                    **options) -> "Engine":
         """Random weights of ``config`` (a typed configuration, a dict of config.json keys, or a path
-        to a config.json), drawn on the device; nothing is written to disk."""
+        to a config.json), drawn on the device; nothing is written to disk.  ``draw_on="cpu"`` draws them
+        with the CPU's generator instead (slower): ``weights.random_tensors`` with the same declarations,
+        seed and scheme then gives another program the same values."""
         if isinstance(config, str):
             with open(config if config.endswith(".json") else os.path.join(config, "config.json")) as f:
                 config = json.load(f)
@@ -73,10 +85,20 @@ class Engine:
         model = Model(config.model_spec())
         model.config = config
         wd = weight_dtype or (torch.bfloat16 if resolve_dtype(dtype) == torch.bfloat16 else torch.float32)
-        tensors = random_tensors(model.declared(), seed, init, wd, device=device)
+        tensors = random_tensors(model.declared(), seed, init, wd, device=device, draw_on=draw_on)
         model.load(tensors, dtype, device, where="random weights")
         del tensors
         return cls(model, dtype=dtype, device=device, **options)
+
+    def _poison_freed(self) -> None:
+        """Debugging mode: overwrites the pages given back since the last step (queued before the next one)."""
+        if not self.poison_freed_pages:
+            return
+        mgr = self.pool.manager
+        for g in range(mgr.num_groups()):
+            pages = mgr.take_freed(g)
+            self.pages_poisoned += len(pages)
+            self.pool.poison_pages(g, pages)
 
     # ---- requests ---------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -105,6 +127,7 @@ class Engine:
             return []
         for slot in self.scheduler.take_new_slots():
             self.pool.clear_state(slot)
+        self._poison_freed()
         logits = self.runner.step(plan, borrow=True)     # the native plan goes to the native packer as it is
         self.steps += 1
         self.last_step_tokens = sum(p.n_tokens for p in plan)
@@ -149,7 +172,15 @@ class Engine:
             params = [params or SamplingParams()] * len(prompts)
         if len(params) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
-        ids = [self.add_request(p, q) for p, q in zip(prompts, params)]
+        ids = []
+        try:
+            for p, q in zip(prompts, params):
+                ids.append(self.add_request(p, q))
+        except Exception:
+            for rid in ids:                       # a refused prompt leaves nothing of this call behind
+                self.scheduler.abort(rid)
+                self._params.pop(rid, None)
+            raise
         results: Dict[int, List[int]] = {}
         while self.has_unfinished():
             for o in self.step():
@@ -182,6 +213,7 @@ class Engine:
             if not mgr.append(e.slot, len(e.tokens)):
                 raise RuntimeError(f"slot {e.slot}: no pages left for {len(e.tokens)} more tokens "
                                    f"(free pages per group: {[mgr.free_pages(g) for g in range(mgr.num_groups())]})")
+        self._poison_freed()
         out = self.runner.step(entries)
         if any(len(e.tokens) > 1 for e in entries):
             # a step with prompt portions may have run kernels whose waits are bounded (TMA + tcgen05): a wait that

@@ -22,6 +22,7 @@ import torch
 from ..cache import CachePool
 from ..kernels import ops
 from ..kernels.library import host
+from ..parts import AttentionLike
 from .attention_dispatch import run_attention
 
 
@@ -68,6 +69,7 @@ class StepContext:
         self.max_seg_rows = 0
         self.max_ctx = 0
         self.pool: Optional[CachePool] = None
+        self.position_encoding = None          # the model's position encoding: mixers call it if it acts inside them
         self.runner = None
         self.fixed_shapes = False              # the step is being captured for replay: no size may depend on this batch
         self.max_positions = 0
@@ -110,9 +112,7 @@ class ModelRunner:
         self._copied = None    # event after the last host->device copy of the packed buffer
         self._stream_obj = None
         # decode-only steps replay a captured CUDA graph unless a part reads device values on the host
-        self.use_graphs = all(getattr(part, "capturable", True)
-                              for layer in model.layers for _, part in layer.parts()) \
-            and getattr(model.position, "capturable", True) and getattr(model.final_norm, "capturable", True)
+        self.use_graphs = all(getattr(part, "capturable", True) for _, part in model.all_parts())
         self._graphs: Dict[tuple, tuple] = {}    # (rows of a decode-only step, context class) -> (graph, logits)
         # Steps with prompt portions: a step's SHAPE (tokens and wanted rows per entry, in order) fixes every launch
         # of it; what differs between two steps of one shape (tokens, positions, block tables, wanted rows) is in
@@ -128,7 +128,7 @@ class ModelRunner:
         worst = heads = 0
         for layer in model.layers:
             m = layer.mixer
-            if hasattr(m, "n_head") and hasattr(m, "head_dim"):
+            if isinstance(m, AttentionLike):
                 worst = max(worst, ops.decode_scratch_floats(S, m.n_head, m.head_dim, 32))
                 heads = max(heads, m.n_head)
         self._scratch = torch.empty(max(worst, 1), dtype=torch.float32, device=self.device)
@@ -208,6 +208,7 @@ class ModelRunner:
         T, S, R = info.n_rows, info.n_segments, info.n_logit_rows
         ctx = StepContext()
         ctx.dtype, ctx.pool, ctx.error_flag = self.model.dtype, pool, self.error_flag
+        ctx.position_encoding = self.model.position
         ctx.runner, ctx.max_positions, ctx.fixed_shapes = self, self.model.spec.max_positions, bool(pad_rows) or fixed_shapes
         ctx.n_rows, ctx.n_segments, ctx.n_logit_rows, ctx.n_decode = T, S, R, info.n_decode
         ctx.tokens, ctx.positions, ctx.row_seq = (self._dev_view(n, T) for n in ("tokens", "positions", "row_seq"))
@@ -286,14 +287,17 @@ class ModelRunner:
         if seen[0] < self.shape_graph_after or seen[1] < self.shape_graph_min_host_s:
             return None
         ctx = self.build_context(entries, fixed_shapes=True)
-        self.model.forward(ctx)                           # warm-up outside the capture (writes the same cache values)
+        # The step itself runs ONCE, launch by launch, with the launches the graph will hold; the capture that
+        # follows records them without running them, and the recorded step's output buffer takes this run's
+        # logits.  (Running it a second time through the fresh graph would be harmless for keys and values,
+        # which are written alike both times, but would move a mixer's own per-request state on twice.)
+        first = self.model.forward(ctx)
         graph, logits = capture_graph(lambda: self.model.forward(ctx))
+        logits.copy_(first)
         while len(self._shape_graphs) >= self.max_shape_graphs:
             self._shape_graphs.popitem(last=False)        # the shape not used for the longest time makes room
         self._shape_graphs[shape] = (graph, logits)
         self.shape_captures += 1
-        graph.replay()
-        self.graph_replays += 1
         return logits
 
     def _decode_step_graph(self, entries, native: bool) -> torch.Tensor:
@@ -309,11 +313,14 @@ class ModelRunner:
         have = self._graphs.get((rows, limit))
         if have is None:
             ctx = self.build_context(entries, pad_rows=rows, all_logits=True, ctx_limit=limit)
-            self.model.forward(ctx)                       # warm-up outside the capture (writes the same cache values)
+            first = self.model.forward(ctx)               # this step runs once, launch by launch; the capture only records
             have = self._graphs[(rows, limit)] = capture_graph(lambda: self.model.forward(ctx))
-        graph, logits = have
-        graph.replay()
-        self.graph_replays += 1
+            graph, logits = have
+            logits.copy_(first)
+        else:
+            graph, logits = have
+            graph.replay()
+            self.graph_replays += 1
         want = [i for i, e in enumerate(entries) if (e.sample if native else len(e.want))]
         if len(want) == rows:
             return logits

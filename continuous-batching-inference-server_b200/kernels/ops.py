@@ -87,8 +87,12 @@ def _need_cuda(*ts):
             raise KernelError("kernels take CUDA tensors only; there is no CPU path")
 
 
-def embed_pos_add(tokens, positions, wte, wpe, out, err):
-    """out[r] = wte[tokens[r]] + wpe[positions[r]] in 32-bit; err (int32[1]) is set on a bad index."""
+NORM_MAX_WIDTH = 200 * 1024 // 4 - 33     # the widest row add_layernorm takes (cbis_norm_max_width() says the same)
+ATTENTION_MAX_HEAD_DIM = 256             # the general attention kernel's limit; the tiled ones take less and say so
+
+
+def embed_pos_add(tokens, positions, wte, wpe, out, err, multiplier: float = 1.0):
+    """out[r] = wte[tokens[r]] * multiplier + wpe[positions[r]] in 32-bit; err (int32[1]) is set on a bad index."""
     _need_cuda(tokens, positions, wte, wpe, out, err)
     T, d = out.shape
     assert out.dtype == torch.float32 and out.is_contiguous() and wte.is_contiguous()
@@ -96,19 +100,21 @@ def embed_pos_add(tokens, positions, wte, wpe, out, err):
     st = kernels().cbis_embed_pos_add(_ptr(tokens), _ptr(positions), _ptr(wte), _ptr(wpe), _ptr(out),
                                       c_int(T), c_int(d), c_int(wte.shape[0]),
                                       c_int(wpe.shape[0] if wpe is not None else 0),
-                                      c_int(dtype_code(wte.dtype)), _ptr(err), _stream())
+                                      c_int(dtype_code(wte.dtype)), c_float(multiplier), _ptr(err), _stream())
     _check(st, "embed_pos_add", f"T={T} d={d}")
 
 
 def add_layernorm(x, delta, delta_bias, gamma, beta, eps, out, rows=None):
     """x += delta + delta_bias (32-bit, in place unless ``rows``); out = LayerNorm(x) * gamma + beta.
 
-    ``rows`` (int32[R]) selects source rows: out[r] = LN(x[rows[r]] + ...), x is left as it is."""
+    ``rows`` (int32[R]) selects source rows: out[r] = LN(x[rows[r]] + ...), x is left as it is.
+    ``gamma`` None: no normalisation, out = x + delta + delta_bias in ``out``'s dtype."""
     _need_cuda(x, delta, delta_bias, gamma, beta, out, rows)
     d = x.shape[-1]
     R = rows.shape[0] if rows is not None else x.shape[0]
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == d
-    assert gamma.dtype == torch.float32 and beta.dtype == torch.float32
+    assert gamma is None or gamma.dtype == torch.float32
+    assert beta is None or (gamma is not None and beta.dtype == torch.float32)
     assert delta is None or (delta.is_contiguous() and delta.shape == x.shape)
     assert delta_bias is None or delta_bias.dtype == torch.float32
     assert out.shape[0] >= R
@@ -126,6 +132,15 @@ def bias_act(x, bias, act):
     st = kernels().cbis_bias_act(_ptr(x), _ptr(bias), c_int(ACT[act]), c_int(M), c_int(N),
                                  c_int(dtype_code(x.dtype)), _stream())
     _check(st, "bias_act", f"M={M} N={N}")
+
+
+def scale_soft_cap(x, scale: float, cap: float):
+    """x = cap * tanh(x * scale / cap) if cap > 0 else x * scale, in place on 32-bit values."""
+    _need_cuda(x)
+    M, N = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    st = kernels().cbis_scale_soft_cap(_ptr(x), c_float(scale), c_float(cap), c_int(M), c_int(N), _stream())
+    _check(st, "scale_soft_cap", f"M={M} N={N}")
 
 
 def bias_act_out(src, bias, act, dst):
@@ -225,6 +240,7 @@ def raise_if_kernel_errors(device="cuda") -> None:
         code = int(flag.item())
         if code:
             flag.zero_()
+            _tc_pending.pop(key, None)      # a copy of the flag asked for earlier would report the same event again
             raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
                               f"product, 11-19 the prefill attention); the step's results are invalid")
 
@@ -267,17 +283,21 @@ def tcgen05_error_flag(device) -> torch.Tensor:
     return _tc_error[key]
 
 
-def gemm_tcgen05(x, w_nk, bias, act, out):
+def gemm_tcgen05(x, w_nk, bias, act, out, spin_limit: int = 0, starve: bool = False):
     """out = act(x @ w_nk^T + bias) on the tcgen05 tensor cores (TMA operands, accumulator in tensor
-    memory, bias and activation on the 32-bit sums).  bfloat16, K a multiple of 8."""
+    memory, bias and activation on the 32-bit sums).  bfloat16, K a multiple of 8.
+    ``spin_limit`` (0: the service limit) bounds every wait inside the kernel; ``starve`` (up to 128 rows,
+    for the test of the give-up path) makes the kernel request no operands, so that its waits run out:
+    it then sets the error flag (``tcgen05_error_flag``), frees its tensor memory and returns."""
     _need_cuda(x, w_nk, bias, out)
     M, K = x.shape
     N = w_nk.shape[0]
     assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
-    st = kernels().cbis_gemm_tcgen05_bf16(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
-                                          c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
-                                          c_int(dtype_code(out.dtype)), _ptr(tcgen05_error_flag(x.device)), _stream())
+    st = kernels().cbis_gemm_tcgen05_bf16_ex(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
+                                             c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
+                                             c_int(dtype_code(out.dtype)), _ptr(tcgen05_error_flag(x.device)), _stream(),
+                                             ctypes.c_uint(spin_limit), c_int(1 if starve else 0))
     _check(st, "gemm_tcgen05", f"M={M} N={N} K={K}")
 
 
@@ -546,6 +566,7 @@ def slots_from_table(positions, row_seq, block_table, page_size, slot_mapping, n
 
 
 _sample_scratch = {}
+_sample_outgrown = []     # buffers that a later call outgrew: a captured graph may still hold their addresses
 
 
 def _sample_buffers(device, R: int, chunks: int):
@@ -557,6 +578,8 @@ def _sample_buffers(device, R: int, chunks: int):
         if torch.cuda.is_current_stream_capturing():
             raise KernelError("sampling scratch would have to grow during graph capture")
         n = max(R * chunks, 64 * 64)
+        if have is not None:
+            _sample_outgrown.append(have)
         have = (torch.empty(n, dtype=torch.float32, device=device), torch.empty(n, dtype=torch.int32, device=device),
                 torch.zeros(max(R, 1024), dtype=torch.int32, device=device))
         _sample_scratch[key] = have

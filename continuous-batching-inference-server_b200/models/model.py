@@ -14,7 +14,7 @@ import torch
 
 from ..config import ModelSpec, load_config
 from ..kernels import ops
-from ..parts import (make_block, make_feed_forward, make_mixer, make_norm, make_position)
+from ..parts import (make_block, make_embedding, make_feed_forward, make_head, make_mixer, make_norm, make_position)
 from ..weights import TensorDecl, check_tensors, read_model_tensors
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -48,8 +48,12 @@ class Layer:
 
 
 class Model:
+    """Embedding, layers in the order of the schedule, final norm and head: each a part built from its
+    ``PartSpec`` through the registries.  This class decides nothing about the architecture."""
+
     def __init__(self, spec: ModelSpec):
         self.spec = spec
+        self.embedding = make_embedding(spec.embedding_spec())
         self.position = make_position(spec.position)
         self.layers: List[Layer] = [Layer(ls, i) for i, ls in enumerate(spec.layers)]
         for i in spec.schedule:
@@ -59,37 +63,41 @@ class Model:
             if ls.cache_source is not None and not 0 <= ls.cache_source < len(self.layers):
                 raise ValueError(f"layer {ls.prefix!r} reads the cache of layer {ls.cache_source}, which does not exist")
         self.final_norm = make_norm(spec.final_norm)
-        self.token_table: Optional[torch.Tensor] = None
-        self.head: Optional[torch.Tensor] = None
+        self.head_part = make_head(spec.head_spec())
         self.dtype: Optional[torch.dtype] = None
         self.device = None
 
+    @property
+    def token_table(self) -> Optional[torch.Tensor]:
+        return self.embedding.table
+
+    @property
+    def head(self) -> Optional[torch.Tensor]:
+        """The head's matrix ``[vocab, width]`` (the token table itself when the head is tied)."""
+        return getattr(self.head_part, "weight", None)
+
+    def all_parts(self):
+        """(tensor-name prefix, part) of every part of the model, in loading order."""
+        out = [("", self.embedding), ("", self.position)]
+        for layer in self.layers:
+            out += layer.parts()
+        return out + [(self.spec.final_norm_prefix, self.final_norm), ("", self.head_part)]
+
     # ---- weights -------------------------------------------------------
     def declared(self) -> List[TensorDecl]:
-        s = self.spec
-        decls = [TensorDecl(s.token_embedding, (s.vocab_size, s.width), "table")]
-        decls += self.position.tensors("")
-        for layer in self.layers:
-            for prefix, part in layer.parts():
-                decls += part.tensors(prefix)
-        decls += self.final_norm.tensors(s.final_norm_prefix)
-        if s.head is not None:
-            decls.append(TensorDecl(s.head, (s.vocab_size, s.width), "matrix"))
+        decls = []
+        for prefix, part in self.all_parts():
+            decls += part.tensors(prefix)
         return decls
 
     def load(self, tensors: Dict[str, torch.Tensor], dtype, device="cuda", where="weights") -> "Model":
         dtype = resolve_dtype(dtype)
         check_tensors(self.declared(), tensors, self.spec.ignored_tensors, where)
-        s = self.spec
         self.dtype, self.device = dtype, torch.device(device)
-        self.token_table = tensors[s.token_embedding].to(device=device, dtype=dtype).contiguous()
-        self.position.load("", tensors, dtype, device)
-        for layer in self.layers:
-            for prefix, part in layer.parts():
-                part.load(prefix, tensors, dtype, device)
-        self.final_norm.load(s.final_norm_prefix, tensors, dtype, device)
-        self.head = (self.token_table if s.head is None
-                     else tensors[s.head].to(device=device, dtype=dtype).contiguous())
+        for prefix, part in self.all_parts():
+            if part is self.head_part:
+                part.tie(self.embedding)
+            part.load(prefix, tensors, dtype, device)
         self.register_weight_order()
         return self
 
@@ -101,37 +109,33 @@ class Model:
         for li in self.spec.schedule:
             layer = self.layers[li]
             order += layer.mixer.streamed_weights() + layer.feed_forward.streamed_weights()
-        ops.add_weight_order(order + [self.head])
+        ops.add_weight_order(order + self.head_part.streamed_weights())
 
     def weight_bytes(self) -> int:
-        """Bytes of all weights a step reads (each once; a tied head counts once)."""
+        """Bytes of all weights a step reads (each once; a tied head counts once; of the embedding's and the
+        position encoding's tables a step reads single rows, which do not count)."""
         seen, total = set(), 0
         def add(t):
             nonlocal total
             if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
-        add(self.head)
-        for layer in self.layers:
-            for _, part in layer.parts():
-                for v in vars(part).values():
-                    add(v)
-        for v in vars(self.final_norm).values():
-            add(v)
+        for _, part in self.all_parts():
+            if part is self.embedding or part is self.position:
+                continue
+            for v in vars(part).values():
+                add(v)
         return total
 
     # ---- one step ------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Logits (float32 ``[R, vocab]``) at ``ctx.logit_rows`` for the rows of this step."""
-        x = self.position.embed(ctx, self.token_table)
+        x = self.embedding.forward(ctx, self.position)
         pending = None
         for li in self.spec.schedule:
             layer = self.layers[li]
             pending = layer.block.forward(ctx, x, pending, ctx.layer_cache(li), ctx.layer_state(li))
-        if ctx.n_logit_rows == 0:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=x.device)
-        h = self.final_norm.forward(ctx, x, pending, rows=ctx.logit_rows)
-        return ops.linear(h, self.head, None, None, out_dtype=torch.float32)
+        return self.head_part.forward(ctx, x, pending, self.final_norm)
 
 
 def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:

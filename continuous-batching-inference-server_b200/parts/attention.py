@@ -21,6 +21,9 @@ class PagedAttention(Mixer):
                  own_kv: bool = True, names=("attn.c_attn", "attn.c_proj")):
         if n_head % n_kv_head:
             raise ValueError(f"n_head={n_head} is not a multiple of n_kv_head={n_kv_head}")
+        if not 0 < int(head_dim) <= ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError(f"head_dim={head_dim} is outside 1..{ops.ATTENTION_MAX_HEAD_DIM}, the largest head "
+                             f"any attention kernel takes")
         self.width, self.n_head, self.n_kv_head, self.head_dim = int(width), int(n_head), int(n_kv_head), int(head_dim)
         self.scale, self.window, self.own_kv = float(scale), int(window), bool(own_kv)
         self.qkv_name, self.proj_name = names
@@ -33,7 +36,7 @@ class PagedAttention(Mixer):
         return self.d_q + (2 * self.d_kv if self.own_kv else 0)
 
     def cache_need(self):
-        return CacheNeed(self.n_kv_head, self.head_dim, self.window) if self.own_kv else None
+        return CacheNeed.keys_values(self.n_kv_head, self.head_dim, self.window) if self.own_kv else None
 
     def tensors(self, prefix):
         return [TensorDecl(f"{prefix}{self.qkv_name}.weight", (self.width, self.qkv_width)),
@@ -54,6 +57,10 @@ class PagedAttention(Mixer):
         if cache is None:
             raise RuntimeError("attention needs a cache: its own or the layer's it reads")
         qkv = ops.linear(h, self.w_qkv, self.b_qkv)
+        pe = ctx.position_encoding
+        if pe is not None and pe.acts_in_mixer:      # e.g. a rotation of queries and keys, before the keys are cached
+            pe.apply_in_mixer(ctx, qkv[:, :self.d_q], qkv[:, self.d_q:self.d_q + self.d_kv] if self.own_kv else None,
+                              self.head_dim)
         view = ctx.groups[cache.group]
         out = torch.empty((ctx.n_rows, self.d_q), dtype=qkv.dtype, device=qkv.device)
         ctx.attention(self, qkv, cache, view, out)      # stores this step's k, v (if own_kv), then attends

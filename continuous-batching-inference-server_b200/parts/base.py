@@ -4,8 +4,9 @@ A part gets its sizes and constants as constructor parameters (from a ``PartSpec
 declares the tensors it needs under a name prefix, takes them at load time, and is
 run by a block with a ``StepContext``.  No part knows which model or which layer it
 is in.  New kinds are added with ``register_mixer`` / ``register_feed_forward`` /
-``register_norm`` / ``register_position`` / ``register_block``; a configuration then
-names them in its ``ModelSpec``.
+``register_norm`` / ``register_position`` / ``register_block`` / ``register_embedding`` /
+``register_head``; a configuration then names them in its ``ModelSpec``.  A part refuses sizes
+that no kernel takes in its constructor, so a model that cannot run fails when it is built.
 
 Values that flow between parts:
 
@@ -17,7 +18,7 @@ Values that flow between parts:
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional, Tuple
+from typing import Callable, Dict, List, Optional, Protocol, Tuple, runtime_checkable
 
 import torch
 
@@ -32,12 +33,44 @@ class Delta:
 
 
 @dataclass(frozen=True)
+class CacheArray:
+    """One array a mixer keeps per token: ``heads`` x ``width`` elements of the compute dtype.  The pool
+    stores it in pages ``[num_pages, heads, page_size, width]``, so a (page, head) tile is one run."""
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
 class CacheNeed:
-    """Keys and values a mixer keeps per token: pages of ``[n_kv_head, page_size, head_dim]``.
-    ``window`` 0 keeps every token; w > 0 keeps only what queries at later positions can reach."""
+    """What a mixer keeps per token, as a list of named arrays (attention: "k" and "v" of
+    ``[n_kv_head, head_dim]``; a mixer with one compressed vector per token: one array of one head).
+    ``window`` 0 keeps every token; w > 0 keeps only what queries at later positions can reach.
+    Layers whose needs are equal share a group: one pool of pages, one block table per request."""
+    arrays: Tuple[CacheArray, ...]
+    window: int = 0
+
+    @staticmethod
+    def keys_values(n_kv_head: int, head_dim: int, window: int = 0) -> "CacheNeed":
+        return CacheNeed((CacheArray("k", n_kv_head, head_dim), CacheArray("v", n_kv_head, head_dim)), window)
+
+    def elements_per_token(self) -> int:
+        return sum(a.heads * a.width for a in self.arrays)
+
+
+@runtime_checkable
+class AttentionLike(Protocol):
+    """What ``StepContext.attention`` reads off a mixer to choose and run an attention kernel over the
+    mixer's "k" and "v" pages.  ``qkv`` handed to it has the columns q (``d_q``), then k and v
+    (``d_kv`` each) if ``own_kv``; with ``own_kv`` False only q, and the pages of another layer are read."""
+    n_head: int
     n_kv_head: int
     head_dim: int
-    window: int = 0
+    d_q: int
+    d_kv: int
+    own_kv: bool
+    window: int
+    scale: float
 
 
 @dataclass(frozen=True)
@@ -91,7 +124,9 @@ class Mixer(Part):
         return None
 
     def forward(self, ctx, h: torch.Tensor, cache, state: Optional[torch.Tensor]) -> Delta:
-        """``cache``: the ``LayerCache`` of this layer (or of the layer it reads), None if it keeps none.
+        """``cache``: the ``LayerCache`` of this layer (or of the layer it reads), None if it keeps none;
+        ``cache.arrays[name]`` are its pages ``[num_pages, heads, page_size, width]``, addressed through
+        ``ctx.groups[cache.group]`` (block table per segment, token slot per row).
         ``state``: ``[max_requests, *shape]`` if it declared a state; row ``ctx.seg_slot[s]`` belongs to segment s."""
         raise NotImplementedError
 
@@ -111,10 +146,39 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     """Position information.  ``embed`` makes the residual stream of a step from its tokens
-    (a lookup in the token table plus whatever the encoding adds at the input); encodings that
-    act inside a mixer are handed to mixers through ``StepContext.position``."""
+    (a lookup in the token table, times ``multiplier`` if the embedding has one, plus whatever the
+    encoding adds at the input).  An encoding that acts inside the mixers instead (a rotation of
+    queries and keys) sets ``acts_in_mixer`` and defines ``apply_in_mixer``; a mixer finds the
+    model's encoding as ``ctx.position_encoding`` and calls it on its queries and keys BEFORE the
+    keys go into the cache, so a cached page holds keys as the scores need them."""
+
+    acts_in_mixer = False
 
     def embed(self, ctx, token_table: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def apply_in_mixer(self, ctx, q: torch.Tensor, k: Optional[torch.Tensor], head_dim: int) -> None:
+        """Changes ``q`` ``[T, n_head * head_dim]`` and ``k`` ``[T, n_kv_head * head_dim]`` (views, maybe
+        strided; k None for a mixer without keys of its own) in place by ``ctx.positions``."""
+
+
+class Embedding(Part):
+    """The model's input: the residual stream (float32 ``[T, width]``) of a step's tokens.  ``table`` is
+    the token table, which a head may share."""
+
+    table: Optional[torch.Tensor] = None
+
+    def forward(self, ctx, position: PositionEncoding) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The model's output: float32 logits ``[R, vocab]`` at the rows ``ctx.logit_rows``."""
+
+    def tie(self, embedding: Embedding) -> None:
+        """Called after the embedding is loaded and before ``load``: a tied head takes the table here."""
+
+    def forward(self, ctx, x: torch.Tensor, pending: Optional[Delta], final_norm: Norm) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -136,6 +200,8 @@ _FEED_FORWARDS: Dict[str, Callable[..., FeedForward]] = {}
 _NORMS: Dict[str, Callable[..., Norm]] = {}
 _POSITIONS: Dict[str, Callable[..., PositionEncoding]] = {}
 _BLOCKS: Dict[str, Callable[..., Block]] = {}
+_EMBEDDINGS: Dict[str, Callable[..., Embedding]] = {}
+_HEADS: Dict[str, Callable[..., Head]] = {}
 
 
 def register_mixer(kind: str, factory) -> None:
@@ -158,6 +224,14 @@ def register_block(kind: str, factory) -> None:
     _BLOCKS[kind] = factory
 
 
+def register_embedding(kind: str, factory) -> None:
+    _EMBEDDINGS[kind] = factory
+
+
+def register_head(kind: str, factory) -> None:
+    _HEADS[kind] = factory
+
+
 def _make(table, what, spec, **extra):
     if spec.kind not in table:
         raise KeyError(f"unknown {what} kind {spec.kind!r}; known: {sorted(table)}")
@@ -178,6 +252,14 @@ def make_norm(spec) -> Norm:
 
 def make_position(spec) -> PositionEncoding:
     return _make(_POSITIONS, "position encoding", spec)
+
+
+def make_embedding(spec) -> Embedding:
+    return _make(_EMBEDDINGS, "embedding", spec)
+
+
+def make_head(spec) -> Head:
+    return _make(_HEADS, "head", spec)
 
 
 def make_block(kind: str, mixer, feed_forward, norm_mixer, norm_feed_forward) -> Block:

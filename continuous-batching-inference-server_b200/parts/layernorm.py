@@ -16,11 +16,13 @@ class LayerNorm(Norm):
 
     def __init__(self, width: int, eps: float):
         self.width, self.eps = int(width), float(eps)
+        if not 0 < self.width <= ops.NORM_MAX_WIDTH:
+            raise ValueError(f"LayerNorm: width {self.width} is outside 1..{ops.NORM_MAX_WIDTH}, the widest row the kernel takes")
         self.weight = self.bias = None
 
     def tensors(self, prefix):
-        return [TensorDecl(prefix + "weight", (self.width,), "vector"),
-                TensorDecl(prefix + "bias", (self.width,), "vector")]
+        return [TensorDecl(prefix + "weight", (self.width,), "norm_weight"),
+                TensorDecl(prefix + "bias", (self.width,), "norm_bias")]
 
     def load(self, prefix, tensors, dtype, device):
         self.weight = self._vector(tensors[prefix + "weight"], device)
@@ -34,4 +36,21 @@ class LayerNorm(Norm):
         return out
 
 
+class NoNorm(Norm):
+    """No normalisation: adds what is pending to the residual stream and hands the rows on in the
+    compute dtype (for a model without a final norm)."""
+
+    def __init__(self, width: int):
+        self.width = int(width)
+        if not 0 < self.width <= ops.NORM_MAX_WIDTH:
+            raise ValueError(f"width {self.width} is outside 1..{ops.NORM_MAX_WIDTH}, the widest row the kernel takes")
+
+    def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
+        n = rows.shape[0] if rows is not None else x.shape[0]
+        out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)
+        ops.add_layernorm(x, delta.value if delta else None, delta.bias if delta else None, None, None, 0.0, out, rows)
+        return out
+
+
 register_norm("layernorm", LayerNorm)
+register_norm("none", NoNorm)

@@ -23,9 +23,9 @@ class LearnedPositions(PositionEncoding):
     def load(self, prefix, tensors, dtype, device):
         self.table = self._matrix(tensors[prefix + self.tensor], dtype, device)
 
-    def embed(self, ctx, token_table):
+    def embed(self, ctx, token_table, multiplier: float = 1.0):
         x = torch.empty((ctx.n_rows, self.width), dtype=torch.float32, device=token_table.device)
-        ops.embed_pos_add(ctx.tokens, ctx.positions, token_table, self.table, x, ctx.error_flag)
+        ops.embed_pos_add(ctx.tokens, ctx.positions, token_table, self.table, x, ctx.error_flag, multiplier)
         return x
 
 
@@ -35,9 +35,9 @@ class NoPositions(PositionEncoding):
     def __init__(self, width: int):
         self.width = int(width)
 
-    def embed(self, ctx, token_table):
+    def embed(self, ctx, token_table, multiplier: float = 1.0):
         x = torch.empty((ctx.n_rows, self.width), dtype=torch.float32, device=token_table.device)
-        ops.embed_pos_add(ctx.tokens, ctx.positions, token_table, None, x, ctx.error_flag)
+        ops.embed_pos_add(ctx.tokens, ctx.positions, token_table, None, x, ctx.error_flag, multiplier)
         return x
 
 

@@ -18,16 +18,25 @@ import torch
 from .safetensors_io import WeightsError, read_safetensors
 
 
+ROLES = ("matrix", "table", "vector", "norm_weight", "norm_bias")
+
+
 @dataclass(frozen=True)
 class TensorDecl:
     """A tensor that a part expects: full name, shape, and role.
 
     role "matrix" / "table": used by matrix products or row lookups, held in the
-    compute dtype; "vector": biases and norm parameters, always applied in 32-bit.
+    compute dtype; "vector": a bias, "norm_weight" / "norm_bias": the scale and shift of
+    a norm; these three are always applied in 32-bit.  The role, never the name, tells
+    the random-weights mode how to draw a tensor (a norm's scale is drawn around 1).
     """
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
+
+    def __post_init__(self):
+        if self.role not in ROLES:
+            raise ValueError(f"tensor {self.name!r}: role {self.role!r} is not one of {sorted(ROLES)}")
 
 
 def _stored_form(t: torch.Tensor) -> torch.Tensor:

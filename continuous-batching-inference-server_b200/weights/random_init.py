@@ -28,26 +28,26 @@ class InitScheme:
 
 
 def random_tensors(declared: Sequence[TensorDecl], seed: int, scheme: InitScheme = InitScheme(),
-                   dtype: torch.dtype = torch.bfloat16, device: str = "cpu") -> Dict[str, torch.Tensor]:
+                   dtype: torch.dtype = torch.bfloat16, device: str = "cpu",
+                   draw_on: str = None) -> Dict[str, torch.Tensor]:
+    """One tensor per declaration, on ``device``.  How a tensor is drawn follows from its declared
+    role alone.  ``draw_on`` names the device whose generator draws the values (default: ``device``):
+    torch's CPU and CUDA generators give different values for one seed, so values that another
+    program has to draw again (a plain implementation on the CPU) are drawn with ``draw_on="cpu"``."""
+    draw_on = draw_on or device
+    by_role = {"norm_weight": (1.0, scheme.norm_weight_std), "norm_bias": (0.0, scheme.norm_bias_std),
+               "vector": (0.0, scheme.bias_std), "matrix": (0.0, scheme.matrix_std),
+               "table": (0.0, scheme.matrix_std)}
     out = {}
     for d in declared:
-        g = torch.Generator(device=device)
+        g = torch.Generator(device=draw_on)
         g.manual_seed((int(seed) * 1000003 + zlib.crc32(d.name.encode())) & 0x7FFFFFFFFFFFFFFF)
-        is_norm = ".ln_" in d.name or d.name.startswith("ln_") or "norm" in d.name
-        if d.role == "vector":
-            if d.name.endswith("weight") and is_norm:
-                mean, std = 1.0, scheme.norm_weight_std
-            elif is_norm:
-                mean, std = 0.0, scheme.norm_bias_std
-            else:
-                mean, std = 0.0, scheme.bias_std
-        else:
-            mean, std = 0.0, scheme.matrix_std
+        mean, std = by_role[d.role]
         if std == 0.0:
             t = torch.full(d.shape, mean, dtype=torch.float32, device=device)
         else:
-            t = torch.empty(d.shape, dtype=torch.float32, device=device).normal_(mean, std, generator=g)
-        out[d.name] = t.to(dtype)
+            t = torch.empty(d.shape, dtype=torch.float32, device=draw_on).normal_(mean, std, generator=g)
+        out[d.name] = t.to(dtype).to(device)
     return out
 
 

@@ -44,13 +44,14 @@ class Trace:
         return worst
 
 
-def run_trace(trace, folder, dtype, out_dir, max_tokens=None, page_size=None, timeout=600):
+def run_trace(trace, folder, dtype, out_dir, max_tokens=None, page_size=None, timeout=600, env=None):
     cmd = [sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
            "--max-tokens", str(max_tokens or trace.live_tokens_bound())]
     if page_size:
         cmd += ["--page-size", str(page_size)]
     text = "".join(json.dumps(s) + "\n" for s in trace.steps)
-    r = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
+    r = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout,
+                       env=dict(os.environ, **env) if env else None)
     assert r.returncode == 0, f"trace_run failed:\n{r.stdout[-2000:]}\n{r.stderr[-4000:]}"
     done = [l for l in r.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {i}" for i in range(len(trace.steps))], r.stdout[-2000:]

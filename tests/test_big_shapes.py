@@ -1,11 +1,16 @@
-"""The layer sizes of the benchmark configuration (width 2048, 16 heads of 128, inner 8192, vocabulary
-50257) with two layers (GPU): here the kernels for head size 128 run inside the engine - the tiled
-prefill attention, the split-KV decode attention, the few-rows product, the library product - and every
-way of cutting a request must give the logits of the 32-bit path, which stands in for the plain
-implementation at sizes where that one is too slow."""
+"""The layer sizes of the benchmark configurations (width 2048, 16 heads of 128, inner 8192, vocabulary
+50257; and the GPT-2 XL sizes) with two layers (GPU): here the kernels for head sizes 128 and 64 run inside
+the engine - the tiled prefill attention, the split-KV decode attention, the few-rows product, the TMA +
+tcgen05 products.  The 32-bit path is compared with the plain implementation once (its weights are drawn
+on the CPU so that the plain side can draw them again); every way of cutting a request in bfloat16 must
+then give the logits of the 32-bit path; a step shape that keeps coming back is replayed from a CUDA graph
+and must give the bits of the launch-by-launch run; and the decode loop that stays on the device gives the
+tokens of generation."""
 import numpy as np
 import pytest
 import torch
+
+import plain_gpt
 
 pytestmark = pytest.mark.gpu
 
@@ -21,8 +26,10 @@ def engines(request):
     import cbis_b200 as cb
     cfg = BIG if request.param == "1.3b" else XL
     opts = dict(page_size=16, num_pages=80, max_num_seqs=4, max_batched_tokens=1024)
-    e32 = cb.Engine.from_random(cfg, seed=3, dtype="float32", weight_dtype=torch.bfloat16, **opts)
-    e16 = cb.Engine.from_random(cfg, seed=3, dtype="bfloat16", **opts)
+    # both engines hold the same bfloat16 values, drawn by the CPU's generator: the plain side draws them again
+    e32 = cb.Engine.from_random(cfg, seed=3, dtype="float32", weight_dtype=torch.bfloat16, draw_on="cpu", **opts)
+    e16 = cb.Engine.from_random(cfg, seed=3, dtype="bfloat16", draw_on="cpu", **opts)
+    e32.config_dict = e16.config_dict = cfg
     yield e32, e16
     del e32, e16
     torch.cuda.empty_cache()
@@ -88,3 +95,142 @@ def test_greedy_tokens_of_both_paths_agree_where_the_margin_allows(engines):
         for j, t in enumerate(o):
             row = lg[len(p) - 1 + j]
             assert row[t] >= row.max() - 0.03 * lg.abs().max()
+
+
+def test_32_bit_path_matches_the_plain_implementation_at_these_sizes(engines):
+    """The chain embed ... logits at head size 128 / width 2048 and at head size 64 / width 1600 (K no power of
+    two), 32-bit path against the plain implementation in float64 on the CPU, whole and with the last tokens one
+    by one.  (The reference checks its one fixed size this way: src/correctness_check.cpp:75-88.)"""
+    from cbis_b200.weights import InitScheme, random_tensors
+    e32, _ = engines
+    cfg = e32.config_dict
+    w = {k: v.double() for k, v in random_tensors(e32.model.declared(), 3, InitScheme(), torch.bfloat16).items()}
+    g = torch.Generator().manual_seed(7)
+    toks = torch.randint(0, 50257, (200,), generator=g).tolist()
+    with torch.no_grad():
+        ref = plain_gpt.forward(cfg, w, toks)
+    del w
+    scale = ref.abs().max().item()
+    whole = run_cut(e32, {"a": toks}, [[("a", 200)]])["a"].double()
+    assert (whole - ref).abs().max().item() < 1e-3 * scale
+    tail = run_cut(e32, {"a": toks}, [[("a", 190)]] + [[("a", 1)] for _ in range(10)])["a"].double()
+    assert (tail - ref).abs().max().item() < 1e-3 * scale
+
+
+def test_a_repeated_mixed_step_shape_is_replayed_from_a_graph_with_the_same_bits(engines):
+    """A 512-token portion beside two decoding rows, again and again: after a few times the shape is captured
+    (TMA + tcgen05 products and attention inside a CUDA graph) and replayed; every replayed step gives the bits
+    of the same step run launch by launch."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    _, e16 = engines
+    g = torch.Generator().manual_seed(11)
+    long_ = torch.randint(0, 50257, (512 * 7,), generator=g).tolist()
+    d1, d2 = torch.randint(0, 50257, (30,), generator=g).tolist(), torch.randint(0, 50257, (40,), generator=g).tolist()
+
+    def run(graphs):
+        r = e16.runner
+        keep = (r.shape_graphs, r.shape_graph_after, r.shape_graph_min_host_s)
+        r.shape_graphs, r.shape_graph_after, r.shape_graph_min_host_s = graphs, 3, 0.0
+        r._shape_seen.clear(); r._shape_graphs.clear()
+        c0, p0 = r.shape_captures, r.shape_replays
+        outs = []
+        try:
+            sd1, sd2 = e16.open_request(1), e16.open_request(2)
+            e16.forward_step([StepEntry(sd1, 0, d1[:20], []), StepEntry(sd2, 0, d2[:33], [])])
+            n1, n2 = 20, 33
+            for rep in range(7):
+                # 7 x 512 tokens exceed the model's 2,048 (1,024) positions: a new request every third (first) portion
+                per = 3 if e16.model.spec.max_positions >= 2048 else 1
+                if rep % per == 0:
+                    if rep:
+                        e16.close_request(sl)
+                    sl, at = e16.open_request(3), 0
+                part = long_[rep * 512:(rep + 1) * 512]
+                outs.append(e16.forward_step([StepEntry(sl, at, part, [0, 511]), StepEntry(sd1, n1, d1[n1:n1 + 1], [0]),
+                                              StepEntry(sd2, n2, d2[n2:n2 + 1], [0])]).clone())
+                at += 512; n1 += 1; n2 += 1
+            for s_ in (sl, sd1, sd2):
+                e16.close_request(s_)
+        finally:
+            r.shape_graphs, r.shape_graph_after, r.shape_graph_min_host_s = keep
+        return torch.stack(outs), r.shape_captures - c0, r.shape_replays - p0
+
+    eager, c_e, p_e = run(False)
+    graphed, c_g, p_g = run(True)
+    assert (c_e, p_e) == (0, 0) and c_g == 1 and p_g == 4        # steps 1-2 launch by launch, 3 captured, 4-7 replayed
+    assert torch.isfinite(eager).all() and torch.equal(eager, graphed)
+
+
+def test_device_decode_loop_gives_the_tokens_of_generate_at_these_sizes(engines):
+    """The loop that the benchmark times (model, argmax and the move to the next position in one graph) against
+    greedy generation through the scheduler, 80 steps, across five page edges."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    e32, e16 = engines
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, 50257, (n,), generator=g).tolist() for n in (60, 9, 33)]
+    n_new = 80
+    for eng, exact in ((e32, True), (e16, False)):
+        want = eng.generate(prompts, cb.SamplingParams(max_new_tokens=n_new))
+        slots = [eng.open_request(i) for i in range(3)]
+        first = eng.forward_step([StepEntry(s, 0, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).argmax(-1).tolist()
+        for s in slots:
+            assert eng.pool.manager.append(s, n_new)
+        loop = eng.runner.decode_loop([StepEntry(s, len(p), [t], [0]) for s, p, t in zip(slots, prompts, first)])
+        got = [[t] for t in first]
+        for o, t in zip(got, loop.last_tokens()):
+            o.append(t)
+        for _ in range(n_new - 2):
+            loop.run(1)
+            for o, t in zip(got, loop.last_tokens()):
+                o.append(t)
+        del loop
+        for s in slots:
+            eng.close_request(s)
+        if exact:
+            assert got == want
+        else:   # bfloat16: both runs choose, by the 32-bit path's scores for their own sequence, within a margin of the best
+            assert [o[:4] for o in got] == [o[:4] for o in want]
+            for p, o in zip(prompts, got):
+                lg = e32.logits(p + o[:-1]).float().cpu()
+                for j, t in enumerate(o):
+                    row = lg[len(p) - 1 + j]
+                    assert row[t] >= row.max() - 0.03 * lg.abs().max()
+
+
+def test_long_positions_change_the_split_of_the_keys_in_a_captured_step():
+    """A model with 32,768 positions: a step captured for replay sizes its split of the keys for the bound of the
+    positions, not for the step's own context, so the captured launches differ from the launch-by-launch ones;
+    the logits agree to rounding and with the 32-bit path."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    cfg = dict(architectures=["GPT2LMHeadModel"], n_layer=2, n_embd=256, n_head=2, n_inner=512, vocab_size=1031,
+               n_positions=32768, activation_function="gelu", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+    opts = dict(page_size=16, num_pages=200, max_num_seqs=2, max_batched_tokens=512)
+    e32 = cb.Engine.from_random(cfg, seed=5, dtype="float32", weight_dtype=torch.bfloat16, draw_on="cpu", **opts)
+    e16 = cb.Engine.from_random(cfg, seed=5, dtype="bfloat16", draw_on="cpu", **opts)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, 1031, (1200,), generator=g).tolist()
+
+    def run(eng, graphs):
+        r = eng.runner
+        r.shape_graphs, r.shape_graph_after, r.shape_graph_min_host_s = graphs, 2, 0.0
+        r._shape_seen.clear(); r._shape_graphs.clear()
+        outs = []
+        for rep in range(2):
+            slot = eng.open_request(rep)
+            for at in range(0, 1200, 300):
+                outs.append(eng.forward_step([StepEntry(slot, at, toks[at:at + 300], [0, 150, 299])]).clone())
+            # then token by token: decode-only steps, captured for a class of context lengths
+            outs.append(torch.cat([eng.forward_step([StepEntry(slot, 1200 + i, [toks[i]], [0])]) for i in range(3)]))
+            eng.close_request(slot)
+        return torch.cat(outs), r.shape_captures
+
+    ref, _ = run(e32, False)
+    eager, c0 = run(e16, False)
+    graphed, c1 = run(e16, True)
+    scale = ref.abs().max().item()
+    assert c0 == 0 and c1 >= 1
+    assert (eager - ref).abs().max().item() < 0.02 * scale and (graphed - ref).abs().max().item() < 0.02 * scale
+    assert (graphed - eager).abs().max().item() < 0.01 * scale

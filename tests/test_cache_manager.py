@@ -128,3 +128,20 @@ def test_random_orders_keep_the_books(seed):
     for s in list(live):
         m.release(s)
     assert all(m.free_pages(g) == groups[g][1] for g in range(2)) and m.check() == ""
+
+
+def test_pages_given_back_are_noted_for_the_debugging_mode():
+    m = make([(4, 8, 0), (4, 8, 6)])
+    a, b = m.admit(1), m.admit(2)
+    assert m.append(a, 9) and m.append(b, 5)
+    assert m.take_freed(0) == [] and m.take_freed(1) == []      # nothing is noted until it is switched on
+    m.record_freed(True)
+    m.release(b)
+    assert sorted(m.take_freed(0)) == [3, 4] and sorted(m.take_freed(1)) == [3, 4]
+    assert m.take_freed(0) == []                                 # handed over once
+    assert m.append(a, 8)                                        # 17 tokens; the window of 6 lets the first pages go
+    assert m.release_out_of_window(a) == 3                       # the next query, at 17, reads keys 12..17
+    assert m.take_freed(0) == [] and sorted(m.take_freed(1)) == [0, 1, 2]
+    m.release(a)
+    assert len(m.take_freed(0)) == 5 and len(m.take_freed(1)) == 2
+    assert m.check() == ""

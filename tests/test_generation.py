@@ -125,6 +125,91 @@ def test_preemption_gives_the_same_tokens(folder_b, dtype):
     assert tight.pool.manager.free_pages(0) == 11 and tight.pool.manager.check() == ""
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_with_freed_pages_poisoned(folder_b, dtype):
+    """The debugging mode that fills every page a request gives back with NaN before the next step: under
+    preemption (pages change hands in the middle of generation) no NaN reaches any logit, and the tokens are those
+    of an engine with room for everything."""
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_B, [9, 14, 20, 11], 3)
+    params = cb.SamplingParams(max_new_tokens=24, temperature=0.7, seed=99)
+    roomy = cb.Engine(folder_b, dtype=dtype, page_size=8, num_pages=40, max_num_seqs=4, max_batched_tokens=32)
+    want = roomy.generate(prompts, params)
+    tight = cb.Engine(folder_b, dtype=dtype, page_size=8, num_pages=11, max_num_seqs=4, max_batched_tokens=32,
+                      poison_freed_pages=True)
+    seen_nan = []
+    run_step = tight.runner.step
+    def watched(plan, borrow=False):
+        out = run_step(plan, borrow=borrow)
+        seen_nan.append(bool(torch.isnan(out).any()))
+        return out
+    tight.runner.step = watched
+    got = tight.generate(prompts, params)
+    assert tight.scheduler.preemptions() >= 1 and tight.pages_poisoned >= 4 and not any(seen_nan)
+    if dtype == "float32":
+        assert got == want
+    else:
+        check_against_plain(folder_b, prompts, got, 0.7, 99, 0, exact=False)
+    # the mode does what it says: the pages given back at the end hold NaN once the next step has been queued
+    tight.generate([prompts[0][:3]], cb.SamplingParams(max_new_tokens=1))
+    k = tight.pool.layer_cache[0].k
+    assert torch.isnan(k.float()).any() and tight.pool.manager.check() == ""
+
+
+@pytest.mark.parametrize("which", ["a", "b"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_device_decode_loop_gives_the_tokens_of_generate(folder_a, folder_b, which, dtype):
+    """The decode loop that never leaves the device (model, argmax and the move to the next position in one
+    graph, pages reserved ahead) against greedy generation through the scheduler and against the plain
+    implementation, across several page edges."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    folder, cfgd, page = (folder_a, tc.TINY_A, tc.PAGE_A) if which == "a" else (folder_b, tc.TINY_B, tc.PAGE_B)
+    n_new = 64 if which == "a" else 48                         # 4 pages of 16, 6 pages of 8
+    prompts = prompts_for(cfgd, [5, 17, 11], 21)
+    opts = dict(dtype=dtype, page_size=page, num_pages=40, max_num_seqs=4, max_batched_tokens=64)
+    want = cb.Engine(folder, **opts).generate(prompts, cb.SamplingParams(max_new_tokens=n_new))
+    eng = cb.Engine(folder, **opts)
+    if not eng.runner.use_graphs:
+        pytest.skip("no graphs")
+    slots = [eng.open_request(i) for i in range(len(prompts))]
+    first = eng.forward_step([StepEntry(s, 0, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).argmax(-1).tolist()
+    for s in slots:
+        assert eng.pool.manager.append(s, n_new)               # the pages of all steps, taken beforehand
+    loop = eng.runner.decode_loop([StepEntry(s, len(p), [t], [0]) for s, p, t in zip(slots, prompts, first)])
+    got = [[t] for t in first]
+    for o, t in zip(got, loop.last_tokens()):                  # building the loop ran its first step
+        o.append(t)
+    for _ in range(n_new - 2):
+        loop.run(1)
+        for o, t in zip(got, loop.last_tokens()):
+            o.append(t)
+    assert loop.steps_done == n_new - 1
+    if dtype == "float32":
+        assert got == want
+        cfg, w = plain_gpt.read_model_folder(folder, torch.float64)
+        assert got == [plain_gpt.generate(cfg, w, p, n_new) for p in prompts]
+    else:
+        check_against_plain(folder, prompts, got, 0.0, 0, 0, exact=False)
+        assert [o[:4] for o in got] == [o[:4] for o in want]   # later, a near-tie may send the two runs different ways
+    for s in slots:
+        eng.close_request(s)
+    assert eng.pool.manager.check() == ""
+
+
+def test_a_refused_prompt_leaves_nothing_of_the_call_behind(folder_a):
+    import cbis_b200 as cb
+    eng = cb.Engine(folder_a, dtype="float32", page_size=16, num_pages=8, max_num_seqs=2, max_batched_tokens=32)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.generate([[1, 2, 3], [4, 5], [6, 9999]], cb.SamplingParams(max_new_tokens=4))
+    assert eng.scheduler.idle() and not eng._params
+    with pytest.raises(ValueError, match="exceeds the model"):
+        eng.generate([[1, 2], [3] * 500], cb.SamplingParams(max_new_tokens=4))
+    assert eng.scheduler.idle() and not eng._params
+    out = eng.generate([[1, 2, 3]], cb.SamplingParams(max_new_tokens=4))
+    assert len(out) == 1 and len(out[0]) == 4 and eng.pool.manager.free_pages(0) == 8
+
+
 def test_eos_stops_a_request(folder_a):
     import cbis_b200 as cb
     eng = cb.Engine(folder_a, dtype="float32", page_size=16, num_pages=8, max_num_seqs=2, max_batched_tokens=32)

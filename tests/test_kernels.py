@@ -329,11 +329,18 @@ def test_decode_attention_split_kv(ops, n_head, n_kv_head, hd, ps, window, nspli
             ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
                                   scratch, counters, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
         return
+    bits_before = [t.clone().view(torch.int16) for t in (kc, vc)]
     ops.paged_decode_bf16(qkv, dq, dq + dkv, kc, vc, dev(c["bt"]), dev(row_seq), dev(positions), dev(slots), out,
                           scratch, counters, n_head, n_kv_head, hd, ps, c["scale"], window, nsplit)
     assert (out[:S].double().cpu() - c["ref"]).abs().max() < 1e-2 * max(1.0, c["ref"].abs().max().item())
     assert torch.equal(out[S].cpu(), torch.zeros(dq, dtype=torch.bfloat16))
-    assert not torch.isnan(kc.float()).any() or True
+    # the kernel wrote the S token slots of the current positions and nothing else (the padding row has slot -1)
+    written = torch.zeros(kc.shape[0], kc.shape[2], dtype=torch.bool, device="cuda")
+    for s, n in enumerate(seg_ctx):
+        written[int(c["bt"][s, (n - 1) // ps]), (n - 1) % ps] = True
+    for t, before in zip((kc, vc), bits_before):
+        changed = (t.view(torch.int16) != before).any(dim=3).any(dim=1)              # [page, offset]
+        assert torch.equal(changed, written)
     for s, n in enumerate(seg_ctx):                                                   # the kernel stored k and v
         page, off = int(c["bt"][s, (n - 1) // ps]), (n - 1) % ps
         assert torch.equal(kc[page, :, off, :].reshape(-1), qkv[s, dq:dq + dkv])
@@ -624,4 +631,66 @@ def test_prefill_attention_tcgen05_is_repeatable(ops):
 def test_prefill_attention_tcgen05_two_blocks_per_sm(ops):
     """Its shared memory, registers and tensor memory are sized so that an SM holds two blocks: one block's
     softmax runs while the other's products do."""
-    assert ops.paged_prefill_tc5_blocks_per_sm() >= 1
+    assert ops.paged_prefill_tc5_blocks_per_sm() >= 2
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(ops):
+    """The TMA + tcgen05 product is told to request no operands and to give every wait a short limit: its waits
+    for operands wait for a signal that nothing sends, run out, the kernel sets the error flag, frees its tensor
+    memory and returns (no copy in flight, no trap).  The host sees the flag as an exception that names the cause
+    and clears it; the next launch, of the same kernel with the same tensor memory, gives the right result."""
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 96, 512, 256
+    x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
+    w = dev((torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16))
+    flag = ops.tcgen05_error_flag("cuda")
+    assert flag.item() == 0
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_tcgen05(x, w, None, None, out, spin_limit=64, starve=True)
+    torch.cuda.synchronize()                                                        # it came back by itself
+    assert flag.item() != 0
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        ops.raise_if_kernel_errors("cuda")
+    assert flag.item() == 0                                                         # reported once, then cleared
+    ops.raise_if_kernel_errors("cuda")
+    ops.gemm_tcgen05(x, w, None, None, out)                                         # tensor memory was given back
+    ref = x.double() @ w.double().t()
+    assert (out.double() - ref).abs().max().item() < 1e-2 * ref.abs().max().item()
+    assert flag.item() == 0
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.gemm_tcgen05(dev(torch.zeros(300, K, dtype=torch.bfloat16)), w, None, None,
+                         torch.empty(300, N, dtype=torch.bfloat16, device="cuda"), starve=True)
+
+
+def test_error_flag_set_from_the_host_reaches_every_reporting_path(ops, folder_a):
+    """What the engine does when a kernel has reported a wait that ran out, shown by writing the flag from the
+    host: the blocking check raises and clears; the polling check raises within two calls; a bare step reports it
+    at one of the next calls or when the request is closed; the engine's own step raises."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    flag = ops.tcgen05_error_flag("cuda")
+    flag.fill_(13)
+    with pytest.raises(ops.KernelError, match="code 13"):
+        ops.raise_if_kernel_errors("cuda")
+    assert flag.item() == 0
+    flag.fill_(2)
+    with pytest.raises(ops.KernelError, match="code 2"):
+        for _ in range(3):
+            ops.poll_kernel_errors("cuda")
+            torch.cuda.synchronize()
+    assert flag.item() == 0
+    ops.poll_kernel_errors("cuda"); torch.cuda.synchronize(); ops.poll_kernel_errors("cuda")   # clean again
+    eng = cb.Engine(folder_a, dtype="bfloat16", page_size=16, num_pages=8, max_num_seqs=2, max_batched_tokens=32)
+    slot = eng.open_request(0)
+    eng.forward_step([StepEntry(slot, 0, [1, 2, 3, 4], [3])])
+    flag.fill_(11)
+    with pytest.raises(ops.KernelError, match="code 11"):
+        eng.forward_step([StepEntry(slot, 4, [5, 6], [1])])
+        eng.close_request(slot)                                 # at the latest here
+    assert flag.item() == 0
+    if eng.pool.manager.live(slot):
+        eng.close_request(slot)
+    flag.fill_(21)
+    with pytest.raises(ops.KernelError, match="code 21"):
+        eng.generate([[1, 2, 3, 4, 5]], cb.SamplingParams(max_new_tokens=2))       # a step with a prompt portion checks
+    assert flag.item() == 0

@@ -98,6 +98,31 @@ def test_replay_modes(tiny, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_freed_pages_filled_with_nan(tiny, dtype, tmp_path):
+    """The same trace in the debugging mode that overwrites every page a request gives back with NaN before the
+    next step: pages change hands many times (the pool is smaller than the requests together), and a kernel that
+    read a page its request no longer holds, or a token slot beyond its request's length in a page that was used
+    before, would put NaN into some logit.  Every logit is finite and equal to the plain implementation's."""
+    import re
+    folder, cfg, page = tiny
+    seqs = sequences_for(cfg, seed=cfg["n_layer"])
+    trace = build_trace(seqs)
+    out = str(tmp_path / "out")
+    r = run_trace(trace, folder, dtype, out, max_tokens=trace.live_tokens_bound(), page_size=page,
+                  env={"CBIS_POISON_FREED_PAGES": "1"})
+    m = re.search(r"(\d+) freed pages were filled with NaN", r.stderr)
+    assert m and int(m.group(1)) >= 20, r.stderr[-500:]
+    got = read_logits(trace, out, cfg["vocab_size"])
+    _, ref = plain_logits(folder, seqs)
+    for (rid, pos), rows in got.items():
+        scale = np.abs(ref[rid]).max()
+        tol = TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale
+        for row in rows:
+            assert np.isfinite(row).all(), f"request {rid} position {pos}: a logit is not finite"
+            assert np.abs(row.astype(np.float64) - ref[rid][pos]).max() < tol, (rid, pos)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cuts_agree_with_each_other(tiny, dtype, tmp_path):
     """The same request whole, token by token and in portions, within one run: logits at a position
     do not depend on the cut beyond rounding."""

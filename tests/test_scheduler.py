@@ -152,6 +152,24 @@ def test_admission_by_what_fits_now_is_settled_by_preemption_later():
     assert starts0 == sorted(set(starts0))                   # the older request never started over
 
 
+def test_a_preempted_request_is_recomputed_once_not_every_few_steps():
+    """The pages a preempted request gives up would let its first portion in again at once; it would then be
+    recomputed and thrown out again whenever the older request crosses a page.  It comes back only when all it
+    holds so far and a page more fit, and never in the step that threw it out."""
+    cache, sch = make(num_pages=7, page=4, max_seqs=2, budget=32, chunk=32)
+    sch.add(0, [1] * 8, 18)                                  # grows to 25 tokens: all 7 pages
+    sch.add(1, [2] * 8, 18)
+    done, plans = run_to_end(cache, sch)
+    assert set(done) == {0, 1} and all(len(o) == 18 for _, o in done.values())
+    restarts = [len(t) for plan in plans for rid, st, t, _ in plan if rid == 1 and st == 0]
+    assert sch.preemptions() == 1 and len(restarts) == 2     # its first run and ONE recomputation
+    for a, b in zip(plans, plans[1:]):                       # the step that preempts it does not hold it
+        if any(rid == 1 for rid, *_ in a) and not any(rid == 1 for rid, *_ in b):
+            assert [rid for rid, *_ in b] == [0]
+    starts0 = [st for plan in plans for rid, st, _, _ in plan if rid == 0]
+    assert starts0 == sorted(set(starts0))
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_random_workloads_finish_with_books_kept(seed):
     rng = random.Random(seed)

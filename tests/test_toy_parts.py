@@ -139,7 +139,7 @@ def test_toy_mixer_with_state_builds_and_steps(window):
     eng = cb.Engine(model, dtype="float32", page_size=4, num_pages=16 if window == 0 else 10, max_num_seqs=3,
                     max_batched_tokens=64)
     assert set(eng.pool.state) == {1} and eng.pool.state[1].shape == (3, 24)
-    assert len(eng.pool.groups) == 1 and eng.pool.groups[0].layers == [0] and eng.pool.groups[0].need.n_kv_head == 1
+    assert len(eng.pool.groups) == 1 and eng.pool.groups[0].layers == [0] and eng.pool.groups[0].need.arrays[0].heads == 1
     w = {k: v.double() for k, v in tensors.items()}
     g = torch.Generator().manual_seed(2)
     a = torch.randint(0, 40, (40,), generator=g).tolist()

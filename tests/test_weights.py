@@ -119,3 +119,42 @@ def test_loaded_dtypes_by_role(folder_b):
     assert a32.b_qkv.dtype == torch.float32 and a16.b_qkv.dtype == torch.float32      # vectors act in 32-bit
     assert m16.token_table.dtype == torch.bfloat16 and m16.head is not m16.token_table
     assert load_model.__module__ and Model is not None
+
+
+def test_random_weights_are_drawn_by_declared_role_not_by_name():
+    """A norm's scale is drawn around 1 because its declaration says so, whatever it is called; a tensor whose
+    name merely looks like a norm's is drawn as its role says."""
+    from cbis_b200.weights import InitScheme, TensorDecl, random_tensors
+    decls = [TensorDecl("rms.scale", (64,), "norm_weight"), TensorDecl("rms.shift", (64,), "norm_bias"),
+             TensorDecl("h.0.ln_1.weight", (64, 64), "matrix"), TensorDecl("out.bias", (64,), "vector")]
+    t = random_tensors(decls, 3, InitScheme(0.02, 0.5, 0.1, 0.3), torch.float32)
+    assert abs(t["rms.scale"].mean().item() - 1.0) < 0.05 and 0.05 < t["rms.scale"].std().item() < 0.2
+    assert abs(t["rms.shift"].mean().item()) < 0.15 and 0.15 < t["rms.shift"].std().item() < 0.5
+    assert abs(t["h.0.ln_1.weight"].mean().item()) < 0.01 and t["h.0.ln_1.weight"].std().item() < 0.03
+    assert 0.3 < t["out.bias"].std().item() < 0.7
+    plain = random_tensors(decls[:1], 3, InitScheme(), torch.float32)
+    assert torch.equal(plain["rms.scale"], torch.ones(64))
+    with pytest.raises(ValueError, match="role"):
+        TensorDecl("x", (1,), "gamma")
+
+
+def test_head_and_embedding_are_parts_of_the_spec():
+    """A tensor name stands for a plain token table or an untied plain head; a PartSpec names any other kind."""
+    from cbis_b200.config import PartSpec
+    spec = cb.config_from_dict(tc.TINY_B).model_spec()
+    assert spec.embedding_spec() == PartSpec("token_table", {"vocab_size": 317, "width": 96, "tensor": "wte.weight"})
+    assert spec.head_spec().params["tensor"] == "lm_head.weight"
+    m = Model(spec)
+    names = [d.name for d in m.declared()]
+    assert names[0] == "wte.weight" and names[-1] == "lm_head.weight" and len(names) == len(set(names))
+    tied = Model(cb.config_from_dict(tc.TINY_A).model_spec())
+    assert "lm_head.weight" not in [d.name for d in tied.declared()]
+
+
+def test_sizes_no_kernel_takes_are_refused_when_the_model_is_built():
+    big_head = dict(tc.TINY_A, n_embd=1040, n_head=2)                 # head size 520
+    with pytest.raises(ValueError, match="head_dim=520"):
+        Model(cb.config_from_dict(big_head).model_spec())
+    wide = dict(tc.TINY_A, n_embd=65536, n_head=512)
+    with pytest.raises(ValueError, match="width 65536"):
+        Model(cb.config_from_dict(wide).model_spec())
