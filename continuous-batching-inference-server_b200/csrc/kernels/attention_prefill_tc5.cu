@@ -601,14 +601,28 @@ CBIS_EXPORT int cbis_paged_prefill_tc5(const void* q, int q_ld, int total_rows, 
   return (int)e;
 }
 
-// How many blocks of the kernel above an SM holds at a time (it is sized for two); negative: a CUDA error.
+// How many blocks of the kernel above an SM has room for at a time (it is sized for two), worked out from what a
+// block takes (registers as compiled, dynamic + static + reserved shared memory, 256 of the 512 columns of tensor
+// memory) and what the device's SMs have; negative: a CUDA error.  (The occupancy calls of the runtime answer for
+// whole clusters and count an SM pair once; the profiler's counters show two blocks per SM at work.)
 CBIS_EXPORT int cbis_paged_prefill_tc5_blocks_per_sm() {
   auto kern = tc5::paged_prefill_tc5_kernel<128>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc5::smem_bytes(128));
+  cudaFuncAttributes fa;
+  cudaError_t e = cudaFuncGetAttributes(&fa, kern);
   if (e != cudaSuccess) return -(int)e;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  int dev = 0, smem_sm = 0, smem_reserved = 0, regs_sm = 0, threads_sm = 0;
+  e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return -(int)e;
-  int n = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, tc5::THREADS, tc5::smem_bytes(128));
-  return e == cudaSuccess ? n : -(int)e;
+  if ((e = cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev)) != cudaSuccess) return -(int)e;
+  if ((e = cudaDeviceGetAttribute(&smem_reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev)) != cudaSuccess) return -(int)e;
+  if ((e = cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev)) != cudaSuccess) return -(int)e;
+  if ((e = cudaDeviceGetAttribute(&threads_sm, cudaDevAttrMaxThreadsPerMultiProcessor, dev)) != cudaSuccess) return -(int)e;
+  const int warps = (tc5::THREADS + 31) / 32;
+  const int regs_block = warps * ((fa.numRegs * 32 + 255) / 256 * 256);          // registers come in units of 256 per warp
+  const int smem_block = (tc5::smem_bytes(128) + (int)fa.sharedSizeBytes + smem_reserved + 127) / 128 * 128;
+  int n = smem_sm / smem_block;
+  n = regs_sm / regs_block < n ? regs_sm / regs_block : n;
+  n = threads_sm / tc5::THREADS < n ? threads_sm / tc5::THREADS : n;
+  n = 512 / 256 < n ? 512 / 256 : n;                                             // tensor-memory columns
+  return n;
 }

@@ -10,6 +10,7 @@ table per REQUEST and token slots; only wanted rows reach the head; logits stay 
 """
 from __future__ import annotations
 
+import gc
 import os
 import time
 from collections import OrderedDict
@@ -335,17 +336,26 @@ class ModelRunner:
 def capture_graph(fn):
     """Captures the launches of ``fn()`` into a CUDA graph on a side stream; returns (graph, what fn returned).
     ``torch.cuda.graph`` does the same but first collects garbage and empties the allocator's cache, which costs
-    up to seconds when much memory is cached: too much for a capture in the middle of serving."""
+    up to seconds when much memory is cached: too much for a capture in the middle of serving.  What its
+    collection is for is done here by switching the cyclic garbage collector off while the capture runs: if it
+    came by in the middle and freed another engine's graphs or buffers, the memory calls that this causes would
+    end the capture with an error.  Calls of other threads do not touch the capture (thread-local mode)."""
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        graph.capture_begin()
-        try:
-            out = fn()
-        finally:
-            graph.capture_end()
+    gc_was_on = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.stream(side):
+            graph.capture_begin(capture_error_mode="thread_local")
+            try:
+                out = fn()
+            finally:
+                graph.capture_end()
+    finally:
+        if gc_was_on:
+            gc.enable()
     torch.cuda.current_stream().wait_stream(side)
     return graph, out
 

@@ -542,11 +542,12 @@ def paged_prefill_tc5(q, k_cache, v_cache, block_table, cu_rows, seg_start, out,
     _check(st, "paged_prefill_tc5", f"segments={n_seg} heads={n_head}/{n_kv_head} page={page_size} chunks={n_chunks}x{chunk_keys}")
 
 
-def paged_prefill_tc5_blocks_per_sm():
-    """How many blocks of the tcgen05 prefill attention an SM holds at a time (the kernel is sized for two)."""
+def paged_prefill_tc5_blocks_per_sm() -> int:
+    """How many blocks of the tcgen05 prefill attention an SM has room for at a time (it is sized for two): from the
+    registers, shared memory and tensor memory a block takes as compiled and what the device's SMs have."""
     n = kernels().cbis_paged_prefill_tc5_blocks_per_sm()
     if n < 0:
-        raise KernelError(f"paged_prefill_tc5: occupancy query failed with CUDA error {-n}")
+        raise KernelError(f"paged_prefill_tc5: a device query failed with CUDA error {-n}")
     return n
 
 

@@ -140,9 +140,8 @@ def test_a_repeated_mixed_step_shape_is_replayed_from_a_graph_with_the_same_bits
             e16.forward_step([StepEntry(sd1, 0, d1[:20], []), StepEntry(sd2, 0, d2[:33], [])])
             n1, n2 = 20, 33
             for rep in range(7):
-                # 7 x 512 tokens exceed the model's 2,048 (1,024) positions: a new request every third (first) portion
-                per = 3 if e16.model.spec.max_positions >= 2048 else 1
-                if rep % per == 0:
+                # two portions fill the 1,024 positions of one of the models and most of the pool: a new request then
+                if rep % 2 == 0:
                     if rep:
                         e16.close_request(sl)
                     sl, at = e16.open_request(3), 0

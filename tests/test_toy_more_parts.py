@@ -336,7 +336,7 @@ def test_mixer_with_state_of_its_own_inside_captured_steps():
     W, V, P = 24, 33, 64
     norm = PartSpec("layernorm", {"width": W, "eps": 1e-5})
     mix = PartSpec("running_sum_test", {"width": W})
-    att = PartSpec("attention", {"width": W, "n_head": 2, "n_kv_head": 2, "head_dim": 12, "scale": 0.3, "window": 0})
+    att = PartSpec("attention", {"width": W, "n_head": 2, "n_kv_head": 2, "head_dim": 12, "scale": 12 ** -0.5, "window": 0})
     ffn = PartSpec("dense", {"width": W, "inner": 40, "activation": "gelu_erf"})
     layers = (LayerSpec("h.0.", "pre_norm", mix, ffn, norm, norm), LayerSpec("h.1.", "pre_norm", att, ffn, norm, norm))
     spec = ModelSpec(W, V, P, "wte.weight", PartSpec("learned", {"width": W, "n_positions": P}), layers, (0, 1), norm,
