@@ -13,22 +13,11 @@
 // The current token's key and value can come straight from the step's projections (`k_off >= 0`):
 // the block that meets position p takes them from `qkv` and stores them into the page, so the
 // separate cache-write launch is not needed at decode.
-#include "common.cuh"
+#include "attention_decode_tc.cuh"
 #include <math.h>
 
 namespace cbis {
 
-__device__ __forceinline__ void unpack8(const uint4& r, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-constexpr int DEC_WARPS = 4;
 constexpr int DEC_U = 4;  // keys in flight per lane group
 
 // part: [rows][n_head][nsplit][hd + 2] floats: acc[hd] (not normalised), max, sum.
@@ -230,43 +219,9 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
 }
 
 // ---------------------------------------------------------------------------------------------
-// The fast form for head sizes 64 and 128 and pages of a multiple of 16 keys.  A warp takes 16
-// keys of a page at a time: K and V of the tile are each one contiguous run in the page, fetched
-// with 16-byte loads that bypass L1.  The 16 scores come from the tensor cores (mma.sync
-// m16n8k16, the query in row 0 of the A operand, the K order of both operands permuted alike so
-// that a 16-byte load of a key is two B fragments); they are scaled and masked in 32-bit, the
-// running (max, sum) is kept in 32-bit, and P*V is accumulated in 32-bit on the FP32 units from
-// the coalesced V loads.  That is about a sixth of the instructions per key of the form above,
-// which issues too many to keep up with HBM.
+// The fast form for head sizes 64 and 128 and pages of a multiple of 16 keys: decode_tc_item of
+// attention_decode_tc.cuh, one block of four warps per (row, head, split).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 ldcg16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-// Keys and values are read once per step: they are marked to leave L2 first, so that they do not push
-// out the weights that the products have prefetched.
-__device__ __forceinline__ unsigned long long l2_evict_first_policy() {
-  unsigned long long pol;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol));
-  return pol;
-}
-__device__ __forceinline__ uint4 ldcg16_stream(const void* p, unsigned long long pol) {
-  uint4 v;
-  asm volatile("ld.global.cg.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p), "l"(pol));
-  return v;
-}
-
-__device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, __nv_bfloat16* kc, __nv_bfloat16* vc,
@@ -274,203 +229,11 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
                        const int* slot_mapping, __nv_bfloat16* __restrict__ out, int out_ld, float* part,
                        unsigned int* counters, int n_head, int n_kv_head, int ps, float scale, int window,
                        int nsplit) {
-  constexpr int NC = HD / 32;        // 16-byte loads per key for the score fragments (4 lanes x 16 B = 32 dims each)
-  constexpr int LPK = HD / 8;        // lanes per key in the coalesced V loads
-  constexpr int KPL = 32 / LPK;      // keys per warp-wide V load
-  constexpr int NV = 16 / KPL;       // V loads per 16-key tile
-  __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
-  __shared__ float sm_acc[DEC_WARPS][HD];
-  __shared__ float sm_p[DEC_WARPS][16];
-  __shared__ bool is_last;
+  __shared__ DecodeTcShared<HD> sm;
   pdl_trigger();
-  // The step's tables (rows, positions, block tables) were written before the step's first kernel and the
-  // cached keys and values of earlier positions by earlier steps: they are read, and this warp's first
-  // tile is fetched, while the kernels ahead (the projection of this step's q, k, v) still run.
-  const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int seq = row_seq[row];
-  if (seq < 0) {  // a padding row of a fixed-size batch
-    pdl_wait();
-    if (split == 0)
-      for (int t = threadIdx.x; t < HD; t += blockDim.x) out[(size_t)row * out_ld + h * HD + t] = __float2bfloat16_rn(0.f);
-    return;
-  }
-  const int hk = h / (n_head / n_kv_head);
-  const int pos = positions[row];
-  const int kend = pos + 1;
-  const int kstart = window > 0 ? max(0, kend - window) : 0;
-  const int first_tile = kstart >> 4;
-  const int per = (((kend - (first_tile << 4)) + nsplit - 1) / nsplit + 31) & ~31;   // keys per split, whole tiles
-  const int ks = (first_tile << 4) + split * per;
-  const int ke = min(kend, ks + per);
-  const int* bt = block_table + (size_t)seq * max_blocks;
-  const int g = lane >> 2, t = lane & 3;
-
-  const int vsub = lane % LPK, vgrp = lane / LPK;
-  const unsigned long long pol = l2_evict_first_policy();
-  uint4 kb[2][NC], vb[NV];
-  auto load_tile = [&](int tile) {
-    const int j0 = tile << 4;
-    const int page = bt[j0 / ps];
-    const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j0 % ps)) * HD;   // 16 keys from here are one run
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
-#pragma unroll
-    for (int i = 0; i < NV; ++i) vb[i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
-  };
-  int tile = (ks >> 4) + warp;
-  // not the tile that holds the current token: its key and value are stored below, after the wait
-  bool preloaded = (tile << 4) < ke && tile != (pos >> 4);
-  if (preloaded) load_tile(tile);
-  pdl_wait();
-
-  // The current token's key and value go into their page first; the loop below then reads them
-  // like any other key.  (Blocks of query heads that share this key/value head store the same values.)
-  if (k_off >= 0 && pos >= ks && pos < ke) {
-    const int slot = slot_mapping[row];
-    if (slot >= 0 && threadIdx.x < 2 * LPK) {
-      const int which = threadIdx.x / LPK, sub = threadIdx.x % LPK;
-      const uint4 v = ldcg16(qkv + (size_t)row * ld + (which ? v_off : k_off) + hk * HD + sub * 8);
-      const size_t dst = (((size_t)(slot / ps) * n_kv_head + hk) * ps + (slot % ps)) * HD + sub * 8;
-      *reinterpret_cast<uint4*>((which ? vc : kc) + dst) = v;
-    }
-    __syncthreads();
-  }
-
-  // the query as A fragments: row 0 only, so lanes 0..3 hold it and the rest hold zeros
-  uint4 qa[NC];
-#pragma unroll
-  for (int c = 0; c < NC; ++c)
-    qa[c] = g == 0 ? ldcg16(qkv + (size_t)row * ld + h * HD + c * 32 + t * 8) : make_uint4(0, 0, 0, 0);
-
-  float m = -INFINITY, l = 0.f, acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-
-  for (; (tile << 4) < ke; tile += DEC_WARPS) {
-    const int j0 = tile << 4;
-    if (!preloaded) load_tile(tile);
-    preloaded = false;
-    // scores of the 16 keys: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1)
-    float sc[2][4];
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-#pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        mma_16816(sc[nt], qa[c].x, 0u, qa[c].y, 0u, kb[nt][c].x, kb[nt][c].y);
-        mma_16816(sc[nt], qa[c].z, 0u, qa[c].w, 0u, kb[nt][c].z, kb[nt][c].w);
-      }
-    }
-    float s4[4], mx = -INFINITY;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = j0 + (e >> 1) * 8 + 2 * t + (e & 1);
-      s4[e] = (g == 0 && j >= kstart && j < ke) ? sc[e >> 1][e & 1] * scale : -INFINITY;
-      mx = fmaxf(mx, s4[e]);
-    }
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    mx = __shfl_sync(0xffffffffu, mx, 0);
-    const float m_new = fmaxf(m, mx);
-    if (m_new == -INFINITY) continue;                 // no key of this tile is in range (uniform over the warp)
-    const float corr = expf(m - m_new);
-    if (g == 0) {
-      float psum = 0.f;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = expf(s4[e] - m_new);
-        psum += p;
-        sm_p[warp][(e >> 1) * 8 + 2 * t + (e & 1)] = p;
-      }
-      l = l * corr + psum;                            // lanes 0..3 each carry a part of the sum
-    }
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] *= corr;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const float p = sm_p[warp][i * KPL + vgrp];
-      if (p != 0.f) {                                 // keys out of range have p = 0 and whatever the page holds
-        float vf[8];
-        unpack8(vb[i], vf);
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc[d] = fmaf(p, vf[d], acc[d]);
-      }
-    }
-    __syncwarp();
-    m = m_new;
-  }
-  // merge within the warp: the sum's parts (lanes 0..3) and the accumulators of the key groups
-  l += __shfl_xor_sync(0xffffffffu, l, 1);
-  l += __shfl_xor_sync(0xffffffffu, l, 2);
-#pragma unroll
-  for (int o = LPK; o < 32; o <<= 1)
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-  if (lane == 0) {
-    sm_m[warp] = m;
-    sm_l[warp] = l;
-  }
-  if (vgrp == 0) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sm_acc[warp][vsub * 8 + i] = acc[i];
-  }
-  __syncthreads();
-  float M = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w]);
-  float wgt[DEC_WARPS], L = 0.f;
-#pragma unroll
-  for (int w = 0; w < DEC_WARPS; ++w) {
-    wgt[w] = sm_m[w] > -INFINITY ? expf(sm_m[w] - M) : 0.f;
-    L += sm_l[w] * wgt[w];
-  }
-  for (int tt = threadIdx.x; tt < HD; tt += blockDim.x) {
-    float v = 0.f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) v += sm_acc[w][tt] * wgt[w];
-    if (nsplit == 1) {
-      out[(size_t)row * out_ld + h * HD + tt] = __float2bfloat16_rn(v / L);
-    } else {
-      float* p = part + (((size_t)row * n_head + h) * nsplit + split) * (HD + 2);
-      p[tt] = v;
-      if (tt == 0) {
-        p[HD] = M;
-        p[HD + 1] = L;
-      }
-    }
-  }
-  if (nsplit == 1) return;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) is_last = atomicAdd(&counters[row * n_head + h], 1u) == (unsigned)nsplit - 1;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  // weights of the splits first (one thread per split), then every thread sums its dims over the splits
-  __shared__ float sm_w[32];
-  __shared__ float sm_inv;
-  const float* p = part + ((size_t)row * n_head + h) * nsplit * (HD + 2);
-  if (warp == 0) {
-    const float ms = lane < nsplit ? __ldcg(p + (size_t)lane * (HD + 2) + HD) : -INFINITY;
-    const float ls = lane < nsplit ? __ldcg(p + (size_t)lane * (HD + 2) + HD + 1) : 0.f;
-    const float Mx = warp_max(ms);
-    const float w = ms > -INFINITY ? expf(ms - Mx) : 0.f;
-    sm_w[lane] = w;
-    const float Ls = warp_sum(ls * w);
-    if (lane == 0) sm_inv = 1.f / Ls;
-  }
-  __syncthreads();
-  for (int tt = threadIdx.x; tt < HD; tt += blockDim.x) {
-    float v = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < nsplit; ++s) v = fmaf(__ldcg(p + (size_t)s * (HD + 2) + tt), sm_w[s], v);
-    out[(size_t)row * out_ld + h * HD + tt] = __float2bfloat16_rn(v * sm_inv);
-  }
-  if (threadIdx.x == 0) counters[row * n_head + h] = 0;
+  decode_tc_item<HD, true>(qkv, ld, k_off, v_off, kc, vc, block_table, max_blocks, row_seq, positions, slot_mapping, out,
+                           out_ld, part, counters, n_head, n_kv_head, ps, scale, window, nsplit, blockIdx.x, blockIdx.y,
+                           blockIdx.z, threadIdx.x, sm, 0);
 }
 
 // After a decode step whose next tokens were chosen on the device: the chosen token becomes the

@@ -241,8 +241,9 @@ def raise_if_kernel_errors(device="cuda") -> None:
         if code:
             flag.zero_()
             _tc_pending.pop(key, None)      # a copy of the flag asked for earlier would report the same event again
-            raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
-                              f"product, 11-19 the prefill attention); the step's results are invalid")
+            raise KernelError(f"a bounded wait inside a TMA kernel ran out (code {code}: 1-6 and 21-24 the tcgen05 "
+                              f"product, 11-19 the prefill attention, 31-34 the persistent decode kernel); the step's "
+                              f"results are invalid")
 
 
 
@@ -266,8 +267,9 @@ def poll_kernel_errors(device="cuda") -> None:
         if code:
             _tc_pending.pop(key, None)
             flag.zero_()
-            raise KernelError(f"a bounded wait inside a TMA + tcgen05 kernel ran out (code {code}: 1-4 and 21-24 the "
-                              f"product, 11-19 the prefill attention); the results of a recent step are invalid")
+            raise KernelError(f"a bounded wait inside a TMA kernel ran out (code {code}: 1-6 and 21-24 the tcgen05 "
+                              f"product, 11-19 the prefill attention, 31-34 the persistent decode kernel); the results "
+                              f"of a recent step are invalid")
     else:
         host, event = torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event()
     host.copy_(flag, non_blocking=True)
@@ -549,6 +551,64 @@ def paged_prefill_tc5_blocks_per_sm() -> int:
     if n < 0:
         raise KernelError(f"paged_prefill_tc5: a device query failed with CUDA error {-n}")
     return n
+
+
+USE_FUSED_DECODE = __import__("os").environ.get("CBIS_FUSED_DECODE", "1") != "0"   # 0: decode steps run kernel by kernel
+FUSED_DECODE_MAX_ROWS = 16
+
+
+def decode_layers_blocks(n_min: int) -> int:
+    """Blocks the persistent decode kernel runs with: one per SM, fewer when the narrowest product of a layer has
+    fewer than 8 columns per block."""
+    n = kernels().cbis_decode_layers_blocks(c_int(n_min))
+    if n <= 0:
+        raise KernelError("decode_layers: the device could not be queried")
+    return n
+
+
+def decode_layers_map(w_nk, blocks: int) -> torch.Tensor:
+    """The 128-byte TMA descriptor of a weight matrix ``[N, K]`` for ``blocks`` blocks, as a CPU uint8 tensor."""
+    _need_cuda(w_nk)
+    assert w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.dim() == 2
+    out = torch.zeros(128, dtype=torch.uint8)
+    st = kernels().cbis_decode_layers_map(c_void_p(out.data_ptr()), _ptr(w_nk), c_int(w_nk.shape[0]), c_int(w_nk.shape[1]),
+                                          c_int(blocks))
+    _check(st, "decode_layers_map", f"N={w_nk.shape[0]} K={w_nk.shape[1]} blocks={blocks}", launches=0)
+    return out
+
+
+def decode_layers_desc_bytes() -> int:
+    return int(kernels().cbis_decode_layers_desc_bytes())
+
+
+def decode_layers_splits(rows: int, n_head: int, max_context: int, blocks: int) -> int:
+    """How many ways the persistent decode kernel splits a request's keys: its (row, head, split) items go round the
+    two groups of four warps of every block; the choice leaves the last round as full as possible, with pieces of 64
+    keys or more, at most 32 ways."""
+    groups, pairs = 2 * blocks, max(1, rows * n_head)
+    best, best_cost = 1, None
+    for n in range(1, max(1, min(32, max_context // 64)) + 1):
+        cost = -(-pairs * n // groups) / n          # rounds of items times the length of a piece
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = n, cost
+    return best
+
+
+def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_dim, F, page_size, act, window, scale,
+                  nsplit, x, qkv, attn, hidden, block_table, row_seq, positions, slot_mapping, part, counters,
+                  grid_counter):
+    """``n_layers`` pre-norm layers of a decode step of ``M`` <= 16 rows in one persistent kernel (see
+    csrc/kernels/decode_layers.cu).  ``grid_counter`` (int32[1]) must be zero; a wait that runs out inside the kernel
+    sets the flag that ``raise_if_kernel_errors`` reads."""
+    _need_cuda(maps, layers, x, qkv, attn, hidden, block_table, row_seq, positions, slot_mapping, part, counters, grid_counter)
+    assert x.dtype == torch.float32 and x.is_contiguous() and qkv.dtype == torch.bfloat16 and hidden.dtype == torch.bfloat16
+    assert block_table.is_contiguous() and block_table.dtype == torch.int32
+    st = kernels().cbis_decode_layers(
+        _ptr(maps), _ptr(layers), c_int(n_layers), c_int(blocks), c_int(M), c_int(d), c_int(n_head), c_int(n_kv_head),
+        c_int(head_dim), c_int(F), c_int(page_size), c_int(ACT[act]), c_int(window), c_float(scale), c_int(nsplit), _ptr(x),
+        _ptr(qkv), _ptr(attn), _ptr(hidden), _ptr(block_table), c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions),
+        _ptr(slot_mapping), _ptr(part), _ptr(counters), _ptr(grid_counter), _ptr(tcgen05_error_flag(x.device)), _stream())
+    _check(st, "decode_layers", f"layers={n_layers} rows={M} width={d} heads={n_head}/{n_kv_head} head_dim={head_dim} inner={F}")
 
 
 def decode_advance(tokens, positions, seg_start, seg_ctx, sampled, n):

@@ -132,9 +132,28 @@ class Model:
         """Logits (float32 ``[R, vocab]``) at ``ctx.logit_rows`` for the rows of this step."""
         x = self.embedding.forward(ctx, self.position)
         pending = None
-        for li in self.spec.schedule:
-            layer = self.layers[li]
-            pending = layer.block.forward(ctx, x, pending, ctx.layer_cache(li), ctx.layer_state(li))
+        sched = self.spec.schedule
+        i = 0
+        while i < len(sched):
+            li = sched[i]
+            block, cache, state = self.layers[li].block, ctx.layer_cache(li), ctx.layer_state(li)
+            key = block.run_key(ctx, cache, state)
+            if key is None:
+                pending = block.forward(ctx, x, pending, cache, state)
+                i += 1
+                continue
+            # a run of consecutive layers whose blocks can go together (for instance one kernel for all of them)
+            run = [(block, cache, state)]
+            j = i + 1
+            while j < len(sched):
+                nxt = self.layers[sched[j]].block
+                c2, s2 = ctx.layer_cache(sched[j]), ctx.layer_state(sched[j])
+                if type(nxt) is not type(block) or nxt.run_key(ctx, c2, s2) != key:
+                    break
+                run.append((nxt, c2, s2))
+                j += 1
+            pending = type(block).forward_run(ctx, [r[0] for r in run], x, pending, [r[1] for r in run], [r[2] for r in run])
+            i = j
         return self.head_part.forward(ctx, x, pending, self.final_norm)
 
 

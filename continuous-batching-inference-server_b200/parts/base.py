@@ -194,6 +194,19 @@ class Block:
         Returns this layer's own pending output (or None if x is up to date)."""
         raise NotImplementedError
 
+    def run_key(self, ctx, cache, state):
+        """A block that can run TOGETHER with the blocks after it in one go (one kernel for a run of layers) returns
+        a hashable key for this step, else None.  The model hands every maximal run of consecutive layers with equal
+        keys to ``forward_run`` of their class; a run of one is allowed."""
+        return None
+
+    @classmethod
+    def forward_run(cls, ctx, blocks, x: torch.Tensor, pending: Optional[Delta], caches, states) -> Optional[Delta]:
+        """Runs ``blocks`` (equal ``run_key``) one after the other; the contract of ``forward`` for the whole run."""
+        for block, cache, state in zip(blocks, caches, states):
+            pending = block.forward(ctx, x, pending, cache, state)
+        return pending
+
 
 _MIXERS: Dict[str, Callable[..., Mixer]] = {}
 _FEED_FORWARDS: Dict[str, Callable[..., FeedForward]] = {}
