@@ -553,7 +553,11 @@ def paged_prefill_tc5_blocks_per_sm() -> int:
     return n
 
 
-USE_FUSED_DECODE = __import__("os").environ.get("CBIS_FUSED_DECODE", "1") != "0"   # 0: decode steps run kernel by kernel
+# 1: decode steps of up to 16 rows run their layers in ONE persistent kernel (csrc/kernels/decode_layers.cu).  Off by
+# default: measured at the 1.3B sizes it takes 1.6 ms per step at batch 1 and 2.1 ms at batch 8, the chain of kernels 0.95
+# and 1.24 ms (its twelve dependent phases per layer each wait for L2 or for the other blocks while the memory system is
+# kept busy by its own weight stream, and eight warps per SM do not hide that).
+USE_FUSED_DECODE = __import__("os").environ.get("CBIS_FUSED_DECODE", "0") == "1"
 FUSED_DECODE_MAX_ROWS = 16
 
 
@@ -582,16 +586,11 @@ def decode_layers_desc_bytes() -> int:
 
 
 def decode_layers_splits(rows: int, n_head: int, max_context: int, blocks: int) -> int:
-    """How many ways the persistent decode kernel splits a request's keys: its (row, head, split) items go round the
-    two groups of four warps of every block; the choice leaves the last round as full as possible, with pieces of 64
-    keys or more, at most 32 ways."""
+    """How many ways the persistent decode kernel splits a request's keys: its (row, head, split) items go to the two
+    groups of four warps of every block.  An item has a fixed cost (its query, the meeting of its warps, the merge),
+    so the items are as long as one round over the groups allows: pieces of 64 keys or more, at most 32 ways."""
     groups, pairs = 2 * blocks, max(1, rows * n_head)
-    best, best_cost = 1, None
-    for n in range(1, max(1, min(32, max_context // 64)) + 1):
-        cost = -(-pairs * n // groups) / n          # rounds of items times the length of a piece
-        if best_cost is None or cost < best_cost - 1e-9:
-            best, best_cost = n, cost
-    return best
+    return max(1, min(32, groups // pairs, max_context // 64))
 
 
 def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_dim, F, page_size, act, window, scale,

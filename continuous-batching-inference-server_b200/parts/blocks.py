@@ -17,9 +17,10 @@ class PreNormBlock(Block):
     Each add is folded into the norm that follows it, so a layer's feed-forward output
     is handed on as pending and added by the next layer's first norm (or the final norm).
 
-    A decode step (single tokens only, up to 16 rows, bfloat16) of consecutive blocks made of LayerNorm, paged
-    attention with keys of its own (head size 64 or 128) and a dense feed-forward runs as ONE persistent kernel
-    for the whole run of layers (``ops.decode_layers``); everything else runs part by part."""
+    With ``CBIS_FUSED_DECODE=1`` a decode step (single tokens only, up to 16 rows, bfloat16) of consecutive blocks
+    made of LayerNorm, paged attention with keys of its own (head size 64 or 128) and a dense feed-forward runs as ONE
+    persistent kernel for the whole run of layers (``ops.decode_layers``); everything else, and by default this too
+    (the chain of kernels is the faster of the two as measured), runs part by part."""
 
     def forward(self, ctx, x, pending, cache, state):
         h = self.norm_mixer.forward(ctx, x, pending)

@@ -1,4 +1,4 @@
-"""The persistent decode kernel (a run of layers in one launch) against the same layers run kernel by kernel and
+"""The persistent decode kernel (a run of layers in one launch; an option, CBIS_FUSED_DECODE=1) against the same layers run kernel by kernel and
 against the plain implementation (GPU): head sizes 64 and 128, shared key/value heads, a window, widths that are
 no power of two, 1 to 16 rows, requests of very different lengths side by side, page edges, padding rows of a
 captured step, and generation through the scheduler."""
@@ -145,7 +145,11 @@ def test_generation_with_the_persistent_kernel_equals_generation_without(tmp_pat
     params = [cb.SamplingParams(max_new_tokens=n) for n in (40, 12, 64, 30, 50)]
     eng = cb.Engine(folder, dtype="bfloat16", page_size=16, num_pages=30, max_num_seqs=5, max_batched_tokens=128,
                     poison_freed_pages=True)
-    outs = eng.generate(prompts, params)
+    keep, ops.USE_FUSED_DECODE = ops.USE_FUSED_DECODE, True
+    try:
+        outs = eng.generate(prompts, params)
+    finally:
+        ops.USE_FUSED_DECODE = keep
     assert [len(o) for o in outs] == [40, 12, 64, 30, 50]
     assert any(p is not False for p in eng.runner.__dict__.get("_decode_layer_plans", {}).values())
     ops.raise_if_kernel_errors()
