@@ -70,6 +70,7 @@ struct Params {
   unsigned int* grid_counter;   // zero at launch
   int* error;
   int a_pitch, red_cols;        // shared-memory row pitches: normalised rows (elements), partial sums (floats)
+  unsigned long long* trace;    // measuring aid (null in service): block 0 notes the time at every phase boundary
 };
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -143,6 +144,16 @@ __device__ __forceinline__ bool grid_meet(const Params& p, unsigned target, Shar
 }
 
 enum { EPI_STORE = 0, EPI_ADD_X = 1 };
+
+// Measuring aid: block 0 writes the nanosecond timer at the n-th phase boundary (12 per layer, 256 at most).
+__device__ __forceinline__ void stamp(const Params& p, int ctid, int& n) {
+  if (p.trace && blockIdx.x == 0 && ctid == 0 && n < 256) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    p.trace[n] = t;
+  }
+  ++n;
+}
 
 // LayerNorm of the step's rows from the residual stream (L2) into shared memory as bfloat16 [Mpad][pitch]; the
 // columns from d to the next multiple of 64 are zero (the products' last piece along K reads them).
@@ -438,16 +449,21 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
   const int group = cw / DEC_WARPS, gtid = ctid % (DEC_WARPS * 32);
   const int n_qkv = p.d_q + 2 * p.d_kv;
   unsigned it = 0, meetings = 0;
+  int ns = 0;
   pdl_wait();   // the residual stream comes from the kernel before
   bool ok = true;
   for (int l = 0; l < p.n_layers && ok; ++l) {
     const LayerDesc L = p.layers[l];
+    stamp(p, ctid, ns);
     // q | k | v = LN1(x) W^T + b
     norm_rows<LOW8>(p, L.ln1_g, L.ln1_b, L.eps1, a_smem, cw, lane);
     consumer_sync();
+    stamp(p, ctid, ns);
     product_any<true, LOW8>(p, p.prod[0], it, ring, sh, a_smem, nullptr, 0, red, L.b_qkv, EPI_STORE, CBIS_ACT_NONE, p.qkv,
                             n_qkv, cw, lane);
+    stamp(p, ctid, ns);
     if (!(ok = grid_meet(p, ++meetings * gridDim.x, sh, ctid))) break;
+    stamp(p, ctid, ns);
     // attention: (row, head, split) items over the groups of four warps of all blocks
     {
       const int n_items = p.M * p.n_head * p.nsplit, n_groups = gridDim.x * (CONSUMER_WARPS / DEC_WARPS);
@@ -460,19 +476,28 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
         group_sync(BAR_GROUP0 + group, DEC_WARPS * 32);
       }
     }
+    stamp(p, ctid, ns);
     if (!(ok = grid_meet(p, ++meetings * gridDim.x, sh, ctid))) break;
+    stamp(p, ctid, ns);
     // x += attn W_o^T + b_o
     product_any<false, LOW8>(p, p.prod[1], it, ring, sh, nullptr, p.attn, p.d_q, red, L.b_o, EPI_ADD_X, 0, nullptr, 0, cw, lane);
+    stamp(p, ctid, ns);
     if (!(ok = grid_meet(p, ++meetings * gridDim.x, sh, ctid))) break;
+    stamp(p, ctid, ns);
     // hidden = act(LN2(x) W_fc^T + b_fc)
     norm_rows<LOW8>(p, L.ln2_g, L.ln2_b, L.eps2, a_smem, cw, lane);
     consumer_sync();
+    stamp(p, ctid, ns);
     product_any<true, LOW8>(p, p.prod[2], it, ring, sh, a_smem, nullptr, 0, red, L.b_fc, EPI_STORE, p.act, p.hidden, p.F, cw, lane);
+    stamp(p, ctid, ns);
     if (!(ok = grid_meet(p, ++meetings * gridDim.x, sh, ctid))) break;
+    stamp(p, ctid, ns);
     // x += hidden W_proj^T + b_proj
     product_any<false, LOW8>(p, p.prod[3], it, ring, sh, nullptr, p.hidden, p.F, red, L.b_proj, EPI_ADD_X, 0, nullptr, 0, cw, lane);
+    stamp(p, ctid, ns);
     if (l + 1 < p.n_layers && !(ok = grid_meet(p, ++meetings * gridDim.x, sh, ctid))) break;
   }
+  stamp(p, ctid, ns);
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -553,13 +578,15 @@ CBIS_EXPORT int cbis_decode_layers_desc_bytes() { return (int)sizeof(dl::LayerDe
 // maps: device array of n_layers * 4 tensor maps made by cbis_decode_layers_map with the same `blocks`;
 // layers: device array of n_layers records; x [M, d] float; qkv [M, d_q + 2 d_kv], attn [M, d_q], hidden [M, F]
 // bfloat16 scratch; part / counters: the decode attention's scratch for M rows, n_head heads and nsplit splits
-// (counters zero); grid_counter: one unsigned int, zero at launch; error: int, set non-zero if a wait ran out.
+// (counters zero); grid_counter: one unsigned int, zero at launch; error: int, set non-zero if a wait ran out;
+// trace: null, or 256 x 8 bytes that take block 0's timer at every phase boundary (12 per layer) for measuring.
 // Refuses (CBIS_ERR_BAD_SIZE / CBIS_ERR_TOO_LARGE) what it does not take: the caller then runs the layers kernel by kernel.
 CBIS_EXPORT int cbis_decode_layers(const void* maps, const void* layers, int n_layers, int blocks, int M, int d, int n_head,
                                    int n_kv_head, int hd, int F, int ps, int act, int window, float scale, int nsplit,
                                    float* x, void* qkv, void* attn, void* hidden, const int* block_table, int max_blocks,
                                    const int* row_seq, const int* positions, const int* slot_mapping, float* part,
-                                   unsigned int* counters, unsigned int* grid_counter, int* error, void* stream) {
+                                   unsigned int* counters, unsigned int* grid_counter, int* error, void* stream,
+                                   unsigned long long* trace) {
   if (n_layers <= 0 || M <= 0) return CBIS_OK;
   if (M > 16 || (hd != 64 && hd != 128) || ps <= 0 || ps % 16 || d <= 0 || d % 8 || F <= 0 || F % 8 || n_head <= 0 ||
       n_kv_head <= 0 || n_head % n_kv_head || nsplit < 1 || nsplit > 32 || blocks <= 0)
@@ -581,7 +608,7 @@ CBIS_EXPORT int cbis_decode_layers(const void* maps, const void* layers, int n_l
   p.ps = ps; p.act = act; p.window = window; p.nsplit = nsplit; p.max_blocks = max_blocks; p.scale = scale;
   p.x = x; p.qkv = (__nv_bfloat16*)qkv; p.attn = (__nv_bfloat16*)attn; p.hidden = (__nv_bfloat16*)hidden;
   p.block_table = block_table; p.row_seq = row_seq; p.positions = positions; p.slot_mapping = slot_mapping;
-  p.part = part; p.counters = counters; p.grid_counter = grid_counter; p.error = error;
+  p.part = part; p.counters = counters; p.grid_counter = grid_counter; p.error = error; p.trace = trace;
   dl::plan_product(&p.prod[0], p.d_q + 2 * p.d_kv, d, blocks);
   dl::plan_product(&p.prod[1], d, p.d_q, blocks);
   dl::plan_product(&p.prod[2], F, d, blocks);

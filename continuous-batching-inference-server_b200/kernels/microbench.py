@@ -8,6 +8,7 @@ launch streams from HBM, as in a real step) or launch by launch for profilers.
     python -m cbis_b200.kernels.microbench --op layernorm --rows 8 --k 2048
     python -m cbis_b200.kernels.microbench --op sample --rows 8 --n 50257
     python -m cbis_b200.kernels.microbench --op prefill_attn --rows 512 --ctx 32768 --heads 8 --head-dim 32 [--dtype float32]
+    python -m cbis_b200.kernels.microbench --op decode_layers_phases --rows 8 --ctx 1024 --layers 6
 
 ``--no-graph`` launches the kernels directly (a profiler then sees ordinary launches).
 """
@@ -42,10 +43,41 @@ def timed(fn, use_graph=True, reps=20):
     return e0.elapsed_time(e1) / reps * 1e3
 
 
+def decode_layers_phases(rows: int, ctx_len: int, layers: int):
+    """Microseconds per phase and layer of the persistent decode kernel as its block 0 sees them (1.3B layer sizes)."""
+    import cbis_b200 as cb
+    from cbis_b200.engine import StepEntry
+    from cbis_b200.kernels import ops
+    cfg = dict(architectures=["GPT2LMHeadModel"], n_layer=layers, n_embd=2048, n_head=16, n_inner=8192, vocab_size=50257,
+               n_positions=2048, activation_function="gelu", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+    eng = cb.Engine.from_random(cfg, seed=1, dtype="bfloat16", page_size=16, max_tokens=rows * 2048, max_num_seqs=rows,
+                                max_batched_tokens=2048, prefill_chunk=2048)
+    g = torch.Generator().manual_seed(0)
+    slots = [eng.open_request(i) for i in range(rows)]
+    for s in slots:
+        eng.forward_step([StepEntry(s, 0, torch.randint(0, 50257, (ctx_len,), generator=g).tolist(), [])])
+    eng.runner.use_graphs, ops.USE_FUSED_DECODE = False, True
+    for step in range(4):
+        eng.forward_step([StepEntry(s, ctx_len + step, [5], [0]) for s in slots])
+    plan = next(iter(eng.runner.__dict__["_decode_layer_plans"].values()))
+    plan.trace = torch.zeros(256, dtype=torch.int64, device="cuda")
+    eng.forward_step([StepEntry(s, ctx_len + 4, [5], [0]) for s in slots])
+    torch.cuda.synchronize()
+    t = plan.trace.cpu().tolist()
+    names = ["LN1", "QKV", "meet", "attention", "meet", "O", "meet", "LN2", "FC", "meet", "PROJ", "meet"]
+    for layer in range(min(layers, 21)):
+        row = t[layer * 12:layer * 12 + 13]
+        if 0 in row:
+            break
+        print(f"layer {layer}: " + " ".join(f"{n}={(b - a) / 1e3:.1f}" for n, a, b in zip(names, row, row[1:])) +
+              f" | total {(row[12] - row[0]) / 1e3:.1f} us")
+
+
 def main():
     from cbis_b200.kernels import ops
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", required=True, choices=["decode_attn", "prefill_attn", "gemm", "gemm_tc", "gemm_f32", "layernorm", "sample"])
+    ap.add_argument("--op", required=True, choices=["decode_attn", "prefill_attn", "gemm", "gemm_tc", "gemm_f32", "layernorm", "sample",
+                                                    "decode_layers_phases"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="prefill_attn: the path")
     ap.add_argument("--chunks", type=int, default=-1, help="prefill_attn: key chunks (-1: the engine's own choice, 1: none)")
     ap.add_argument("--rows", type=int, default=8)
@@ -61,6 +93,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--reps", type=int, default=20)
     a = ap.parse_args()
+    if a.op == "decode_layers_phases":
+        return decode_layers_phases(a.rows, a.ctx, a.layers)
     dev, M, L = "cuda", a.rows, a.layers
     torch.manual_seed(0)
     if a.op == "gemm":

@@ -595,10 +595,11 @@ def decode_layers_splits(rows: int, n_head: int, max_context: int, blocks: int) 
 
 def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_dim, F, page_size, act, window, scale,
                   nsplit, x, qkv, attn, hidden, block_table, row_seq, positions, slot_mapping, part, counters,
-                  grid_counter):
+                  grid_counter, trace=None):
     """``n_layers`` pre-norm layers of a decode step of ``M`` <= 16 rows in one persistent kernel (see
     csrc/kernels/decode_layers.cu).  ``grid_counter`` (int32[1]) must be zero; a wait that runs out inside the kernel
-    sets the flag that ``raise_if_kernel_errors`` reads."""
+    sets the flag that ``raise_if_kernel_errors`` reads.  ``trace`` (int64[256], for measuring): block 0's
+    nanosecond timer at every phase boundary, 12 per layer."""
     _need_cuda(maps, layers, x, qkv, attn, hidden, block_table, row_seq, positions, slot_mapping, part, counters, grid_counter)
     assert x.dtype == torch.float32 and x.is_contiguous() and qkv.dtype == torch.bfloat16 and hidden.dtype == torch.bfloat16
     assert block_table.is_contiguous() and block_table.dtype == torch.int32
@@ -606,7 +607,8 @@ def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_
         _ptr(maps), _ptr(layers), c_int(n_layers), c_int(blocks), c_int(M), c_int(d), c_int(n_head), c_int(n_kv_head),
         c_int(head_dim), c_int(F), c_int(page_size), c_int(ACT[act]), c_int(window), c_float(scale), c_int(nsplit), _ptr(x),
         _ptr(qkv), _ptr(attn), _ptr(hidden), _ptr(block_table), c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions),
-        _ptr(slot_mapping), _ptr(part), _ptr(counters), _ptr(grid_counter), _ptr(tcgen05_error_flag(x.device)), _stream())
+        _ptr(slot_mapping), _ptr(part), _ptr(counters), _ptr(grid_counter), _ptr(tcgen05_error_flag(x.device)), _stream(),
+        _ptr(trace))
     _check(st, "decode_layers", f"layers={n_layers} rows={M} width={d} heads={n_head}/{n_kv_head} head_dim={head_dim} inner={F}")
 
 

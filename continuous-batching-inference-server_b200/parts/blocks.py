@@ -119,7 +119,7 @@ class _DecodeLayersPlan:
         ops.decode_layers(self.maps, self.layers, self.n_layers, self.blocks, M, self.d, self.n_head, self.n_kv_head,
                           self.hd, self.F, self.page_size, self.act, self.window, self.scale, nsplit, x, self.qkv,
                           self.attn, self.hidden, view.block_table, ctx.row_seq, ctx.positions, view.slot_mapping, part,
-                          counters, self.grid_counter)
+                          counters, self.grid_counter, getattr(self, "trace", None))
 
 
 register_block("pre_norm", PreNormBlock)
