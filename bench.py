@@ -43,6 +43,10 @@ CONFIG_6_7B = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer
 CONFIG_XL = dict(architectures=["GPT2LMHeadModel"], model_type="gpt2", n_layer=48, n_embd=1600, n_head=25,
                  n_inner=6400, vocab_size=50257, n_positions=1024, activation_function="gelu_new",
                  layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+# the reference's one fixed model (include/config.hpp:5-21) for its own workload (--config batching)
+CONFIG_REFERENCE = dict(architectures=["TinyGPT"], n_layer=4, n_embd=256, n_head=8, n_inner=1024, vocab_size=1000,
+                        n_positions=2048, activation_function="gelu", layer_norm_epsilon=1e-5, tie_word_embeddings=False)
+REFERENCE_BUILD = os.path.join(ROOT, "baseline", "_ref")     # the unmodified reference, built with its own CMakeLists
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -111,9 +115,10 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl"],
+    ap.add_argument("--config", default="1.3b", choices=["1.3b", "6.7b", "xl", "batching"],
                     help="1.3b: the default measurement; 6.7b: batch-64 decode at context 2,048; "
-                         "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each)")
+                         "xl: 64 mixed requests through the scheduler (prompts 32-768, 256 outputs each); "
+                         "batching: the reference's own workload at the reference's own sizes (both --impl arms)")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--prompt-len", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
@@ -122,10 +127,14 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="time only the 2,048-token prefill (for profilers)")
     args = ap.parse_args()
 
+    if args.config == "batching":
+        return reference_workload(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++/CUDA project without setup.py or pyproject.toml: pip cannot "
-                          "install it offline; its sizes are compile-time constants (d=256, L=4) built for sm_89"}))
+                          "the reference cannot run this configuration: its model sizes are compile-time constants "
+                          "(include/config.hpp:5-21: 4 layers, width 256, vocabulary 1000) and it computes in fp32 only; "
+                          "built unmodified with its own CMakeLists it runs its own workload here: "
+                          "bench.py --config batching --impl reference"}))
         return 0
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (single-GPU tier)")
@@ -177,8 +186,9 @@ def main() -> int:
             eng.forward_step([StepEntry(slots[j], 0, ps[j], []) for j in range(i, min(i + per, len(ps)))])
         return slots
 
-    def decode_device(batch, steps, warm):
+    def decode_device(batch, steps, warm, prompt_len=None):
         """tokens/s of `steps` captured decode steps after `warm` untimed ones; also ms/step, launches/step."""
+        PL = prompt_len or args.prompt_len
         ps = prompts(batch, PL)
         slots = prefill_slots(ps)
         for s in slots:
@@ -268,6 +278,11 @@ def main() -> int:
         for b in (1, 64):
             v, _, _ = decode_device(b, min(K, 256), W)
             pts[f"decode_b{b}"] = round(v, 1)
+        # the default batch at the two ends of the context range: 32 steps from context 1,024 and 32 steps up to the last position
+        v, _, _ = decode_device(B, 32, 3, prompt_len=PL)
+        pts[f"decode_b{B}_ctx{PL}"] = round(v, 1)
+        v, _, _ = decode_device(B, 32, 3, prompt_len=P - 40)
+        pts[f"decode_b{B}_ctx{P}"] = round(v, 1)
         result["points"] = pts
         # ---- end to end through the Python entry point -------------------------------------------
         ps = prompts(B, PL)
@@ -299,6 +314,52 @@ def main() -> int:
     return 0
 
 
+def reference_workload(args) -> int:
+    """The reference's own workload (src/bench_batching.cpp:26-33: 240 requests, Poisson arrivals 6 ms apart, prompts of
+    4-16 and outputs of 8-32 tokens, 16 slots) at the reference's own model sizes.  --impl reference runs the unmodified
+    reference's bench_batching (built with its own CMakeLists into baseline/_ref; its sm_89 PTX is compiled for the GPU
+    at load) on its committed weights; the default arm runs this engine (bin/bench_batching) on random weights of the
+    same sizes.  The throughput of both is set by the arrival rate; the latencies are what the engines decide."""
+    import re
+    import tempfile
+    line = {"metric": "the reference's continuous-batching workload: tokens/s (prompt + output) and request latency",
+            "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "data": "synthetic (uniform random token ids)",
+            "config": {"model": "TinyGPT, the reference's sizes", "n_layer": 4, "n_embd": 256, "n_head": 8, "n_inner": 1024,
+                       "vocab_size": 1000, "requests": 240, "mean_interarrival_ms": 6.0, "max_live": 16}}
+    if args.impl == "reference":
+        exe, weights = os.path.join(REFERENCE_BUILD, "build", "bench_batching"), os.path.join(REFERENCE_BUILD, "weights.bin")
+        if not (os.path.isfile(exe) and os.path.isfile(weights)):
+            print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no build of the reference "
+                              "(cmake -S <reference> -B baseline/_ref/build && cmake --build baseline/_ref/build; "
+                              "its python/weights.bin copied to baseline/_ref/weights.bin)"}))
+            return 0
+        r = subprocess.run([exe, weights], capture_output=True, text=True, timeout=600)
+        part = r.stdout.split("== static")[0]
+        m = re.search(r"wall clock\s*:\s*([\d.]+) ms.*?token throughput\s*:\s*([\d.]+) tok/s.*?p50/p95/p99\s*:\s*([\d.]+) / "
+                      r"([\d.]+) / ([\d.]+) ms", part, re.S)
+        if r.returncode != 0 or not m:
+            print(json.dumps({"impl": "reference", "unavailable": f"the reference's bench_batching ended with {r.returncode}"}))
+            return 0
+        line.update(impl="reference", dtype="fp32", value=float(m.group(2)), wall_ms=float(m.group(1)),
+                    latency_ms={"p50": float(m.group(3)), "p95": float(m.group(4)), "p99": float(m.group(5))})
+        print(json.dumps(line))
+        return 0
+    with tempfile.TemporaryDirectory() as d:
+        cfg = os.path.join(d, "config.json")
+        with open(cfg, "w") as f:
+            json.dump(CONFIG_REFERENCE, f)
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "bench_batching"), "--random", cfg, "--json"],
+                           capture_output=True, text=True, timeout=900)
+    out = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    if r.returncode != 0 or not out:
+        print(r.stdout[-2000:], r.stderr[-2000:], file=sys.stderr)
+        return 1
+    mine = json.loads(out[-1])
+    line.update(impl="b200", dtype="bf16", value=mine["tokens_per_s"], wall_ms=mine["wall_ms"], latency_ms=mine["latency_ms"])
+    print(json.dumps(line))
+    return 0
+
+
 def mixed_workload(args, cb, torch) -> int:
     """GPT-2 XL layer sizes: 64 requests, prompt lengths uniform in 32..768, 256 outputs each, all submitted at
     t = 0 and run by the scheduler (token budget 2,048, prompt portions of 512)."""
@@ -316,17 +377,37 @@ def mixed_workload(args, cb, torch) -> int:
     eng.generate(prompts, cb.SamplingParams(max_new_tokens=2))           # graphs of the large buckets
     torch.cuda.synchronize()
     steps0 = eng.steps
+    step_ms, step_tokens = [], []
+    ids = [eng.add_request(p, cb.SamplingParams(max_new_tokens=n_out)) for p in prompts]
+    done = {}
     t0 = time.perf_counter()
-    outs = eng.generate(prompts, cb.SamplingParams(max_new_tokens=n_out))
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
+    last = t0
+    while eng.has_unfinished():          # what generate() does, with the wall time of every step noted
+        for o in eng.step():
+            done[o.request_id] = o.tokens
+        now = time.perf_counter()        # the step's sampled tokens have been read back: the device has finished it
+        step_ms.append((now - last) * 1e3)
+        step_tokens.append(eng.last_step_tokens)
+        last = now
+    wall = last - t0
+    outs = [done[i] for i in ids]
     n_prompt, n_gen = sum(map(len, prompts)), sum(map(len, outs))
+    edges = [0.5, 1, 2, 3, 4, 6, 8, 12, 16, 24, 32]
+    hist, lo = {}, 0.0
+    for e in edges + [float("inf")]:
+        hist[f"<={e:g}ms" if e != float("inf") else f">{edges[-1]:g}ms"] = sum(1 for t in step_ms if lo < t <= e)
+        lo = e
+    decode_only = [t for t, n in zip(step_ms, step_tokens) if n <= n_req]
     print(json.dumps({
         "metric": "mixed continuous-batching workload, tokens/s (GPT-2 XL shapes, 64 requests, prompts 32-768, 256 outputs)",
         "value": round((n_prompt + n_gen) / wall, 1), "unit": "tokens/s", "n_gpus": 1, "impl": "b200", "dtype": "bf16",
         "decode_tokens_per_s": round(n_gen / wall, 1), "wall_s": round(wall, 3), "steps": eng.steps - steps0,
         "prompt_tokens": n_prompt, "output_tokens": n_gen, "preemptions": eng.scheduler.preemptions(),
         "graph_replays": eng.runner.graph_replays, "step_shapes_captured": eng.runner.shape_captures,
+        "step_ms": {"median": round(statistics.median(step_ms), 3), "p95": round(sorted(step_ms)[int(0.95 * len(step_ms))], 3),
+                    "max": round(max(step_ms), 3),
+                    "decode_only_median": round(statistics.median(decode_only), 3) if decode_only else None},
+        "step_ms_histogram": hist,
         "higher_is_better": True, "data": "synthetic (random weights, uniform random token ids)",
         "config": {"model": "GPT-2 XL shapes (GPT2LMHeadModel)", "n_layer": cfgd["n_layer"], "n_layer_config": 48,
                    "n_embd": 1600, "n_head": 25, "n_inner": 6400, "vocab_size": 50257, "n_positions": 1024,
