@@ -23,6 +23,24 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address, in the cluster's shared-memory window, of `p` (a shared-memory address of this block) in the block `rank`.
+__device__ __forceinline__ unsigned in_cluster_block(const void* p, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((unsigned)__cvta_generic_to_shared(p)), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(unsigned addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -34,17 +52,27 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
 // MT: 16-row tiles of A (M <= 16*MT); NT: 8-column tiles of W per block; UNROLL: K blocks in flight per warp.
 // LOW8: M <= 8, so rows 8..15 of the one row tile do not exist: their fragments are zeros and are never loaded
 // (fewer registers: four blocks fit on an SM instead of three).
-template <int MT, int NT, int UNROLL, bool LOW8, typename TO>
+// CLUSTER: the kernel is launched in clusters of `ksplit` blocks that share a block's columns and split K.  (A kernel that
+// holds cluster instructions is launched through the cluster scheduler even when it never runs them, which was measured
+// to cost the plain form a third of its speed: the two forms are separate kernels.)
+template <int MT, int NT, int UNROLL, bool LOW8, typename TO, bool CLUSTER = false>
 __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                                                   const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M,
                                                   int N, int K, int act, const void* next_w,
-                                                  unsigned long long next_bytes) {
-  extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1]
+                                                  unsigned long long next_bytes, int ksplit) {
+  extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1], then [ksplit - 1][MT*16 * NT*8] for the other blocks' sums
   constexpr int RS = NT * 8 + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * (NT * 8);
-  const int nkb = (K + 31) / 32;
+  // ksplit > 1: a cluster of ksplit blocks shares the block's columns; each takes a run of the 32-wide K blocks
+  int rank = 0;
+  if constexpr (CLUSTER) rank = (int)cluster_ctarank();
+  else ksplit = 1;
+  const int n0 = (blockIdx.x / ksplit) * (NT * 8);
+  const int nkb_all = (K + 31) / 32;
+  const int per_rank = (nkb_all + ksplit - 1) / ksplit;
+  const int kb_first = rank * per_rank;
+  const int nkb = min(nkb_all, kb_first + per_rank);
 
   float acc[MT][NT][4];
 #pragma unroll
@@ -82,7 +110,7 @@ __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int ld
     if (bias && n < N) bias0 = bias[n];
   }
   bool waited = false;
-  for (int kb0 = warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
+  for (int kb0 = kb_first + warp; kb0 < nkb; kb0 += SM_WARPS * UNROLL) {
     uint4 wv[UNROLL][NT], av[UNROLL][MT][LOW8 ? 1 : 2];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -137,6 +165,22 @@ __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int ld
       mine[(i * 16 + g + 8) * RS + j * 8 + 2 * t + 1] = acc[i][j][3];
     }
   __syncthreads();
+  float* others = red + (size_t)SM_WARPS * (MT * 16) * RS;   // [ksplit - 1][MT*16 * NT*8], in the cluster's first block
+  if constexpr (CLUSTER) {
+   if (rank > 0) {
+    // this block's sums go into the first block's shared memory; it adds them after the cluster has met
+    const unsigned base = in_cluster_block(others + (size_t)(rank - 1) * (MT * 16) * (NT * 8), 0);
+    for (int idx = threadIdx.x; idx < M * (NT * 8); idx += blockDim.x) {
+      const int m = idx / (NT * 8), c = idx % (NT * 8);
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < SM_WARPS; ++w) v += red[((size_t)w * (MT * 16) + m) * RS + c];
+      st_cluster_f32(base + (unsigned)idx * 4u, v);
+    }
+   }
+   cluster_sync();
+   if (rank > 0) return;
+  }
   // blockDim (256) is a multiple of NT*8, so a thread meets the same column at every idx it takes
   for (int idx = threadIdx.x; idx < M * (NT * 8); idx += blockDim.x) {
     const int m = idx / (NT * 8), c = idx % (NT * 8);
@@ -145,6 +189,8 @@ __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int ld
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < SM_WARPS; ++w) v += red[((size_t)w * (MT * 16) + m) * RS + c];
+    if constexpr (CLUSTER)
+      for (int r = 1; r < ksplit; ++r) v += others[(size_t)(r - 1) * (MT * 16) * (NT * 8) + idx];
     v += bias0;
     from_f32(C[(size_t)m * ldc + n], activate(v, act));
   }
@@ -156,37 +202,83 @@ template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                     const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                    const void* next_w, unsigned long long next_bytes) {
-  gemm_small_m_body<MT, NT, UNROLL, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes);
+                    const void* next_w, unsigned long long next_bytes, int ksplit) {
+  gemm_small_m_body<MT, NT, UNROLL, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
 }
 template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32, 4)
 gemm_small_m_low8_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                          const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                         const void* next_w, unsigned long long next_bytes) {
-  gemm_small_m_body<MT, NT, UNROLL, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes);
+                         const void* next_w, unsigned long long next_bytes, int ksplit) {
+  gemm_small_m_body<MT, NT, UNROLL, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
+}
+template <int MT, int NT, int UNROLL, typename TO>
+__global__ void __launch_bounds__(SM_WARPS * 32, 4)
+gemm_small_m_low8_ksplit_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
+                                const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
+                                const void* next_w, unsigned long long next_bytes, int ksplit) {
+  gemm_small_m_body<MT, NT, UNROLL, true, TO, true>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
 }
 
 template <int MT, int NT, int UNROLL, bool LOW8, typename TO>
 static int launch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
-                          int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
-  const size_t smem = (size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) * sizeof(float);
+                          int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st, int ksplit = 1) {
+  const size_t smem = ((size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) + (size_t)(ksplit - 1) * MT * 16 * NT * 8) * sizeof(float);
   void (*kern)(const __nv_bfloat16*, int, const __nv_bfloat16*, const float*, TO*, int, int, int, int, int, const void*,
-               unsigned long long);
-  if constexpr (LOW8) kern = gemm_small_m_low8_kernel<MT, NT, UNROLL, TO>;
+               unsigned long long, int);
+  if constexpr (LOW8) kern = ksplit > 1 ? gemm_small_m_low8_ksplit_kernel<MT, NT, UNROLL, TO> : gemm_small_m_low8_kernel<MT, NT, UNROLL, TO>;
   else kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
+  if (!LOW8 && ksplit > 1) return CBIS_ERR_BAD_SIZE;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int blocks = (N + NT * 8 - 1) / (NT * 8);
-  return (int)launch_pdl(kern, dim3(blocks), dim3(SM_WARPS * 32), smem, st, (const __nv_bfloat16*)A, lda,
-                         (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act, next_w, next_bytes);
+  const int blocks = (N + NT * 8 - 1) / (NT * 8) * ksplit;
+  if (ksplit == 1)
+    return (int)launch_pdl(kern, dim3(blocks), dim3(SM_WARPS * 32), smem, st, (const __nv_bfloat16*)A, lda,
+                           (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act, next_w, next_bytes, 1);
+  // clusters of ksplit blocks along x, launched like the others (programmatic dependent launch)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(SM_WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = ksplit;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return (int)cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K,
+                                 act, next_w, next_bytes, ksplit);
+}
+
+// CBIS_SMALL_M_KSPLIT=0: K is never split over the blocks of a cluster.
+static int ksplit_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("CBIS_SMALL_M_KSPLIT");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on;
 }
 
 template <typename TO>
 static int dispatch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
                             int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
+  // Few columns and a long K (the feed-forward's second product: 2,048 x 8,192): 8 columns per block would leave
+  // each warp 32 K blocks to walk in four dependent rounds.  Then 16 columns per block and K over the 2 or 4 blocks of
+  // a cluster, whose sums meet in the first block's shared memory: one round per warp, as many blocks as before.
+  if (M <= 8 && ksplit_enabled() && N < 148 * 2 * 16 && N >= 64) {
+    const int tiles16 = (N + 15) / 16, nkb = (K + 31) / 32;
+    int ks = 1;
+    while (ks < 4 && tiles16 * ks * 2 <= 4 * 148 && nkb >= SM_WARPS * 4 * ks * 2) ks *= 2;
+    if (ks > 1)
+      return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, ks);
+  }
   // Columns per block: 16 when that still gives the 148 SMs about two blocks each, else 8.
   const bool wide = N >= 148 * 2 * 16;
   // M <= 8 and more 16-column blocks than fit at three per SM (444): the 64-register form runs them in one round
