@@ -125,6 +125,7 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1/64, prefill and e2e")
     ap.add_argument("--prefill-only", action="store_true", help="time only the 2,048-token prefill (for profilers)")
+    ap.add_argument("--prefill-portion", type=int, default=None, help="with --prefill-only: the prompt in steps of this many tokens")
     args = ap.parse_args()
 
     if args.config == "batching":
@@ -231,8 +232,9 @@ def main() -> int:
         return statistics.median(times)
 
     if args.prefill_only:
-        ms = prefill_once(2048)
-        print(json.dumps({"prefill_ms": round(ms, 3), "tokens": 2048, "n_layer": cfgd["n_layer"]}))
+        ms = prefill_once(2048, args.prefill_portion)
+        print(json.dumps({"prefill_ms": round(ms, 3), "tokens": 2048, "portion": args.prefill_portion or 2048,
+                          "n_layer": cfgd["n_layer"]}))
         return 0
 
     # ---- main measurement: decode at the default batch, clocks sampled meanwhile -------------
