@@ -29,7 +29,12 @@ _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _CSRC = os.path.join(_PKG, "csrc")
 _LOCK = threading.Lock()
 _KERNELS = None
+_OPTIONAL = None
 _HOST = None
+
+# Kernels that are options (off by default) live in a library of their own, built when first asked for: a first call
+# compiles what the model in front of it needs, not what it might be told to try.
+OPTIONAL_SOURCES = ("decode_layers.cu",)
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
@@ -90,13 +95,14 @@ def _run(cmd, what):
         raise BuildError(f"building {what} failed:\n{' '.join(cmd)}\n{r.stdout}")
 
 
-def build_kernels(verbose: bool = True) -> str:
-    """Compiles every .cu under csrc/kernels for sm_100a; returns the library's path."""
-    cus = _sources("kernels", (".cu",))
-    deps = _sources("kernels", (".cu", ".cuh", ".h"))
+def build_kernels(verbose: bool = True, optional: bool = False) -> str:
+    """Compiles the .cu files under csrc/kernels for sm_100a (``optional``: those of OPTIONAL_SOURCES, into a library
+    of their own; else all the others); returns the library's path."""
+    cus = [f for f in _sources("kernels", (".cu",)) if (os.path.basename(f) in OPTIONAL_SOURCES) == optional]
+    deps = _sources("kernels", (".cuh", ".h")) + cus
     tag = _digest(deps, " ".join(NVCC_FLAGS))
     out_dir = _build_dir()
-    lib = os.path.join(out_dir, "libcbis_kernels.so")
+    lib = os.path.join(out_dir, "libcbis_kernels_optional.so" if optional else "libcbis_kernels.so")
     stamp = lib + ".hash"
     if os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == tag:
         return lib
@@ -116,7 +122,7 @@ def build_kernels(verbose: bool = True) -> str:
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(one, cus))
     tmp = lib + f".tmp{os.getpid()}"
-    _run([nvcc, "-shared", "-o", tmp, *objs], "libcbis_kernels.so")
+    _run([nvcc, "-shared", "-o", tmp, *objs], os.path.basename(lib))
     os.replace(tmp, lib)
     with open(stamp, "w") as f:
         f.write(tag)
@@ -169,6 +175,15 @@ def host():
             spec.loader.exec_module(mod)
             _HOST = mod
         return _HOST
+
+
+def optional_kernels() -> ctypes.CDLL:
+    """The library of the kernels that are options (built on first use)."""
+    global _OPTIONAL
+    with _LOCK:
+        if _OPTIONAL is None:
+            _OPTIONAL = ctypes.CDLL(build_kernels(optional=True))
+        return _OPTIONAL
 
 
 def kernels() -> ctypes.CDLL:

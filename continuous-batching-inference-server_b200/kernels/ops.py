@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from .library import kernels
+from .library import kernels, optional_kernels
 
 F32, BF16 = 0, 1
 ACT = {None: 0, "none": 0, "gelu_erf": 1, "gelu_tanh": 2}
@@ -564,7 +564,7 @@ FUSED_DECODE_MAX_ROWS = 16
 def decode_layers_blocks(n_min: int) -> int:
     """Blocks the persistent decode kernel runs with: one per SM, fewer when the narrowest product of a layer has
     fewer than 8 columns per block."""
-    n = kernels().cbis_decode_layers_blocks(c_int(n_min))
+    n = optional_kernels().cbis_decode_layers_blocks(c_int(n_min))
     if n <= 0:
         raise KernelError("decode_layers: the device could not be queried")
     return n
@@ -575,14 +575,14 @@ def decode_layers_map(w_nk, blocks: int) -> torch.Tensor:
     _need_cuda(w_nk)
     assert w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.dim() == 2
     out = torch.zeros(128, dtype=torch.uint8)
-    st = kernels().cbis_decode_layers_map(c_void_p(out.data_ptr()), _ptr(w_nk), c_int(w_nk.shape[0]), c_int(w_nk.shape[1]),
+    st = optional_kernels().cbis_decode_layers_map(c_void_p(out.data_ptr()), _ptr(w_nk), c_int(w_nk.shape[0]), c_int(w_nk.shape[1]),
                                           c_int(blocks))
     _check(st, "decode_layers_map", f"N={w_nk.shape[0]} K={w_nk.shape[1]} blocks={blocks}", launches=0)
     return out
 
 
 def decode_layers_desc_bytes() -> int:
-    return int(kernels().cbis_decode_layers_desc_bytes())
+    return int(optional_kernels().cbis_decode_layers_desc_bytes())
 
 
 def decode_layers_splits(rows: int, n_head: int, max_context: int, blocks: int) -> int:
@@ -603,7 +603,7 @@ def decode_layers(maps, layers, n_layers, blocks, M, d, n_head, n_kv_head, head_
     _need_cuda(maps, layers, x, qkv, attn, hidden, block_table, row_seq, positions, slot_mapping, part, counters, grid_counter)
     assert x.dtype == torch.float32 and x.is_contiguous() and qkv.dtype == torch.bfloat16 and hidden.dtype == torch.bfloat16
     assert block_table.is_contiguous() and block_table.dtype == torch.int32
-    st = kernels().cbis_decode_layers(
+    st = optional_kernels().cbis_decode_layers(
         _ptr(maps), _ptr(layers), c_int(n_layers), c_int(blocks), c_int(M), c_int(d), c_int(n_head), c_int(n_kv_head),
         c_int(head_dim), c_int(F), c_int(page_size), c_int(ACT[act]), c_int(window), c_float(scale), c_int(nsplit), _ptr(x),
         _ptr(qkv), _ptr(attn), _ptr(hidden), _ptr(block_table), c_int(block_table.shape[1]), _ptr(row_seq), _ptr(positions),
