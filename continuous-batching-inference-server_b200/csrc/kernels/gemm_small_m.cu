@@ -59,7 +59,7 @@ template <int MT, int NT, int UNROLL, bool LOW8, typename TO, bool CLUSTER = fal
 __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                                                   const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M,
                                                   int N, int K, int act, const void* next_w,
-                                                  unsigned long long next_bytes, int ksplit) {
+                                                  unsigned long long next_bytes, int ksplit, int accumulate) {
   extern __shared__ float red[];  // [SM_WARPS][MT*16][NT*8 + 1], then [ksplit - 1][MT*16 * NT*8] for the other blocks' sums
   constexpr int RS = NT * 8 + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -192,7 +192,9 @@ __device__ __forceinline__ void gemm_small_m_body(const __nv_bfloat16* A, int ld
     if constexpr (CLUSTER)
       for (int r = 1; r < ksplit; ++r) v += others[(size_t)(r - 1) * (MT * 16) * (NT * 8) + idx];
     v += bias0;
-    from_f32(C[(size_t)m * ldc + n], activate(v, act));
+    v = activate(v, act);
+    if (accumulate) v += to_f32(C[(size_t)m * ldc + n]);   // C is the residual stream: written by earlier kernels, all behind the wait
+    from_f32(C[(size_t)m * ldc + n], v);
   }
 }
 
@@ -202,30 +204,31 @@ template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32)
 gemm_small_m_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                     const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                    const void* next_w, unsigned long long next_bytes, int ksplit) {
-  gemm_small_m_body<MT, NT, UNROLL, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
+                    const void* next_w, unsigned long long next_bytes, int ksplit, int accumulate) {
+  gemm_small_m_body<MT, NT, UNROLL, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit, accumulate);
 }
 template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32, 4)
 gemm_small_m_low8_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                          const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                         const void* next_w, unsigned long long next_bytes, int ksplit) {
-  gemm_small_m_body<MT, NT, UNROLL, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
+                         const void* next_w, unsigned long long next_bytes, int ksplit, int accumulate) {
+  gemm_small_m_body<MT, NT, UNROLL, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit, accumulate);
 }
 template <int MT, int NT, int UNROLL, typename TO>
 __global__ void __launch_bounds__(SM_WARPS * 32, 4)
 gemm_small_m_low8_ksplit_kernel(const __nv_bfloat16* A, int lda, const __nv_bfloat16* __restrict__ W,
                                 const float* __restrict__ bias, TO* __restrict__ C, int ldc, int M, int N, int K, int act,
-                                const void* next_w, unsigned long long next_bytes, int ksplit) {
-  gemm_small_m_body<MT, NT, UNROLL, true, TO, true>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit);
+                                const void* next_w, unsigned long long next_bytes, int ksplit, int accumulate) {
+  gemm_small_m_body<MT, NT, UNROLL, true, TO, true>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, ksplit, accumulate);
 }
 
 template <int MT, int NT, int UNROLL, bool LOW8, typename TO>
 static int launch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
-                          int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st, int ksplit = 1) {
+                          int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st, int accumulate,
+                          int ksplit = 1) {
   const size_t smem = ((size_t)SM_WARPS * MT * 16 * (NT * 8 + 1) + (size_t)(ksplit - 1) * MT * 16 * NT * 8) * sizeof(float);
   void (*kern)(const __nv_bfloat16*, int, const __nv_bfloat16*, const float*, TO*, int, int, int, int, int, const void*,
-               unsigned long long, int);
+               unsigned long long, int, int);
   if constexpr (LOW8) kern = ksplit > 1 ? gemm_small_m_low8_ksplit_kernel<MT, NT, UNROLL, TO> : gemm_small_m_low8_kernel<MT, NT, UNROLL, TO>;
   else kern = gemm_small_m_kernel<MT, NT, UNROLL, TO>;
   if (!LOW8 && ksplit > 1) return CBIS_ERR_BAD_SIZE;
@@ -236,7 +239,7 @@ static int launch_small_m(const void* A, int lda, const void* W, const float* bi
   const int blocks = (N + NT * 8 - 1) / (NT * 8) * ksplit;
   if (ksplit == 1)
     return (int)launch_pdl(kern, dim3(blocks), dim3(SM_WARPS * 32), smem, st, (const __nv_bfloat16*)A, lda,
-                           (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act, next_w, next_bytes, 1);
+                           (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K, act, next_w, next_bytes, 1, accumulate);
   // clusters of ksplit blocks along x, launched like the others (programmatic dependent launch)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
@@ -253,7 +256,7 @@ static int launch_small_m(const void* A, int lda, const void* W, const float* bi
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return (int)cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, bias, (TO*)C, ldc, M, N, K,
-                                 act, next_w, next_bytes, ksplit);
+                                 act, next_w, next_bytes, ksplit, accumulate);
 }
 
 // CBIS_SMALL_M_KSPLIT=0: K is never split over the blocks of a cluster.
@@ -268,7 +271,7 @@ static int ksplit_enabled() {
 
 template <typename TO>
 static int dispatch_small_m(const void* A, int lda, const void* W, const float* bias, void* C, int ldc, int M, int N,
-                            int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st) {
+                            int K, int act, const void* next_w, unsigned long long next_bytes, cudaStream_t st, int accumulate) {
   // Few columns and a long K (the feed-forward's second product: 2,048 x 8,192): 8 columns per block would leave
   // each warp 32 K blocks to walk in four dependent rounds.  Then 16 columns per block and K over the 2 or 4 blocks of
   // a cluster, whose sums meet in the first block's shared memory: one round per warp, as many blocks as before.
@@ -277,23 +280,23 @@ static int dispatch_small_m(const void* A, int lda, const void* W, const float* 
     int ks = 1;
     while (ks < 4 && tiles16 * ks * 2 <= 4 * 148 && nkb >= SM_WARPS * 4 * ks * 2) ks *= 2;
     if (ks > 1)
-      return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, ks);
+      return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate, ks);
   }
   // Columns per block: 16 when that still gives the 148 SMs about two blocks each, else 8.
   const bool wide = N >= 148 * 2 * 16;
   // M <= 8 and more 16-column blocks than fit at three per SM (444): the 64-register form runs them in one round
   if (M <= 8 && wide && (N + 15) / 16 > 3 * 148 && (N + 15) / 16 <= 4 * 148)
-    return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    return launch_small_m<1, 2, 4, true, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
   if (M <= 16) {
-    if (wide) return launch_small_m<1, 2, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-    return launch_small_m<1, 1, 8, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    if (wide) return launch_small_m<1, 2, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
+    return launch_small_m<1, 1, 8, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
   }
   if (M <= 32) {
-    if (wide) return launch_small_m<2, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-    return launch_small_m<2, 1, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+    if (wide) return launch_small_m<2, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
+    return launch_small_m<2, 1, 4, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
   }
-  if (wide) return launch_small_m<4, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-  return launch_small_m<4, 1, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  if (wide) return launch_small_m<4, 2, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
+  return launch_small_m<4, 1, 2, false, TO>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
 }
 
 }  // namespace cbis
@@ -303,15 +306,16 @@ using namespace cbis;
 // A [M, lda>=K] bfloat16, W [N, K] bfloat16, bias [N] float or null, C [M, ldc>=N] bfloat16 or float.
 // Takes M <= 64 and K a multiple of 8 with 16-byte aligned operands; refuses anything else.
 // next_w / next_bytes: weights of the product that will run after this one (16-byte aligned), or null:
-// they are prefetched into L2 while this kernel runs.
+// they are prefetched into L2 while this kernel runs.  accumulate (32-bit C only): C += act(A W^T + bias).
 CBIS_EXPORT int cbis_gemm_small_m_bf16(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
                                        int M, int N, int K, int act, int out_dtype, const void* next_w,
-                                       unsigned long long next_bytes, void* stream) {
+                                       unsigned long long next_bytes, int accumulate, void* stream) {
   if (M <= 0 || N <= 0) return CBIS_OK;
   if (M > 64 || K <= 0 || K % 8 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
   if (lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)next_w & 15)) return CBIS_ERR_ALIGNMENT;
   cudaStream_t st = (cudaStream_t)stream;
-  if (out_dtype == CBIS_BF16) return dispatch_small_m<__nv_bfloat16>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
-  if (out_dtype == CBIS_F32) return dispatch_small_m<float>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st);
+  if (accumulate && out_dtype != CBIS_F32) return CBIS_ERR_BAD_DTYPE;   // sums are added into a 32-bit matrix only
+  if (out_dtype == CBIS_BF16) return dispatch_small_m<__nv_bfloat16>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, 0);
+  if (out_dtype == CBIS_F32) return dispatch_small_m<float>(A, lda, W, bias, C, ldc, M, N, K, act, next_w, next_bytes, st, accumulate);
   return CBIS_ERR_BAD_DTYPE;
 }

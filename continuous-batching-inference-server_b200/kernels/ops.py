@@ -124,6 +124,12 @@ def add_layernorm(x, delta, delta_bias, gamma, beta, eps, out, rows=None):
     _check(st, "add_layernorm", f"rows={R} width={d}")
 
 
+def add_delta(x, delta, delta_bias):
+    """x += delta + delta_bias (the 32-bit residual stream, in place): what a layer left pending, added without a
+    norm for a part that normalises inside its own kernel."""
+    add_layernorm(x, delta, delta_bias, None, None, 0.0, torch.empty_like(x, dtype=torch.bfloat16))
+
+
 def bias_act(x, bias, act):
     """x = act(x + bias) in place, arithmetic in 32-bit."""
     _need_cuda(x, bias)
@@ -190,20 +196,76 @@ def add_weight_order(weights) -> None:
         del _next_weight[k]
 
 
-def gemm_small_m(x, w_nk, bias, act, out):
-    """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16, 32-bit accumulation (weight streaming)."""
+def _next_of(w_nk):
+    """(pointer, bytes) of the weight used after ``w_nk``, for the L2 prefetch the weight-streaming kernels issue."""
+    ref = _next_weight.get(w_nk.data_ptr())
+    nxt = ref() if ref is not None else None
+    return _ptr(nxt), ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0)
+
+
+def gemm_small_m(x, w_nk, bias, act, out, accumulate=False):
+    """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16, 32-bit accumulation (weight streaming).
+    ``accumulate`` (32-bit ``out`` only): the result is added to what ``out`` holds."""
     _need_cuda(x, w_nk, bias, out)
     M, K = x.shape
     N = w_nk.shape[0]
     assert x.dtype == torch.bfloat16 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
     assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
-    ref = _next_weight.get(w_nk.data_ptr())
-    nxt = ref() if ref is not None else None
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm_small_m: a product is added into a 32-bit matrix only")
+    nxt, nbytes = _next_of(w_nk)
     st = kernels().cbis_gemm_small_m_bf16(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
                                           c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
-                                          c_int(dtype_code(out.dtype)), _ptr(nxt),
-                                          ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0), _stream())
+                                          c_int(dtype_code(out.dtype)), nxt, nbytes, c_int(1 if accumulate else 0), _stream())
     _check(st, "gemm_small_m", f"M={M} N={N} K={K}")
+
+
+LN_LINEAR_MAX_ROWS = 8
+
+
+_ln_max_k = []
+
+
+def ln_linear_max_k() -> int:
+    if not _ln_max_k:
+        _ln_max_k.append(int(kernels().cbis_gemm_ln_small_m_max_k()))
+    return _ln_max_k[0]
+
+
+# 1: decode steps of up to 8 rows normalise inside the product's kernel and add the layer's results straight into the
+# residual stream (5 kernels a layer instead of 7).  Off by default: measured at the 1.3B sizes it is the slower form,
+# 0.941 ms against 0.900 per step at batch 1 and 1.258 against 1.220 at batch 8; with programmatic dependent launch the
+# separate norm kernel already runs under the next product's first weight loads.
+USE_LN_LINEAR = __import__("os").environ.get("CBIS_LN_LINEAR", "0") == "1"
+
+
+def ln_linear_takes(ctx, norm, w_nk) -> bool:
+    """Whether this step's rows can go through ``ln_linear`` with this norm and weight: a bfloat16 step of up to 8
+    rows, a LayerNorm with weight and bias over rows the kernel takes."""
+    if not USE_LN_LINEAR or ctx.dtype != torch.bfloat16 or not 0 < ctx.n_rows <= LN_LINEAR_MAX_ROWS:
+        return False
+    if norm.as_layernorm() is None:
+        return False
+    if w_nk is None or not w_nk.is_cuda or w_nk.dtype != torch.bfloat16:
+        return False
+    K = w_nk.shape[1]
+    return K == norm.as_layernorm()[0].numel() and K % 8 == 0 and K <= ln_linear_max_k()
+
+
+def ln_linear(x, gamma, beta, eps, w_nk, bias, act, out):
+    """out = act(LayerNorm(x) @ w_nk^T + bias) for up to 8 rows: x the 32-bit rows, statistics in 32-bit, the
+    normalised rows rounded to bfloat16 (as the separate norm kernel hands them to the product), w_nk bfloat16."""
+    _need_cuda(x, gamma, beta, w_nk, bias, out)
+    M, K = x.shape
+    N = w_nk.shape[0]
+    assert x.dtype == torch.float32 and w_nk.dtype == torch.bfloat16 and w_nk.is_contiguous() and w_nk.shape[1] == K
+    assert gamma.dtype == torch.float32 and beta.dtype == torch.float32 and gamma.numel() == K and beta.numel() == K
+    assert x.stride(1) == 1 and out.stride(1) == 1 and out.shape == (M, N)
+    nxt, nbytes = _next_of(w_nk)
+    st = kernels().cbis_gemm_ln_small_m(_ptr(x), c_int(x.stride(0)), _ptr(gamma), _ptr(beta), ctypes.c_float(eps),
+                                        _ptr(w_nk), _ptr(bias), _ptr(out), c_int(out.stride(0)), c_int(M), c_int(N),
+                                        c_int(K), c_int(ACT[act]), c_int(dtype_code(out.dtype)), nxt, nbytes, _stream())
+    _check(st, "ln_linear", f"M={M} N={N} K={K}")
 
 
 def gemm_few_rows(x, w_nk, bias, act, out, ksplit=0):

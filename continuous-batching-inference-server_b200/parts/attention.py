@@ -53,10 +53,22 @@ class PagedAttention(Mixer):
     def streamed_weights(self):
         return [self.w_qkv, self.w_o]
 
+    def fuses_norm(self, ctx, norm):
+        return ops.ln_linear_takes(ctx, norm, self.w_qkv)
+
+    def forward_residual(self, ctx, x, norm, cache, state):
+        qkv = torch.empty((ctx.n_rows, self.qkv_width), dtype=ctx.dtype, device=x.device)
+        ops.ln_linear(x, *norm.as_layernorm(), self.w_qkv, self.b_qkv, None, qkv)
+        out = self._attend(ctx, qkv, cache)
+        ops.gemm_small_m(out, self.w_o, self.b_o, None, x, accumulate=True)
+
     def forward(self, ctx, h, cache, state):
+        out = self._attend(ctx, ops.linear(h, self.w_qkv, self.b_qkv), cache)
+        return Delta(ops.linear(out, self.w_o, None, None, out_dtype=torch.float32), self.b_o)
+
+    def _attend(self, ctx, qkv, cache):
         if cache is None:
             raise RuntimeError("attention needs a cache: its own or the layer's it reads")
-        qkv = ops.linear(h, self.w_qkv, self.b_qkv)
         pe = ctx.position_encoding
         if pe is not None and pe.acts_in_mixer:      # e.g. a rotation of queries and keys, before the keys are cached
             pe.apply_in_mixer(ctx, qkv[:, :self.d_q], qkv[:, self.d_q:self.d_q + self.d_kv] if self.own_kv else None,
@@ -64,7 +76,7 @@ class PagedAttention(Mixer):
         view = ctx.groups[cache.group]
         out = torch.empty((ctx.n_rows, self.d_q), dtype=qkv.dtype, device=qkv.device)
         ctx.attention(self, qkv, cache, view, out)      # stores this step's k, v (if own_kv), then attends
-        return Delta(ops.linear(out, self.w_o, None, None, out_dtype=torch.float32), self.b_o)
+        return out
 
 
 register_mixer("attention", PagedAttention)

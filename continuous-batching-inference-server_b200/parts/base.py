@@ -130,9 +130,25 @@ class Mixer(Part):
         ``state``: ``[max_requests, *shape]`` if it declared a state; row ``ctx.seg_slot[s]`` belongs to segment s."""
         raise NotImplementedError
 
+    # Optional: a mixer may take the residual stream itself, normalise it inside its first kernel and add its result
+    # into it.  A block asks ``fuses_norm`` every step and calls ``forward_residual`` only after a yes.
+    def fuses_norm(self, ctx, norm: "Norm") -> bool:
+        return False
+
+    def forward_residual(self, ctx, x: torch.Tensor, norm: "Norm", cache, state: Optional[torch.Tensor]) -> None:
+        """x += mixer(norm(x)), x the 32-bit residual stream, up to date (nothing pending)."""
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     def forward(self, ctx, h: torch.Tensor) -> Delta:
+        raise NotImplementedError
+
+    def fuses_norm(self, ctx, norm: "Norm") -> bool:      # as Mixer.fuses_norm
+        return False
+
+    def forward_residual(self, ctx, x: torch.Tensor, norm: "Norm") -> None:
+        """x += feed_forward(norm(x)), x the 32-bit residual stream, up to date."""
         raise NotImplementedError
 
 
@@ -142,6 +158,11 @@ class Norm(Part):
         """Adds ``delta`` to the residual stream ``x`` in place (32-bit), returns norm(x) in the
         compute dtype.  With ``rows`` (int32 indices) only those rows are produced and x is not changed."""
         raise NotImplementedError
+
+    def as_layernorm(self):
+        """(weight, bias, eps) if this norm is exactly a LayerNorm with those (a part that normalises inside its
+        own kernel asks for them), else None."""
+        return None
 
 
 class PositionEncoding(Part):

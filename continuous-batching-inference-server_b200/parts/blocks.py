@@ -23,8 +23,22 @@ class PreNormBlock(Block):
     (the chain of kernels is the faster of the two as measured), runs part by part."""
 
     def forward(self, ctx, x, pending, cache, state):
-        h = self.norm_mixer.forward(ctx, x, pending)
-        d = self.mixer.forward(ctx, h, cache, state)
+        # A part that normalises inside its own first kernel and adds into the residual stream (a decode step of a
+        # few rows: two kernels fewer per layer) is handed the stream; any other gets normalised rows and hands
+        # back what is to be added.
+        if self.mixer.fuses_norm(ctx, self.norm_mixer):
+            if pending is not None:
+                ops.add_delta(x, pending.value, pending.bias)
+            self.mixer.forward_residual(ctx, x, self.norm_mixer, cache, state)
+            d = None
+        else:
+            h = self.norm_mixer.forward(ctx, x, pending)
+            d = self.mixer.forward(ctx, h, cache, state)
+        if self.feed_forward.fuses_norm(ctx, self.norm_feed_forward):
+            if d is not None:
+                ops.add_delta(x, d.value, d.bias)
+            self.feed_forward.forward_residual(ctx, x, self.norm_feed_forward)
+            return None
         h = self.norm_feed_forward.forward(ctx, x, d)
         return self.feed_forward.forward(ctx, h)
 
@@ -68,7 +82,7 @@ class PreNormBlock(Block):
         if plan is False:
             return super().forward_run(ctx, blocks, x, pending, caches, states)
         if pending is not None:            # what the layer before left to be added
-            ops.add_layernorm(x, pending.value, pending.bias, None, None, 0.0, torch.empty_like(x, dtype=ctx.dtype))
+            ops.add_delta(x, pending.value, pending.bias)
         try:
             plan.run(ctx, x)
         except ops.KernelError as err:

@@ -36,6 +36,14 @@ class DenseFeedForward(FeedForward):
     def streamed_weights(self):
         return [self.w1, self.w2]
 
+    def fuses_norm(self, ctx, norm):
+        return ops.ln_linear_takes(ctx, norm, self.w1) and self.inner % 8 == 0
+
+    def forward_residual(self, ctx, x, norm):
+        a = torch.empty((ctx.n_rows, self.inner), dtype=ctx.dtype, device=x.device)
+        ops.ln_linear(x, *norm.as_layernorm(), self.w1, self.b1, self.activation, a)
+        ops.gemm_small_m(a, self.w2, self.b2, None, x, accumulate=True)
+
     def forward(self, ctx, h):
         a = ops.linear(h, self.w1, self.b1, self.activation)
         return Delta(ops.linear(a, self.w2, None, None, out_dtype=torch.float32), self.b2)

@@ -28,6 +28,9 @@ class LayerNorm(Norm):
         self.weight = self._vector(tensors[prefix + "weight"], device)
         self.bias = self._vector(tensors[prefix + "bias"], device)
 
+    def as_layernorm(self):
+        return (self.weight, self.bias, self.eps) if self.weight is not None and self.bias is not None else None
+
     def forward(self, ctx, x, delta: Optional[Delta], rows=None, out_dtype=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
         out = torch.empty((n, self.width), dtype=out_dtype or ctx.dtype, device=x.device)

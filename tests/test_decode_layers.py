@@ -1,4 +1,5 @@
-"""The persistent decode kernel (a run of layers in one launch; an option, CBIS_FUSED_DECODE=1) against the same layers run kernel by kernel and
+"""The two optional forms of a decode step, the persistent kernel (a run of layers in one launch, CBIS_FUSED_DECODE=1)
+and the norm inside the product's kernel (CBIS_LN_LINEAR=1), against the same layers run kernel by kernel and
 against the plain implementation (GPU): head sizes 64 and 128, shared key/value heads, a window, widths that are
 no power of two, 1 to 16 rows, requests of very different lengths side by side, page edges, padding rows of a
 captured step, and generation through the scheduler."""
@@ -24,12 +25,12 @@ def folder_of(tmp_path_factory, cfg, seed):
     return d
 
 
-def decode_logits(eng, seqs, n_prompt, fused):
+def decode_logits(eng, seqs, n_prompt, fused, ln_linear=False):
     """Prompts in one step each, then all requests token by token side by side: logits of every decoded position."""
     from cbis_b200.engine import StepEntry
     from cbis_b200.kernels import ops
-    keep = ops.USE_FUSED_DECODE
-    ops.USE_FUSED_DECODE = fused
+    keep, keep_ln = ops.USE_FUSED_DECODE, ops.USE_LN_LINEAR
+    ops.USE_FUSED_DECODE, ops.USE_LN_LINEAR = fused, ln_linear
     eng.runner._graphs.clear()          # captured decode steps hold the launches of the form they were captured with
     try:
         slots = [eng.open_request(i) for i in range(len(seqs))]
@@ -47,8 +48,43 @@ def decode_logits(eng, seqs, n_prompt, fused):
             eng.close_request(s)
         ops.raise_if_kernel_errors()
     finally:
-        ops.USE_FUSED_DECODE = keep
+        ops.USE_FUSED_DECODE, ops.USE_LN_LINEAR = keep, keep_ln
     return [torch.stack(g) for g in got]
+
+
+@pytest.mark.parametrize("which", ["hd64", "hd128"])
+def test_decode_steps_with_the_norm_inside_the_product_match_kernel_by_kernel_and_plain(tmp_path_factory, which, monkeypatch):
+    """CBIS_LN_LINEAR=1: up to 8 rows normalise inside the kernels of the QKV and the first feed-forward product, and
+    the attention's and the feed-forward's outputs are added into the residual stream by their products; 9 rows and
+    more, and the prompts' steps, go the usual way in the same requests."""
+    import cbis_b200 as cb
+    from cbis_b200.kernels import ops
+    cfg = SMALL_64 if which == "hd64" else SMALL_128
+    folder = folder_of(tmp_path_factory, cfg, 77)
+    V = cfg["vocab_size"]
+    g = torch.Generator().manual_seed(9)
+    lens = [150, 40, 97, 33, 64, 18, 129, 70, 51, 20]
+    n_prompt = [120, 1, 64, 31, 48, 2, 100, 63, 17, 3]
+    seqs = [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+    pcfg, w = plain_gpt.read_model_folder(folder, torch.float64)
+    calls = []
+    real = ops.ln_linear
+    monkeypatch.setattr(ops, "ln_linear", lambda *a: (calls.append(a[0].shape[0]), real(*a))[1])
+    for n_req in (1, 5, 8, 10):
+        eng = cb.Engine(folder, dtype="bfloat16", page_size=16, num_pages=80, max_num_seqs=16, max_batched_tokens=256)
+        chain = decode_logits(eng, seqs[:n_req], n_prompt[:n_req], fused=False)
+        assert not calls
+        inside = decode_logits(eng, seqs[:n_req], n_prompt[:n_req], fused=False, ln_linear=True)
+        assert calls and max(calls) <= 8
+        del calls[:]
+        for i in range(n_req):
+            with torch.no_grad():
+                ref = plain_gpt.forward(pcfg, w, seqs[i])[n_prompt[i]:].float()
+            scale = ref.abs().max().item()
+            assert torch.isfinite(inside[i]).all()
+            assert (inside[i] - ref).abs().max().item() < 0.02 * scale, (n_req, i)
+            assert (inside[i] - chain[i]).abs().max().item() < 0.008 * scale, (n_req, i)
+        assert eng.pool.manager.check() == ""
 
 
 @pytest.mark.parametrize("which", ["hd64", "hd128"])

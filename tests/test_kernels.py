@@ -389,6 +389,63 @@ def test_gemm_small_m(ops, M, N, K):
     assert torch.equal(big[:, N:].cpu(), torch.zeros(M, 3))
 
 
+@pytest.mark.parametrize("M", [1, 2, 5, 8])
+@pytest.mark.parametrize("N,K", [(40, 64), (2048, 2048), (317, 96), (4800, 1600), (1000, 2056), (7, 8), (50, 4104)])
+def test_ln_linear_and_accumulating_product(ops, M, N, K):
+    """LayerNorm inside the product's kernel (rows in registers up to 2,048 wide, read again beyond that; K that is
+    no multiple of the 32-wide K block; one or two column groups to the last block), and the product that adds
+    into a 32-bit matrix, each against 64-bit arithmetic."""
+    g = torch.Generator().manual_seed(M * 11 + N + K)
+    x = torch.randn(M, K, generator=g) * 2.0 + 0.7
+    x[:, K // 2] = 40.0                               # one column far from the mean: a centred variance copes
+    gamma, beta = 1 + 0.1 * torch.randn(K, generator=g), 0.1 * torch.randn(K, generator=g)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    eps = 3e-5
+    xd = x.double()
+    hn = (xd - xd.mean(-1, keepdim=True)) / torch.sqrt(xd.var(-1, unbiased=False, keepdim=True) + eps) * gamma.double() + beta.double()
+    hb = hn.float().to(torch.bfloat16)                # the kernel rounds the normalised rows to bfloat16 once
+    ref = hb.double() @ w.double().t() + b.double()
+    scale = max(1.0, ref.abs().max().item())
+    out = torch.full((M, N + 2), float("nan"), device="cuda")
+    ops.ln_linear(dev(x), dev(gamma), dev(beta), eps, dev(w), dev(b), None, out[:, :N])
+    got = out[:, :N].double().cpu()
+    # a normalised value that lands on the other side of a bfloat16 rounding boundary moves one product by 2^-8 of it
+    assert (got - ref).abs().max() < 2e-3 * scale
+    assert (got - (hn @ w.double().t() + b.double())).abs().max() < 2e-2 * scale
+    assert torch.isnan(out[:, N:]).all()
+    out16 = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.ln_linear(dev(x), dev(gamma), dev(beta), eps, dev(w), None, "gelu_tanh", out16)
+    ref2 = plain_gpt.gelu(hb.double() @ w.double().t(), "gelu_new")
+    assert (out16.double().cpu() - ref2).abs().max() < 1.5e-2 * max(1.0, ref2.abs().max().item())
+    # against the norm kernel and the product kernel one after the other: the same roundings, sums in another order
+    h2 = torch.empty(M, K, dtype=torch.bfloat16, device="cuda")
+    ops.add_layernorm(dev(x), None, None, dev(gamma), dev(beta), eps, h2)
+    two = torch.empty(M, N, device="cuda")
+    ops.gemm_small_m(h2, dev(w), dev(b), None, two)
+    assert (two.double().cpu() - got).abs().max() < 2e-3 * scale
+    # x += a W^T + b
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    acc = torch.randn(M, N, generator=g)
+    want = acc.double() + a.double() @ w.double().t() + b.double()
+    accd = dev(acc.clone())
+    ops.gemm_small_m(dev(a), dev(w), dev(b), None, accd, accumulate=True)
+    assert (accd.double().cpu() - want).abs().max() < 1e-5 * max(1.0, want.abs().max().item()) * math.sqrt(K)
+
+
+def test_ln_linear_refuses_what_it_does_not_take(ops):
+    w = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    v = torch.ones(64, device="cuda")
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.ln_linear(torch.zeros(9, 64, device="cuda"), v, v, 1e-5, w, None, None, torch.empty(9, 16, device="cuda"))
+    w = torch.zeros(16, 60, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError, match="does not take"):
+        ops.ln_linear(torch.zeros(2, 60, device="cuda"), v[:60], v[:60], 1e-5, w, None, None, torch.empty(2, 16, device="cuda"))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_small_m(torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda"), torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda"),
+                         None, None, torch.empty(2, 16, dtype=torch.bfloat16, device="cuda"), accumulate=True)
+
+
 def test_gemm_small_m_refuses_what_it_does_not_take(ops):
     x = torch.zeros(65, 64, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
