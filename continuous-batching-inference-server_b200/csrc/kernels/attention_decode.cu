@@ -223,7 +223,7 @@ paged_decode_bf16_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off,
 // attention_decode_tc.cuh, one block of four warps per (row, head, split).
 // ---------------------------------------------------------------------------------------------
 template <int HD>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_WARPS * 32, 4)   // 128 registers: four blocks per SM
 paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, __nv_bfloat16* kc, __nv_bfloat16* vc,
                        const int* block_table, int max_blocks, const int* row_seq, const int* positions,
                        const int* slot_mapping, __nv_bfloat16* __restrict__ out, int out_ld, float* part,
@@ -231,7 +231,7 @@ paged_decode_tc_kernel(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, _
                        int nsplit) {
   __shared__ DecodeTcShared<HD> sm;
   pdl_trigger();
-  decode_tc_item<HD, true>(qkv, ld, k_off, v_off, kc, vc, block_table, max_blocks, row_seq, positions, slot_mapping, out,
+  decode_tc_item<HD, true, (HD <= 64 ? 2 : 1)>(qkv, ld, k_off, v_off, kc, vc, block_table, max_blocks, row_seq, positions, slot_mapping, out,
                            out_ld, part, counters, n_head, n_kv_head, ps, scale, window, nsplit, blockIdx.x, blockIdx.y,
                            blockIdx.z, threadIdx.x, sm, 0);
 }

@@ -9,13 +9,14 @@ namespace cbis {
 
 constexpr int DEC_WARPS = 4;
 
+// Eight bfloat16 -> float with shifts and masks (a bfloat16 is the upper half of the float): the conversion
+// instruction runs on the special-function pipe, which the value tiles of a decode step kept 58 % busy.
 __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(p[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
 
@@ -66,7 +67,7 @@ template <int HD>
 struct DecodeTcShared {
   float m[DEC_WARPS], l[DEC_WARPS];
   float acc[DEC_WARPS][HD];
-  float p[DEC_WARPS][16];
+  float p[DEC_WARPS][32];      // a warp's weights of the keys of its one or two tiles
   float w[32];
   float inv;
   int is_last;
@@ -76,7 +77,7 @@ struct DecodeTcShared {
 // hardware barrier the group meets at.  STANDALONE: the group is a block launched for this alone, which waits for
 // the kernels ahead (programmatic dependent launch) after it has fetched what they do not write.  The group's
 // threads must have met (group_sync) between two calls, since the calls share `sm`.
-template <int HD, bool STANDALONE>
+template <int HD, bool STANDALONE, int TPW = 1>
 __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld, int k_off, int v_off, __nv_bfloat16* kc,
                                                __nv_bfloat16* vc, const int* block_table, int max_blocks,
                                                const int* row_seq, const int* positions, const int* slot_mapping,
@@ -88,6 +89,10 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
   constexpr int KPL = 32 / LPK;      // keys per warp-wide V load
   constexpr int NV = 16 / KPL;       // V loads per 16-key tile
   constexpr int NT = DEC_WARPS * 32;
+  // TPW: 16-key tiles a warp fetches together and takes through one update of its running maximum and sum.  The
+  // stand-alone kernel takes two at head size 64: as many bytes on their way per warp (8 KB) as at head size 128,
+  // and half the bookkeeping per key.
+  static_assert(TPW == 1 || TPW == 2, "the warp's weights have room for two tiles");
   // The step's tables (rows, positions, block tables) were written before the step's first kernel and the
   // cached keys and values of earlier positions by earlier steps: they are read, and this warp's first
   // tile is fetched, while the kernels ahead (the projection of this step's q, k, v) still run.
@@ -111,23 +116,30 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
   const int g = lane >> 2, t = lane & 3;
 
   const int vsub = lane % LPK, vgrp = lane / LPK;
+  const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
   const unsigned long long pol = l2_evict_first_policy();
-  uint4 kb[2][NC], vb[NV];
-  auto load_tile = [&](int tile) {
-    const int j0 = tile << 4;
-    const int page = bt[j0 / ps];
-    const size_t base = (((size_t)page * n_kv_head + hk) * ps + (j0 % ps)) * HD;   // 16 keys from here are one run
+  uint4 kb[TPW][2][NC], vb[TPW][NV];
+  auto load_tiles = [&](int tile) {       // the warp's TPW tiles from `tile` on, as far as they hold keys of this split
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int u = 0; u < TPW; ++u) {
+      const int j0 = (tile + u) << 4;
+      if (j0 < ke) {
+        const int pi = ps_shift >= 0 ? (j0 >> ps_shift) : j0 / ps;      // a shift where the page size is a power of two
+        const size_t base = (((size_t)bt[pi] * n_kv_head + hk) * ps + (j0 - pi * ps)) * HD;   // 16 keys from here are one run
 #pragma unroll
-      for (int c = 0; c < NC; ++c) kb[nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-    for (int i = 0; i < NV; ++i) vb[i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
+          for (int c = 0; c < NC; ++c)
+            kb[u][nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) vb[u][i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
+      }
+    }
   };
-  int tile = (ks >> 4) + warp;
-  // not the tile that holds the current token: its key and value are stored below, after the wait
-  bool preloaded = (tile << 4) < ke && tile != (pos >> 4);
-  if (preloaded) load_tile(tile);
+  int tile = (ks >> 4) + warp * TPW;
+  // not the tiles that hold the current token: its key and value are stored below, after the wait
+  bool preloaded = (tile << 4) < ke && ((pos >> 4) < tile || (pos >> 4) >= tile + TPW);
+  if (preloaded) load_tiles(tile);
   if (STANDALONE) pdl_wait();
 
   // The current token's key and value go into their page first; the loop below then reads them
@@ -153,55 +165,68 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
-  for (; (tile << 4) < ke; tile += DEC_WARPS) {
-    const int j0 = tile << 4;
-    if (!preloaded) load_tile(tile);
+  for (; (tile << 4) < ke; tile += DEC_WARPS * TPW) {
+    if (!preloaded) load_tiles(tile);
     preloaded = false;
-    // scores of the 16 keys: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1)
-    float sc[2][4];
+    // scores of the 16 keys of each tile: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1).
+    // The warp's tiles share one update of the running maximum and sum.
+    float s4[TPW][4], mx = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+    for (int u = 0; u < TPW; ++u) {
+      const int j0 = (tile + u) << 4;
+      float sc[2][4];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        mma_16816(sc[nt], qa[c].x, 0u, qa[c].y, 0u, kb[nt][c].x, kb[nt][c].y);
-        mma_16816(sc[nt], qa[c].z, 0u, qa[c].w, 0u, kb[nt][c].z, kb[nt][c].w);
+      for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+      if (j0 < ke) {                                  // uniform over the warp
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            mma_16816(sc[nt], qa[c].x, 0u, qa[c].y, 0u, kb[u][nt][c].x, kb[u][nt][c].y);
+            mma_16816(sc[nt], qa[c].z, 0u, qa[c].w, 0u, kb[u][nt][c].z, kb[u][nt][c].w);
+          }
       }
-    }
-    float s4[4], mx = -INFINITY;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = j0 + (e >> 1) * 8 + 2 * t + (e & 1);
-      s4[e] = (g == 0 && j >= kstart && j < ke) ? sc[e >> 1][e & 1] * scale : -INFINITY;
-      mx = fmaxf(mx, s4[e]);
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + (e >> 1) * 8 + 2 * t + (e & 1);
+        s4[u][e] = (g == 0 && j >= kstart && j < ke) ? sc[e >> 1][e & 1] * scale : -INFINITY;
+        mx = fmaxf(mx, s4[u][e]);
+      }
     }
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     mx = __shfl_sync(0xffffffffu, mx, 0);
     const float m_new = fmaxf(m, mx);
-    if (m_new == -INFINITY) continue;                 // no key of this tile is in range (uniform over the warp)
+    if (m_new == -INFINITY) continue;                 // no key of these tiles is in range (uniform over the warp)
     const float corr = expf(m - m_new);
     if (g == 0) {
       float psum = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = expf(s4[e] - m_new);
-        psum += p;
-        sm.p[warp][(e >> 1) * 8 + 2 * t + (e & 1)] = p;
-      }
+      for (int u = 0; u < TPW; ++u)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p = expf(s4[u][e] - m_new);
+          psum += p;
+          sm.p[warp][u * 16 + (e >> 1) * 8 + 2 * t + (e & 1)] = p;
+        }
       l = l * corr + psum;                            // lanes 0..3 each carry a part of the sum
     }
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] *= corr;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const float p = sm.p[warp][i * KPL + vgrp];
-      if (p != 0.f) {                                 // keys out of range have p = 0 and whatever the page holds
-        float vf[8];
-        unpack8(vb[i], vf);
+    for (int u = 0; u < TPW; ++u) {
+      if (((tile + u) << 4) < ke) {
 #pragma unroll
-        for (int d = 0; d < 8; ++d) acc[d] = fmaf(p, vf[d], acc[d]);
+        for (int i = 0; i < NV; ++i) {
+          const float p = sm.p[warp][u * 16 + i * KPL + vgrp];
+          if (p != 0.f) {                             // keys out of range have p = 0 and whatever the page holds
+            float vf[8];
+            unpack8(vb[u][i], vf);
+#pragma unroll
+            for (int d = 0; d < 8; ++d) acc[d] = fmaf(p, vf[d], acc[d]);
+          }
+        }
       }
     }
     __syncwarp();

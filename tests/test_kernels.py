@@ -460,6 +460,36 @@ def test_gemm_small_m_refuses_what_it_does_not_take(ops):
     assert out.shape == (4, 16)
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 4800, 1600), (17, 6400, 1600), (40, 317, 96), (300, 1000, 264), (33, 72, 40), (129, 2056, 520)])
+def test_linear_between_few_rows_and_many_uses_one_rounding(ops, M, N, K):
+    """17 rows and more, below the sizes of the tcgen05 product: bias, and bias with the tanh GELU, applied to the
+    32-bit sums and rounded once, whichever way the product goes (the library's epilogue where the bias is exact in
+    bfloat16, else 32-bit sums and this package's epilogue kernel); exact-erf GELU always the latter."""
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.08).to(torch.bfloat16)
+    b_exact = torch.randn(N, generator=g).to(torch.bfloat16).float()
+    b_32 = b_exact + 1e-4 * torch.randn(N, generator=g)             # not a bfloat16 number: the other way
+    for b in (b_exact, b_32):
+        lin = x.double() @ w.double().t() + b.double()
+        for act, name in ((None, None), ("gelu_tanh", "gelu_new"), ("gelu_erf", "gelu")):
+            ref = plain_gpt.gelu(lin, name) if name else lin
+            out = ops.linear(dev(x), dev(w), dev(b), act)
+            assert out.dtype == torch.bfloat16 and out.shape == (M, N)
+            err = (out.double().cpu() - ref).abs()
+            # one bfloat16 rounding of the exact value (2^-9 relative) and the 32-bit sum's own error
+            assert (err <= ref.abs() * 2 ** -8 + 2e-4 * math.sqrt(K) * 0.08 + 1e-5).all(), (act, err.max().item())
+    on = ops.linear(dev(x), dev(w), dev(b_exact), "gelu_tanh")
+    keep = ops.USE_LIBRARY_EPILOGUE
+    ops.USE_LIBRARY_EPILOGUE = False
+    try:
+        off = ops.linear(dev(x), dev(w), dev(b_exact), "gelu_tanh")
+    finally:
+        ops.USE_LIBRARY_EPILOGUE = keep
+    # the two ways differ by the order of the 32-bit sums only: at most the last bfloat16 bit here and there
+    assert ((on.double() - off.double()).abs() <= off.double().abs() * 2 ** -7 + 1e-5).all()
+
+
 def test_bias_act_out_rounds_once(ops):
     g = torch.Generator().manual_seed(5)
     src, b = torch.randn(9, 130, generator=g) * 3, torch.randn(130, generator=g)
