@@ -375,8 +375,8 @@ def mixed_workload(args, cb, torch) -> int:
                                 prefill_chunk=512)
     rng = random.Random(0)
     prompts = [[rng.randrange(cfgd["vocab_size"]) for _ in range(rng.randint(32, 768))] for _ in range(n_req)]
-    eng.generate(prompts[:8], cb.SamplingParams(max_new_tokens=4))       # warm-up: kernels, some graphs
-    eng.generate(prompts, cb.SamplingParams(max_new_tokens=2))           # graphs of the large buckets
+    eng.generate(prompts[:8], cb.SamplingParams(max_new_tokens=4))       # warm-up: kernels
+    eng.warm_up()                                                        # the decode graphs of every batch bucket
     torch.cuda.synchronize()
     steps0 = eng.steps
     step_ms, step_tokens = [], []

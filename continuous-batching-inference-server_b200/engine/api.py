@@ -143,6 +143,37 @@ class Engine:
             out.append(RequestOutput(f.request_id, list(f.output), f.reason))
         return out
 
+    @torch.no_grad()
+    def warm_up(self) -> int:
+        """Captures the graph of a decode step for every batch-size bucket and class of context lengths now, with
+        short requests of its own, so that none is captured in the middle of serving (a capture stalls the engine
+        for tens of milliseconds at 48 layers).  The engine must be idle.  Returns the number of graphs captured."""
+        runner, mgr = self.runner, self.pool.manager
+        if not runner.use_graphs:
+            return 0
+        if not self.scheduler.idle():
+            raise RuntimeError("warm_up: the engine has requests")
+        keys = [k for k in runner.decode_graph_keys() if k not in runner._graphs]
+        if not keys:
+            return 0
+        slots = []
+        try:
+            for _ in range(max(rows for rows, _ in keys)):
+                slots.append(self.open_request(-1 - len(slots)))
+            per = max(1, runner.max_tokens // 2)
+            for i in range(0, len(slots), per):           # a prompt of two tokens each: decode steps follow it
+                self.forward_step([StepEntry(s, 0, [0, 0], []) for s in slots[i:i + per]])
+            for rows, limit in keys:
+                runner.force_context_class = limit
+                try:
+                    self.forward_step([StepEntry(s, mgr.length(s), [0], [0]) for s in slots[:rows]])
+                finally:
+                    runner.force_context_class = None
+        finally:
+            for s in slots:
+                self.close_request(s)
+        return len(keys)
+
     def _sample(self, logits: torch.Tensor, sampling) -> List[int]:
         R = logits.shape[0]
         out = torch.empty(R, dtype=torch.int32, device=logits.device)

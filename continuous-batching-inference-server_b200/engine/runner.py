@@ -225,6 +225,28 @@ class ModelRunner:
                                         self._dev_view(f"slot_mapping{g}", T), mb))
         return ctx
 
+    def context_class(self, max_ctx: int) -> int:
+        limit = 256
+        while limit < max_ctx:
+            limit *= 4
+        return min(limit, self.model.spec.max_positions)
+
+    def decode_graph_keys(self):
+        """Every (rows, class of context lengths) a decode step can be captured for."""
+        rows, b = [], 1
+        while True:
+            rows.append(self._bucket(b))
+            if rows[-1] >= self.max_seqs:
+                break
+            b *= 2
+        classes, c = [], 256
+        while True:
+            classes.append(min(c, self.model.spec.max_positions))
+            if c >= self.model.spec.max_positions:
+                break
+            c *= 4
+        return [(r, c) for r in sorted(set(rows)) for c in sorted(set(classes))]
+
     def _bucket(self, n: int) -> int:
         b = 1
         while b < n:
@@ -307,10 +329,10 @@ class ModelRunner:
         # a graph holds for a number of rows and a class of context lengths (256, 1024, 4096, ... up to the model's
         # positions): kernels that split a request's keys over blocks size the split for the class's bound, so short
         # requests of a model with many positions are not cut into pieces that are mostly empty
-        limit = 256
-        while limit < info.max_ctx:
-            limit *= 4
-        limit = min(limit, self.model.spec.max_positions)
+        limit = self.context_class(info.max_ctx)
+        forced = getattr(self, "force_context_class", None)     # warm-up: the class is named, the requests are short
+        if forced is not None and forced >= limit:
+            limit = forced
         have = self._graphs.get((rows, limit))
         if have is None:
             ctx = self.build_context(entries, pad_rows=rows, all_logits=True, ctx_limit=limit)

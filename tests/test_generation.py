@@ -96,6 +96,29 @@ def test_decoding_across_the_context_classes_of_the_decode_graphs(tmp_path, dtyp
         assert {limit for _, limit in eng.runner._graphs} == {256, 1024, 1300}
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_warm_up_captures_every_decode_graph_and_changes_no_token(tmp_path, dtype):
+    """``Engine.warm_up`` captures the decode step of every batch-size bucket and context class with requests of its
+    own and gives everything back; generation afterwards captures nothing more and gives the plain
+    implementation's tokens (the same requests as in the test above, whose graphs were captured on the way)."""
+    import cbis_b200 as cb
+    cfgd = dict(tc.TINY_B, n_positions=1300)
+    folder = str(tmp_path / "long_b")
+    cb.write_model_folder(folder, cb.config_from_dict(cfgd), seed=5, scheme=cb.InitScheme(*tc.INIT_B))
+    eng = cb.Engine(folder, dtype=dtype, page_size=8, max_tokens=2700, max_num_seqs=3, max_batched_tokens=512)
+    free = eng.pool.manager.free_pages(0)
+    n = eng.warm_up()
+    assert n == len(eng.runner._graphs) == 3 * 3         # buckets 1, 2, 3 (the most requests) x classes 256, 1024, 1300
+    assert eng.warm_up() == 0
+    assert eng.pool.manager.free_pages(0) == free and eng.pool.manager.check() == "" and eng.scheduler.idle()
+    replays = eng.runner.graph_replays
+    prompts = prompts_for(cfgd, [250, 1015, 10], seed=9)
+    outs = eng.generate(prompts, [cb.SamplingParams(max_new_tokens=n) for n in (16, 16, 40)])
+    check_against_plain(folder, prompts, outs, 0.0, 0, 0, exact=dtype == "float32")
+    assert len(eng.runner._graphs) == 9 and eng.runner.graph_replays > replays
+    assert eng.pool.manager.free_pages(0) == free and eng.pool.manager.check() == ""
+
+
 def test_first_tokens_of_a_sequence(tiny):
     import cbis_b200 as cb
     folder, cfg, page = tiny
