@@ -119,27 +119,39 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
   const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
   const unsigned long long pol = l2_evict_first_policy();
   uint4 kb[TPW][2][NC], vb[TPW][NV];
-  auto load_tiles = [&](int tile) {       // the warp's TPW tiles from `tile` on, as far as they hold keys of this split
+  // The warp's TPW tiles from `tile` on, as far as they hold keys of this split: the keys first (with the tiles'
+  // places in the pages, kept for the values), the values later.
+  size_t base[TPW];
+  auto load_keys = [&](int tile) {
 #pragma unroll
     for (int u = 0; u < TPW; ++u) {
       const int j0 = (tile + u) << 4;
       if (j0 < ke) {
         const int pi = ps_shift >= 0 ? (j0 >> ps_shift) : j0 / ps;      // a shift where the page size is a power of two
-        const size_t base = (((size_t)bt[pi] * n_kv_head + hk) * ps + (j0 - pi * ps)) * HD;   // 16 keys from here are one run
+        base[u] = (((size_t)bt[pi] * n_kv_head + hk) * ps + (j0 - pi * ps)) * HD;   // 16 keys from here are one run
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int c = 0; c < NC; ++c)
-            kb[u][nt][c] = ldcg16_stream(kc + base + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
-#pragma unroll
-        for (int i = 0; i < NV; ++i) vb[u][i] = ldcg16_stream(vc + base + (size_t)i * 256 + lane * 8, pol);
+            kb[u][nt][c] = ldcg16_stream(kc + base[u] + (size_t)(nt * 8 + g) * HD + c * 32 + t * 8, pol);
       }
     }
   };
+  auto load_values = [&](int tile) {      // after load_keys(tile), before the next load_keys
+#pragma unroll
+    for (int u = 0; u < TPW; ++u)
+      if (((tile + u) << 4) < ke) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) vb[u][i] = ldcg16_stream(vc + base[u] + (size_t)i * 256 + lane * 8, pol);
+      }
+  };
   int tile = (ks >> 4) + warp * TPW;
   // not the tiles that hold the current token: its key and value are stored below, after the wait
-  bool preloaded = (tile << 4) < ke && ((pos >> 4) < tile || (pos >> 4) >= tile + TPW);
-  if (preloaded) load_tiles(tile);
+  const bool preloaded = (tile << 4) < ke && ((pos >> 4) < tile || (pos >> 4) >= tile + TPW);
+  if (preloaded) {
+    load_keys(tile);
+    load_values(tile);
+  }
   if (STANDALONE) pdl_wait();
 
   // The current token's key and value go into their page first; the loop below then reads them
@@ -165,9 +177,14 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
+  // A round: the values of this round's tiles are asked for, the scores are taken from the keys (asked for a round
+  // earlier), the keys of the next round are asked for, and the softmax update and P V of this round run while they
+  // come: a warp has loads on their way nearly all the time, not only while it waits for them.
+  bool have_keys = preloaded, have_values = preloaded;
   for (; (tile << 4) < ke; tile += DEC_WARPS * TPW) {
-    if (!preloaded) load_tiles(tile);
-    preloaded = false;
+    if (!have_keys) load_keys(tile);
+    if (!have_values) load_values(tile);
+    have_values = false;
     // scores of the 16 keys of each tile: row 0 of the product sits in lanes 0..3 (keys 8nt + 2t, 8nt + 2t + 1).
     // The warp's tiles share one update of the running maximum and sum.
     float s4[TPW][4], mx = -INFINITY;
@@ -193,6 +210,8 @@ __device__ __forceinline__ void decode_tc_item(const __nv_bfloat16* qkv, int ld,
         mx = fmaxf(mx, s4[u][e]);
       }
     }
+    have_keys = ((tile + DEC_WARPS * TPW) << 4) < ke;
+    if (have_keys) load_keys(tile + DEC_WARPS * TPW);   // the scores above were the last use of this round's keys
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     mx = __shfl_sync(0xffffffffu, mx, 0);
