@@ -92,6 +92,8 @@ PYBIND11_MODULE(_cbis_host, m) {
 
   py::class_<PackInfo>(m, "PackInfo")
       .def_readonly("n_rows", &PackInfo::n_rows)
+      .def_readonly("n_tokens", &PackInfo::n_tokens)
+      .def_readonly("n_wanting", &PackInfo::n_wanting)
       .def_readonly("n_segments", &PackInfo::n_segments)
       .def_readonly("n_logit_rows", &PackInfo::n_logit_rows)
       .def_readonly("n_decode", &PackInfo::n_decode)
@@ -125,5 +127,6 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def("waiting_ids", &Scheduler::waiting_ids)
       .def("schedule", &Scheduler::schedule)
       .def("take_new_slots", &Scheduler::take_new_slots)
-      .def("update", &Scheduler::update);
+      .def("update", &Scheduler::update)
+      .def("update_plan", &Scheduler::update_plan);
 }

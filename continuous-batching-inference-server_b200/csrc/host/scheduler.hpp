@@ -174,6 +174,20 @@ class Scheduler {
     return out;
   }
 
+  // The same with the plan itself: `tokens` holds one token for every entry of the plan that samples, in the plan's order.
+  std::vector<Finished> update_plan(const std::vector<PlannedEntry>& plan, const std::vector<int>& tokens) {
+    std::vector<std::pair<int64_t, int>> sampled;
+    sampled.reserve(tokens.size());
+    size_t k = 0;
+    for (const auto& e : plan) {
+      if (!e.sample) continue;
+      if (k >= tokens.size()) throw std::invalid_argument("update_plan: fewer tokens than sampling entries");
+      sampled.emplace_back(e.request_id, tokens[k++]);
+    }
+    if (k != tokens.size()) throw std::invalid_argument("update_plan: more tokens than sampling entries");
+    return update(sampled);
+  }
+
   // Takes the sampled tokens of the last step, in the order of the plan's sampling entries.
   std::vector<Finished> update(const std::vector<std::pair<int64_t, int>>& sampled) {
     std::vector<Finished> done;

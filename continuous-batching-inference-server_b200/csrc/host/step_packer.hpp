@@ -27,6 +27,8 @@ struct PackEntry {
 
 struct PackInfo {
   int n_rows = 0, n_segments = 0, n_logit_rows = 0, n_decode = 0, max_seg_rows = 0, max_ctx = 0;
+  int n_tokens = 0;        // tokens of the entries (n_rows counts the padding rows of a fixed-size step too)
+  int n_wanting = 0;       // entries that want logits at one place or more
   std::vector<int> seg_rows, seg_ctx;  // per segment, in the step's order (padding segments included)
 };
 
@@ -152,6 +154,8 @@ class StepPacker {
       for (int i = real_rows; i < T; ++i) sm[i] = -1;
     }
     info.n_rows = T;
+    info.n_tokens = real_rows;
+    for (const auto& e : entries) info.n_wanting += !e.want.empty();
     info.n_segments = S;
     info.n_logit_rows = R;
     info.max_seg_rows = *std::max_element(info.seg_rows.begin(), info.seg_rows.end());

@@ -63,6 +63,8 @@ class Engine:
         if self.poison_freed_pages:
             self.pool.manager.record_freed(True)
         self._params: Dict[int, SamplingParams] = {}
+        self._not_greedy = 0          # live requests that sample with a temperature
+        self._sampled = self._sampled_host = self._sampled_event = None
         self._next_id = 0
         self.steps = 0
         self.tokens_run = 0
@@ -114,6 +116,7 @@ class Engine:
         eos = -1 if params.eos_token_id is None else int(params.eos_token_id)
         self.scheduler.add(rid, prompt, int(params.max_new_tokens), eos, bool(params.ignore_eos))
         self._params[rid] = params
+        self._not_greedy += params.temperature > 0
         return rid
 
     def has_unfinished(self) -> bool:
@@ -129,19 +132,23 @@ class Engine:
             self.pool.clear_state(slot)
         self._poison_freed()
         logits = self.runner.step(plan, borrow=True)     # the native plan goes to the native packer as it is
+        info = self.runner.last_info
         self.steps += 1
-        self.last_step_tokens = sum(p.n_tokens for p in plan)
-        self.tokens_run += self.last_step_tokens
-        sampling = [p for p in plan if p.sample]
-        if not sampling:
+        self.last_step_tokens = info.n_tokens
+        self.tokens_run += info.n_tokens
+        if info.n_wanting == 0:
             return []
-        tokens = self._sample(logits, sampling)
-        done = self.scheduler.update([(p.request_id, int(t)) for p, t in zip(sampling, tokens)])
+        tokens = self._sample(logits, plan)
         out = []
-        for f in done:
-            self._params.pop(f.request_id, None)
+        for f in self.scheduler.update_plan(plan, tokens):      # the plan's sampling entries and the tokens, in order
+            self._forget(f.request_id)
             out.append(RequestOutput(f.request_id, list(f.output), f.reason))
         return out
+
+    def _forget(self, request_id: int) -> None:
+        params = self._params.pop(request_id, None)
+        if params is not None:
+            self._not_greedy -= params.temperature > 0
 
     @torch.no_grad()
     def warm_up(self) -> int:
@@ -174,18 +181,28 @@ class Engine:
                 self.close_request(s)
         return len(keys)
 
-    def _sample(self, logits: torch.Tensor, sampling) -> List[int]:
+    def _sample(self, logits: torch.Tensor, plan) -> List[int]:
+        """One token for every row of ``logits`` (the plan's sampling entries, in order), read back to the host."""
         R = logits.shape[0]
-        out = torch.empty(R, dtype=torch.int32, device=logits.device)
-        params = [self._params[p.request_id] for p in sampling]
-        if all(q.temperature <= 0 for q in params):
+        if self._sampled is None or self._sampled.shape[0] < R:
+            n = max(R, self.pool.max_requests)
+            self._sampled = torch.empty(n, dtype=torch.int32, device=logits.device)
+            self._sampled_host = torch.empty(n, dtype=torch.int32).pin_memory()
+            self._sampled_event = torch.cuda.Event()
+        out = self._sampled[:R]
+        if self._not_greedy == 0:
             ops.sample(logits, None, None, out)
         else:
+            sampling = [p for p in plan if p.sample]
+            params = [self._params[p.request_id] for p in sampling]
             temps = torch.tensor([float(q.temperature) for q in params], dtype=torch.float32).to(logits.device)
             keys = torch.tensor([request_key(q.seed, p.request_id, p.output_index) for p, q in zip(sampling, params)],
                                 dtype=torch.int64).to(logits.device)
             ops.sample(logits, temps, keys, out)
-        tokens = out.cpu().tolist()
+        self._sampled_host[:R].copy_(out, non_blocking=True)     # pinned memory: the copy is queued, the event says when it is there
+        self._sampled_event.record(self.runner._current_stream())
+        self._sampled_event.synchronize()
+        tokens = self._sampled_host[:R].tolist()
         # kernels with bounded waits report through one flag on the device: read after every step with prompt
         # portions (several such kernels) and every 64th decode step (the few-rows tcgen05 product); the host has
         # just waited for the step anyway
@@ -210,7 +227,7 @@ class Engine:
         except Exception:
             for rid in ids:                       # a refused prompt leaves nothing of this call behind
                 self.scheduler.abort(rid)
-                self._params.pop(rid, None)
+                self._forget(rid)
             raise
         results: Dict[int, List[int]] = {}
         while self.has_unfinished():

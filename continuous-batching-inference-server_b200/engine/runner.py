@@ -182,6 +182,7 @@ class ModelRunner:
         if self._copied is None:
             self._copied = torch.cuda.Event()
         self._copied.record(self._current_stream())
+        self.last_info = info
         return info
 
     def _current_stream(self):
@@ -344,9 +345,11 @@ class ModelRunner:
             graph, logits = have
             graph.replay()
             self.graph_replays += 1
-        want = [i for i, e in enumerate(entries) if (e.sample if native else len(e.want))]
-        if len(want) == rows:
+        if info.n_wanting == rows:
             return logits
+        if info.n_wanting == len(entries):
+            return logits[:len(entries)]      # the entries' rows come first, in their order; the rest is padding
+        want = [i for i, e in enumerate(entries) if (e.sample if native else len(e.want))]
         return logits[torch.tensor(want, dtype=torch.long, device=logits.device)] if want else logits[:0]
 
     @torch.no_grad()

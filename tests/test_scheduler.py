@@ -56,6 +56,24 @@ def test_prompt_is_cut_into_portions_beside_decoding_requests():
     assert cache.free_slots() == 3
 
 
+def test_update_with_the_plan_pairs_the_tokens_with_the_sampling_entries():
+    cache, sch = make(budget=16, chunk=8)
+    sch.add(0, list(range(5)), 2)
+    sch.add(1, list(range(20)), 2)
+    plan = sch.schedule()                                   # request 0 whole (samples), a portion of request 1 (does not)
+    assert [(p.request_id, p.sample) for p in plan] == [(0, True), (1, False)]
+    with pytest.raises(ValueError, match="fewer tokens"):
+        sch.update_plan(plan, [])
+    with pytest.raises(ValueError, match="more tokens"):
+        sch.update_plan(plan, [50, 51])
+    assert sch.update_plan(plan, [50]) == []
+    plan = sch.schedule()
+    assert [(p.request_id, p.start, len(p.tokens), p.sample) for p in plan] == [(0, 5, 1, True), (1, 8, 8, False)]
+    assert plan[0].tokens == [50]
+    done = sch.update_plan(plan, [51])
+    assert [(f.request_id, f.reason, f.output) for f in done] == [(0, "length", [50, 51])]
+
+
 def test_budget_bounds_every_step_and_all_finish():
     cache, sch = make(budget=10, chunk=6, max_seqs=3)
     lens = [1, 7, 23, 40, 13]
