@@ -72,7 +72,9 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def_readonly("tokens", &PlannedEntry::tokens)
       .def_property_readonly("n_tokens", [](const PlannedEntry& e) { return (int)e.tokens.size(); })
       .def_readonly("sample", &PlannedEntry::sample)
-      .def_readonly("output_index", &PlannedEntry::output_index);
+      .def_readonly("output_index", &PlannedEntry::output_index)
+      .def_readonly("ahead", &PlannedEntry::ahead)
+      .def_readonly("source", &PlannedEntry::source);
 
   py::class_<Finished>(m, "Finished")
       .def_readonly("request_id", &Finished::request_id)
@@ -126,6 +128,8 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def("running_ids", &Scheduler::running_ids)
       .def("waiting_ids", &Scheduler::waiting_ids)
       .def("schedule", &Scheduler::schedule)
+      .def("schedule_ahead", &Scheduler::schedule_ahead)
+      .def("ahead_sources", &Scheduler::ahead_sources)
       .def("take_new_slots", &Scheduler::take_new_slots)
       .def("update", &Scheduler::update)
       .def("update_plan", &Scheduler::update_plan);

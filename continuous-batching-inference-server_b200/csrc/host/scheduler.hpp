@@ -15,6 +15,9 @@
 //     by (request, output index), so it continues as it would have;
 //   * waiting requests are admitted FIFO while a slot, budget and pages for their first
 //     portion are there; a request that could never fit is refused when it is added;
+//   * the step after a launched one can be planned before that one's tokens are known (schedule_ahead), when it is
+//     certain but for the tokens: decoding goes on for everyone whatever is sampled, short of an end-of-sequence
+//     token, and then the request's row of the step planned ahead is computed for nothing;
 //   * a step that preempted admits nobody, and a request that was preempted before comes back
 //     only when everything it holds so far, plus a page, fits beside the running requests:
 //     otherwise the pages it just gave up would let it in again at once, to be recomputed and
@@ -46,6 +49,8 @@ struct PlannedEntry {
   std::vector<int> tokens;   // the tokens to run
   bool sample;               // the portion ends the known tokens: its last row yields the next token
   int output_index;          // index of the token that will be sampled (for the sampling key)
+  bool ahead = false;        // planned by schedule_ahead: the one token is a placeholder, the step before samples it
+  int source = -1;           // ahead: which of the step before's sampled tokens (in its sampling entries' order) it is
 };
 
 struct Finished {
@@ -104,6 +109,7 @@ class Scheduler {
   // Decides the next step.  Pages for every planned portion are taken here.  An empty plan
   // with requests left means nothing can run now (cannot happen while a request is running).
   std::vector<PlannedEntry> schedule() {
+    if (pending_ > 0) throw std::logic_error("schedule: the tokens of the step before have not come back (update)");
     std::vector<PlannedEntry> plan;
     int budget = lim_.max_batched_tokens;
     // Pages behind a window are given back only now: the step that was planned last still read
@@ -161,8 +167,57 @@ class Scheduler {
       emit(r, n, &plan);
       budget -= n;
     }
+    remember_sampling(plan);
     return plan;
   }
+
+  // Plans the step AFTER one whose sampled tokens are still on their way (schedule() or schedule_ahead() has been
+  // called and the update has not), if that step is certain but for its tokens: every running request waits for
+  // exactly one sampled token and goes on decoding whatever it is (it reaches neither its output limit nor the
+  // position limit with it; only an end-of-sequence token can stop it, and then its row of this step is computed
+  // for nothing and update_plan passes over it), nobody waits for admission, and pages for one more token each are
+  // free.  Otherwise an empty plan, and nothing has changed: the caller updates first and calls schedule().
+  // The entries hold a placeholder token (0): the device has the real one, `source` says which of the step before's
+  // sampled tokens it is (a request of that step may have ended meanwhile, so the rows need not line up).
+  std::vector<PlannedEntry> schedule_ahead() {
+    std::vector<PlannedEntry> plan;
+    if (pending_ != 1 || running_.empty() || !waiting_.empty() || (int)running_.size() > lim_.max_batched_tokens)
+      return plan;
+    for (int64_t id : running_) {
+      const Req& r = reqs_.at(id);
+      const int size = (int)r.tokens.size();
+      if (r.computed != size) return plan;                                   // tokens still to be fed, or already a step ahead
+      if (size + 1 - r.prompt_len >= r.max_new || size + 1 > lim_.max_positions) return plan;   // ends with the token on its way
+    }
+    for (int64_t id : running_) cache_->release_out_of_window(reqs_.at(id).slot);   // the step before has been launched
+    for (int g = 0; g < cache_->num_groups(); ++g) {
+      long need = 0;
+      for (int64_t id : running_) need += cache_->pages_needed(reqs_.at(id).slot, g, 1);
+      if (need > cache_->free_pages(g)) return plan;
+    }
+    for (int64_t id : running_) {
+      Req& r = reqs_.at(id);
+      if (!cache_->append(r.slot, 1)) throw std::logic_error("scheduler: pages vanished between check and take");
+      PlannedEntry e;
+      e.request_id = r.id;
+      e.slot = r.slot;
+      e.start = r.computed;
+      e.tokens.assign(1, 0);
+      e.sample = true;
+      e.output_index = (int)r.tokens.size() + 1 - r.prompt_len;
+      e.ahead = true;
+      const auto at = std::find(last_sampling_.begin(), last_sampling_.end(), r.id);
+      if (at == last_sampling_.end()) throw std::logic_error("schedule_ahead: a request awaits a token no step samples");
+      e.source = (int)(at - last_sampling_.begin());
+      r.computed += 1;
+      plan.push_back(std::move(e));
+    }
+    remember_sampling(plan);
+    return plan;
+  }
+
+  // The `source` of every entry of the plan that schedule_ahead() made last; empty if entry i takes token i.
+  std::vector<int> ahead_sources() const { return ahead_sources_; }
 
   // Slots admitted by the last schedule() call; their fixed-size state must be cleared before the step.
   std::vector<int> take_new_slots() {
@@ -182,6 +237,8 @@ class Scheduler {
     for (const auto& e : plan) {
       if (!e.sample) continue;
       if (k >= tokens.size()) throw std::invalid_argument("update_plan: fewer tokens than sampling entries");
+      // a request that ended (or was aborted) while its step planned ahead was on its way: that row was for nothing
+      if (e.ahead && !reqs_.count(e.request_id)) { ++k; continue; }
       sampled.emplace_back(e.request_id, tokens[k++]);
     }
     if (k != tokens.size()) throw std::invalid_argument("update_plan: more tokens than sampling entries");
@@ -191,11 +248,14 @@ class Scheduler {
   // Takes the sampled tokens of the last step, in the order of the plan's sampling entries.
   std::vector<Finished> update(const std::vector<std::pair<int64_t, int>>& sampled) {
     std::vector<Finished> done;
+    if (pending_ > 0) --pending_;
     for (const auto& [id, tok] : sampled) {
       auto it = reqs_.find(id);
       if (it == reqs_.end()) throw std::invalid_argument("update: unknown request " + std::to_string(id));
       Req& r = it->second;
-      if (r.computed != (int)r.tokens.size()) throw std::logic_error("update: request has tokens not yet run");
+      // all known tokens have been run, and with a step planned ahead the one that arrives now has been too
+      if (r.computed != (int)r.tokens.size() && r.computed != (int)r.tokens.size() + 1)
+        throw std::logic_error("update: request has tokens not yet run");
       r.tokens.push_back(tok);
       const int generated = (int)r.tokens.size() - r.prompt_len;
       std::string reason;
@@ -243,6 +303,26 @@ class Scheduler {
     plan->push_back(std::move(e));
   }
 
+  // Notes the requests that the plan samples for, in order; a plan that samples counts as open until its update.
+  void remember_sampling(const std::vector<PlannedEntry>& plan) {
+    std::vector<int64_t> ids;
+    bool identity = true;
+    ahead_sources_.clear();
+    for (const PlannedEntry& e : plan) {
+      if (!e.sample) continue;
+      if (e.ahead) {
+        identity = identity && e.source == (int)ids.size();
+        ahead_sources_.push_back(e.source);
+      }
+      ids.push_back(e.request_id);
+    }
+    if (identity) ahead_sources_.clear();
+    if (!ids.empty()) {
+      ++pending_;
+      last_sampling_ = std::move(ids);
+    }
+  }
+
   void preempt(int64_t id) {
     Req& r = reqs_.at(id);
     cache_->release(r.slot);
@@ -261,6 +341,9 @@ class Scheduler {
   std::deque<int64_t> waiting_;
   std::vector<int64_t> running_;  // in admission order
   long preemptions_ = 0;
+  int pending_ = 0;               // steps planned with sampling entries whose tokens have not come back yet
+  std::vector<int64_t> last_sampling_;   // the requests the last such step samples for, in its entries' order
+  std::vector<int> ahead_sources_;
 };
 
 }  // namespace cbis

@@ -65,6 +65,10 @@ class Engine:
         self._params: Dict[int, SamplingParams] = {}
         self._not_greedy = 0          # live requests that sample with a temperature
         self._sampled = self._sampled_host = self._sampled_event = None
+        self._sampled_turn = 0
+        self._in_flight = None        # a step launched ahead: (plan, rows, host buffer, had prompt portions)
+        self.step_ahead = os.environ.get("CBIS_STEP_AHEAD", "1") != "0"
+        self.steps_ahead = 0          # steps launched before the tokens of the step before were read
         self._next_id = 0
         self.steps = 0
         self.tokens_run = 0
@@ -124,26 +128,60 @@ class Engine:
 
     @torch.no_grad()
     def step(self) -> List[RequestOutput]:
-        """One engine step: plan, run, sample, update.  Returns the requests that finished."""
-        plan = self.scheduler.schedule()
-        if not plan:
-            return []
-        for slot in self.scheduler.take_new_slots():
-            self.pool.clear_state(slot)
+        """One engine step: plan, run, sample, update.  Returns the requests that finished.
+
+        While the device runs a step, the next one is planned, packed and launched if it is certain but for its tokens
+        (``Scheduler.schedule_ahead``: everyone goes on decoding; the sampled tokens stay on the device and feed it),
+        and only then are this step's tokens read back: the host's work per step hides behind the device's.  A call
+        then returns the results of the step launched by the call before."""
+        cur = self._in_flight
+        self._in_flight = None
+        if cur is None:
+            plan = self.scheduler.schedule()
+            if not plan:
+                return []
+            for slot in self.scheduler.take_new_slots():
+                self.pool.clear_state(slot)
+            cur = self._launch(plan, None)
+            if cur is None:
+                return []
+        if self.step_ahead:
+            ahead = self.scheduler.schedule_ahead()
+            if ahead:
+                feed = self._sampled[:len(ahead)]
+                source = self.scheduler.ahead_sources()      # empty: entry i takes the i-th sampled token
+                if source:      # a request of the running step has ended meanwhile: the rows no longer line up
+                    feed = self._sampled[torch.tensor(source, dtype=torch.long).to(self._sampled.device)]
+                self._in_flight = self._launch(ahead, feed)
+                self.steps_ahead += 1
+        plan, tokens = cur[0], self._read_tokens(cur)
+        out = []
+        for f in self.scheduler.update_plan(plan, tokens):      # the plan's sampling entries and the tokens, in order
+            self._forget(f.request_id)
+            out.append(RequestOutput(f.request_id, list(f.output), f.reason))
+        if self._in_flight is not None and self.scheduler.idle():
+            # every request of the step launched ahead has ended (an end-of-sequence token): it was for nothing,
+            # and its tokens go back to the scheduler now, which passes over them, so that nothing is left open
+            stale, self._in_flight = self._in_flight, None
+            self.scheduler.update_plan(stale[0], self._read_tokens(stale))
+        return out
+
+    def _launch(self, plan, feed):
+        """Runs the plan's step and its sampling on the device; returns what ``_read_tokens`` needs, None if the
+        step samples nothing.  ``feed``: tokens on the device for a step planned ahead."""
         self._poison_freed()
-        logits = self.runner.step(plan, borrow=True)     # the native plan goes to the native packer as it is
+        self.runner.feed_tokens = feed
+        try:
+            logits = self.runner.step(plan, borrow=True)     # the native plan goes to the native packer as it is
+        finally:
+            self.runner.feed_tokens = None
         info = self.runner.last_info
         self.steps += 1
         self.last_step_tokens = info.n_tokens
         self.tokens_run += info.n_tokens
         if info.n_wanting == 0:
-            return []
-        tokens = self._sample(logits, plan)
-        out = []
-        for f in self.scheduler.update_plan(plan, tokens):      # the plan's sampling entries and the tokens, in order
-            self._forget(f.request_id)
-            out.append(RequestOutput(f.request_id, list(f.output), f.reason))
-        return out
+            return None
+        return (plan,) + self._sample(logits, plan)
 
     def _forget(self, request_id: int) -> None:
         params = self._params.pop(request_id, None)
@@ -181,14 +219,16 @@ class Engine:
                 self.close_request(s)
         return len(keys)
 
-    def _sample(self, logits: torch.Tensor, plan) -> List[int]:
-        """One token for every row of ``logits`` (the plan's sampling entries, in order), read back to the host."""
+    def _sample(self, logits: torch.Tensor, plan):
+        """One token for every row of ``logits`` (the plan's sampling entries, in order) into ``self._sampled`` on the
+        device, and their copy to pinned host memory queued; returns (rows, host buffer, event of the copy, whether
+        the step held prompt portions)."""
         R = logits.shape[0]
         if self._sampled is None or self._sampled.shape[0] < R:
             n = max(R, self.pool.max_requests)
             self._sampled = torch.empty(n, dtype=torch.int32, device=logits.device)
-            self._sampled_host = torch.empty(n, dtype=torch.int32).pin_memory()
-            self._sampled_event = torch.cuda.Event()
+            self._sampled_host = [torch.empty(n, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._sampled_event = [torch.cuda.Event() for _ in range(2)]
         out = self._sampled[:R]
         if self._not_greedy == 0:
             ops.sample(logits, None, None, out)
@@ -199,17 +239,23 @@ class Engine:
             keys = torch.tensor([request_key(q.seed, p.request_id, p.output_index) for p, q in zip(sampling, params)],
                                 dtype=torch.int64).to(logits.device)
             ops.sample(logits, temps, keys, out)
-        self._sampled_host[:R].copy_(out, non_blocking=True)     # pinned memory: the copy is queued, the event says when it is there
-        self._sampled_event.record(self.runner._current_stream())
-        self._sampled_event.synchronize()
-        tokens = self._sampled_host[:R].tolist()
+        # two host buffers in turn: the one of the step before may still be unread when this step is launched ahead
+        k = self._sampled_turn = 1 - self._sampled_turn
+        self._sampled_host[k][:R].copy_(out, non_blocking=True)     # pinned memory: the copy is queued, the event says when it is there
+        self._sampled_event[k].record(self.runner._current_stream())
+        return R, k, self.last_step_tokens > R
+
+    def _read_tokens(self, launched) -> List[int]:
+        _, R, k, had_portions = launched
+        self._sampled_event[k].synchronize()
+        tokens = self._sampled_host[k][:R].tolist()
         # kernels with bounded waits report through one flag on the device: read after every step with prompt
         # portions (several such kernels) and every 64th decode step (the few-rows tcgen05 product); the host has
         # just waited for the step anyway
         self._unchecked = getattr(self, "_unchecked", 0) + 1
-        if self.last_step_tokens > R or self._unchecked >= 64:
+        if had_portions or self._unchecked >= 64:
             self._unchecked = 0
-            ops.raise_if_kernel_errors(logits.device)
+            ops.raise_if_kernel_errors(self.runner.device)
         return tokens
 
     def generate(self, prompts: Sequence[Sequence[int]],

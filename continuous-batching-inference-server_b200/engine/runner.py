@@ -111,6 +111,8 @@ class ModelRunner:
         self._dev = torch.zeros(off, dtype=torch.int32, device=self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = None    # event after the last host->device copy of the packed buffer
+        self.feed_tokens = None   # int32 tokens on the device that replace the next packed step's (single-token entries, in order)
+        self.last_info = None
         self._stream_obj = None
         # decode-only steps replay a captured CUDA graph unless a part reads device values on the host
         self.use_graphs = all(getattr(part, "capturable", True) for _, part in model.all_parts())
@@ -182,6 +184,11 @@ class ModelRunner:
         if self._copied is None:
             self._copied = torch.cuda.Event()
         self._copied.record(self._current_stream())
+        feed = self.feed_tokens   # stays for the whole step: a step that is captured is packed twice
+        if feed is not None:      # a step planned ahead: its tokens are the ones the step before sampled, still on the device
+            if info.n_decode < feed.shape[0] or info.n_tokens != feed.shape[0]:
+                raise StepError("a step fed from the device holds one token for each of the sampled ones")
+            self._dev_view("tokens", feed.shape[0]).copy_(feed)
         self.last_info = info
         return info
 

@@ -119,6 +119,47 @@ def test_warm_up_captures_every_decode_graph_and_changes_no_token(tmp_path, dtyp
     assert eng.pool.manager.free_pages(0) == free and eng.pool.manager.check() == ""
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_steps_launched_ahead_give_the_tokens_of_steps_in_turn(folder_b, dtype, temperature):
+    """While a decode step runs, the next is planned and launched with the sampled tokens fed on the device
+    (CBIS_STEP_AHEAD, on by default).  The same requests with it and without: the same tokens, also when a request
+    stops on an end-of-sequence token while its row of the next step is on its way (the rows of the step after no
+    longer line up with the sampled tokens), when requests end by length at different steps, and when pages run out
+    and a request is preempted."""
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_B, [3, 17, 9, 30, 5], 21)
+    lens = [12, 25, 7, 18, 30]
+
+    def run(ahead, eos, num_pages=40):
+        eng = cb.Engine(folder_b, dtype=dtype, page_size=tc.PAGE_B, num_pages=num_pages, max_num_seqs=4,
+                        max_batched_tokens=48, prefill_chunk=16)
+        eng.step_ahead = ahead
+        params = [cb.SamplingParams(max_new_tokens=n, temperature=temperature, seed=5, eos_token_id=e)
+                  for n, e in zip(lens, eos)]
+        outs = eng.generate(prompts, params)
+        assert eng.pool.manager.check() == "" and eng.pool.manager.free_pages(0) == num_pages and eng._in_flight is None
+        return outs, eng
+
+    none = [None] * 5
+    base, eng = run(False, none)
+    assert eng.steps_ahead == 0
+    got, eng = run(True, none)
+    assert got == base and eng.steps_ahead > 20
+    if dtype == "float32":
+        check_against_plain(folder_b, prompts, got, temperature, 5, 0, exact=True)
+    # requests 1 and 4 stop early: on the token they produced as their 6th and 11th output
+    eos = [None, base[1][5], None, None, base[4][10]]
+    want, _ = run(False, eos)
+    assert len(want[1]) <= 6 and len(want[4]) <= 11 and want[1][-1] == eos[1] and want[4][-1] == eos[4]
+    got, eng = run(True, eos)
+    assert got == want and eng.steps_ahead > 5
+    # few pages: the newest request is preempted and recomputed; planning ahead stops where pages are short
+    want, e0 = run(False, none, num_pages=12)
+    got, e1 = run(True, none, num_pages=12)
+    assert got == want == base and e0.scheduler.preemptions() > 0 and e1.scheduler.preemptions() > 0
+
+
 def test_first_tokens_of_a_sequence(tiny):
     import cbis_b200 as cb
     folder, cfg, page = tiny

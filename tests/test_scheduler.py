@@ -227,3 +227,147 @@ def test_random_workloads_finish_with_books_kept(seed):
     for r, out in done.items():
         assert out == [1000 + k for k in range(want[r])]
     assert cache.free_pages(0) == cache.num_pages(0) and cache.check() == ""
+
+
+# ---- the step after a launched one, planned before its tokens are known -------------------------------------
+
+def drive(cache, sch, arrivals, token, ahead):
+    """Runs the scheduler as the engine does.  ``arrivals``: {step: [(id, prompt, max_new, eos)]}; ``token(id, k)``
+    is request id's k-th output.  With ``ahead`` the next step is planned (schedule_ahead) before the tokens of the
+    running one are given back.  Returns ({id: (reason, output)}, the rows run per step as (id, start, count),
+    how many steps were planned ahead)."""
+    done, steps, n_ahead, in_flight = {}, [], 0, None
+
+    def rows(plan):
+        return [(p.request_id, p.start, len(p.tokens)) for p in plan]
+
+    def tokens(plan):
+        return [token(p.request_id, p.output_index) for p in plan if p.sample]
+
+    for step in range(5000):
+        for a in arrivals.get(step, []):
+            sch.add(*a)
+        cur, in_flight = in_flight, None
+        if cur is None:
+            if sch.idle():
+                if step > max(arrivals, default=0):
+                    break
+                continue
+            cur = sch.schedule()
+            assert cur and cache.check() == ""
+            steps.append(rows(cur))
+            if not any(p.sample for p in cur):
+                continue
+        if ahead:
+            nxt = sch.schedule_ahead()
+            assert cache.check() == ""
+            if nxt:
+                assert all(p.ahead and p.sample and p.tokens == [0] for p in nxt)
+                sampling = [p.request_id for p in cur if p.sample]
+                assert [sampling[p.source] for p in nxt] == [p.request_id for p in nxt]
+                assert sch.ahead_sources() == ([] if [p.source for p in nxt] == list(range(len(nxt))) else [p.source for p in nxt])
+                in_flight = nxt
+                steps.append(rows(nxt))
+                n_ahead += 1
+        for f in sch.update_plan(cur, tokens(cur)):
+            done[f.request_id] = (f.reason, list(f.output))
+        if in_flight is not None and sch.idle():
+            assert sch.update_plan(in_flight, tokens(in_flight)) == []
+            in_flight = None
+    assert sch.idle() and in_flight is None
+    assert cache.free_pages(0) == cache.num_pages(0) and cache.check() == ""
+    return done, steps, n_ahead
+
+
+def test_steps_planned_ahead_are_the_steps_planned_in_turn():
+    """Without end-of-sequence tokens every step planned ahead is, row for row, the step that schedule() plans
+    after the update; with them the requests end with the same outputs, and a request that ended while its row of
+    the next step was on its way is passed over when that step's tokens come back."""
+    arrivals = {0: [(0, [1, 2, 3, 4, 5], 9, -1, False), (1, list(range(11)), 4, -1, False), (2, [7] * 6, 12, -1, False)]}
+    tok = lambda rid, k: 100 * rid + k
+    want, steps_sync, n0 = drive(*make(budget=16, chunk=8), arrivals, tok, ahead=False)
+    got, steps_ahead, n1 = drive(*make(budget=16, chunk=8), arrivals, tok, ahead=True)
+    assert n0 == 0 and n1 > 8
+    assert got == want and steps_ahead == steps_sync
+    # a request that arrives while a step planned ahead is on its way is admitted a step later, and ends the same
+    later = dict(arrivals)
+    later[4] = [(3, [9, 9, 9], 5, -1, False)]
+    want, steps_sync, _ = drive(*make(budget=16, chunk=8), later, tok, ahead=False)
+    got, steps_ahead, _ = drive(*make(budget=16, chunk=8), later, tok, ahead=True)
+    assert got == want and got[3] == ("length", [300 + k for k in range(5)])
+    first = lambda steps: min(i for i, st in enumerate(steps) if any(r[0] == 3 for r in st))
+    assert first(steps_ahead) == first(steps_sync) + 1
+    # request 0 stops at its third output, request 2 at its sixth: their rows of the steps planned ahead are for nothing
+    eos = {0: [(0, [1, 2, 3, 4, 5], 9, 2, False), (1, list(range(11)), 14, -1, False)], 3: [(2, [7] * 6, 12, 205, False)]}
+    want, steps_sync, _ = drive(*make(budget=16, chunk=8), eos, tok, ahead=False)
+    got, steps_ahead, n1 = drive(*make(budget=16, chunk=8), eos, tok, ahead=True)
+    assert want[0] == ("stop", [0, 1, 2]) and want[2] == ("stop", [200 + k for k in range(6)])
+    assert got == want and n1 > 5
+    in_turn = {r for s in steps_sync for r in s}
+    extra = [r for s in steps_ahead for r in s if r not in in_turn]
+    assert extra == [(0, 7, 1), (2, 11, 1)]              # the end-of-sequence token fed once, for nothing, each
+
+
+def test_what_cannot_be_planned_ahead():
+    cache, sch = make(num_pages=6, page=4, max_seqs=2, budget=16, chunk=8, positions=64)
+    assert sch.schedule_ahead() == []                       # nothing runs
+    sch.add(0, [1, 2, 3], 3)
+    sch.add(1, list(range(12)), 6)
+    plan = sch.schedule()                                   # request 0 whole, 8 tokens of request 1
+    assert [(p.request_id, p.sample) for p in plan] == [(0, True), (1, False)]
+    assert sch.schedule_ahead() == []                       # request 1 still has tokens to feed
+    with pytest.raises(RuntimeError, match="have not come back"):
+        sch.schedule()
+    sch.update_plan(plan, [50])
+    plan = sch.schedule()                                   # both sample now
+    assert [(p.request_id, p.start, len(p.tokens), p.sample) for p in plan] == [(0, 3, 1, True), (1, 8, 4, True)]
+    ahead = sch.schedule_ahead()
+    assert [(p.request_id, p.start, p.tokens, p.output_index, p.ahead) for p in ahead] == [(0, 4, [0], 2, True), (1, 12, [0], 1, True)]
+    assert sch.schedule_ahead() == []                       # one step ahead, not two
+    sch.update_plan(plan, [51, 60])
+    assert sch.schedule_ahead() == []                       # request 0's third output is its last: the step after holds one row less
+    done = sch.update_plan(ahead, [52, 61])
+    assert [(f.request_id, f.output) for f in done] == [(0, [50, 51, 52])]
+    plan = sch.schedule()
+    assert [(p.request_id, p.start, p.tokens) for p in plan] == [(1, 13, [61])]
+    sch.add(2, [5, 5], 4)
+    assert sch.schedule_ahead() == []                       # somebody waits for admission
+    sch.update_plan(plan, [62])
+    plan = sch.schedule()
+    assert [(p.request_id, p.start) for p in plan] == [(1, 14), (2, 0)]
+    # pages: request 1 holds 4 pages (15 tokens), request 2 one; the pool has 6; one more token for request 1 needs a fifth
+    ahead = sch.schedule_ahead()
+    assert [(p.request_id, p.start) for p in ahead] == [(1, 15), (2, 2)] and cache.free_pages(0) == 1
+    sch.update_plan(plan, [63, 70])
+    nxt = sch.schedule_ahead()                              # request 1 at 16 tokens takes the last page
+    assert [(p.request_id, p.start) for p in nxt] == [(1, 16), (2, 3)] and cache.free_pages(0) == 0
+    sch.update_plan(ahead, [64, 71])
+    assert sch.schedule_ahead() == []                       # request 1's sixth output, its last, is on its way
+    done = sch.update_plan(nxt, [65, 72])
+    assert [(f.request_id, f.output) for f in done] == [(1, [60, 61, 62, 63, 64, 65])]
+    assert cache.check() == "" and cache.free_pages(0) == 5      # request 2 keeps its one page
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_planned_ahead_end_like_those_planned_in_turn(seed):
+    rng = random.Random(100 + seed)
+    window = rng.choice([0, 0, 12])
+    kw = dict(num_pages=rng.randint(12, 30), page=rng.choice([2, 4, 8]), max_seqs=rng.randint(1, 5),
+              budget=rng.randint(4, 24), chunk=rng.randint(2, 16), positions=48, window=window)
+    arrivals, rid = {}, 0
+    for step in range(120):
+        if rng.random() < 0.25:
+            n, g = rng.randint(1, 30), rng.randint(1, 12)
+            eos = rng.choice([-1, -1, 7])
+            probe_cache, probe = make(**kw)
+            try:
+                probe.add(rid, [rid] * n, g, eos, False)
+            except ValueError:
+                continue                                     # can never fit: refused at add
+            arrivals.setdefault(step, []).append((rid, [rid] * n, g, eos, False))
+            rid += 1
+    tok = lambda r, k: 7 if (r * 31 + k * 17) % 11 == 0 else 1000 + k
+    want, _, _ = drive(*make(**kw), arrivals, tok, ahead=False)
+    got, _, n_ahead = drive(*make(**kw), arrivals, tok, ahead=True)
+    assert got == want and len(want) == rid
+    assert n_ahead > 0 or rid == 0
