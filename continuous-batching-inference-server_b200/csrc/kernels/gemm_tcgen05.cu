@@ -520,7 +520,46 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           }
         }
       }
-      if (sizeof(TO) != 2 || !c_by_tma) {
+      if constexpr (sizeof(TO) == 4) {
+        if (c_by_tma) {
+          // 32-bit results: pieces of 16 columns (the same 64 bytes of a thread's row), staged the same way; one TMA
+          // copy stores the piece, or adds it into C (c_by_tma 2: C is the residual stream, C += A W^T + bias).
+          // The tile's width is a multiple of 16, so the pieces do not overlap (a sum must not be added twice);
+          // rows past M and columns past N are clipped by the copy.
+          unsigned char* mine = staging + (warp - 2) * P2_STAGING_BYTES;
+          for (int c0 = turn * 16; c0 < bn; c0 += 16 * (TC_EPI_WARPS / 4)) {
+            if (n0 + c0 >= N) break;
+            float v[16];
+            tmem_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + buf * TC_BN + (unsigned)c0, v);
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the copy before has read `mine`
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float o[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int n = n0 + c0 + q * 4 + i;
+                o[i] = activate(v[q * 4 + i] + ((bias && n < N) ? bias[n] : 0.f), act);
+              }
+              *reinterpret_cast<float4*>(mine + lane * 64 + ((q ^ ((lane >> 1) & 3)) * 16)) = make_float4(o[0], o[1], o[2], o[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              if (c_by_tma == 2)
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&map_c), "r"(n0 + c0), "r"(m0 + quarter * 32), "r"(smem_u32(mine))
+                             : "memory");
+              else
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&map_c), "r"(n0 + c0), "r"(m0 + quarter * 32), "r"(smem_u32(mine))
+                             : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+      }
+      if (!c_by_tma) {
         for (int c0 = turn * 16; c0 < bn; c0 += 16 * (TC_EPI_WARPS / 4)) {
           if (n0 + c0 >= N) break;
           float v[16];
@@ -601,6 +640,19 @@ static int make_map_c(CUtensorMap* map, void* ptr, int rows, int N, int ld) {
   return r == CUDA_SUCCESS ? CBIS_OK : CBIS_ERR_BAD_SIZE;
 }
 
+// The 32-bit result [rows, N] with row pitch ld as a 2-D tensor for copies of 32 rows x 16 columns, 64-byte swizzle.
+static int make_map_c_f32(CUtensorMap* map, void* ptr, int rows, int N, int ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return CBIS_ERR_BAD_SIZE;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  const cuuint32_t box[2] = {16, 32};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? CBIS_OK : CBIS_ERR_BAD_SIZE;
+}
+
 }  // namespace cbis
 
 using namespace cbis;
@@ -609,19 +661,21 @@ using namespace cbis;
 // null, C [M, ldc] bfloat16 or float.  error: int on the device, set non-zero if a wait inside the kernel ran out.
 // spin_limit (0: the service limit) and starve are for the single-block form (M <= 128) and exist for the test
 // of the give-up path: see the kernel.  With starve the result is not computed and *error becomes non-zero.
+// accumulate (32-bit C, more than 128 rows, 16-byte aligned rows of C): C += act(A W^T + bias); refused otherwise.
 CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
                                           int M, int N, int K, int act, int out_dtype, int* error, void* stream,
-                                          unsigned spin_limit, int starve);
+                                          unsigned spin_limit, int starve, int accumulate);
 
 CBIS_EXPORT int cbis_gemm_tcgen05_bf16(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
                                        int M, int N, int K, int act, int out_dtype, int* error, void* stream) {
-  return cbis_gemm_tcgen05_bf16_ex(A, lda, W, bias, C, ldc, M, N, K, act, out_dtype, error, stream, 0, 0);
+  return cbis_gemm_tcgen05_bf16_ex(A, lda, W, bias, C, ldc, M, N, K, act, out_dtype, error, stream, 0, 0, 0);
 }
 
 CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W, const float* bias, void* C, int ldc,
                                           int M, int N, int K, int act, int out_dtype, int* error, void* stream,
-                                          unsigned spin_limit, int starve) {
+                                          unsigned spin_limit, int starve, int accumulate) {
   if (M <= 0 || N <= 0) return CBIS_OK;
+  if (accumulate && (out_dtype != CBIS_F32 || M <= TC_BM || starve || !pair_enabled())) return CBIS_ERR_BAD_SIZE;
   if (spin_limit == 0) spin_limit = TC_SPIN_LIMIT;
   if (starve && M > TC_BM) return CBIS_ERR_BAD_SIZE;     // only the single-block form can be starved
   if (K <= 0 || K % 8 || lda % 8 || lda < K || ldc < N) return CBIS_ERR_BAD_SIZE;
@@ -648,8 +702,13 @@ CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W,
     if (st != CBIS_OK) return st;
     // the result goes out through TMA when it is bfloat16, 16-byte aligned rows and at least one piece wide
     CUtensorMap map_c = map_a;
-    const int c_by_tma = out_dtype == CBIS_BF16 && ((uintptr_t)C & 15) == 0 && ldc % 8 == 0 && N >= 32 &&
-                         make_map_c(&map_c, C, M, N, ldc) == CBIS_OK;
+    int c_by_tma = out_dtype == CBIS_BF16 && ((uintptr_t)C & 15) == 0 && ldc % 8 == 0 && N >= 32 &&
+                   make_map_c(&map_c, C, M, N, ldc) == CBIS_OK;
+    // ... and when it is 32-bit with 16-byte aligned rows: pieces of 16 columns, stored or added into C
+    if (out_dtype == CBIS_F32 && ((uintptr_t)C & 15) == 0 && ldc % 4 == 0 && N >= 16 &&
+        make_map_c_f32(&map_c, C, M, N, ldc) == CBIS_OK)
+      c_by_tma = accumulate ? 2 : 1;
+    if (accumulate && c_by_tma != 2) return CBIS_ERR_ALIGNMENT;
     const size_t smem = (size_t)P2_STAGES * P2_STAGE_BYTES + TC_EPI_WARPS * P2_STAGING_BYTES + 1024 + 256;
     const int num_tiles = ((N + bn - 1) / bn) * m_tiles;
     const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
@@ -664,8 +723,8 @@ CBIS_EXPORT int cbis_gemm_tcgen05_bf16_ex(const void* A, int lda, const void* W,
       auto kern = gemm_tcgen05_pair_kernel<float>;
       e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      e = launch_pdl(kern, grid, dim3(TC_THREADS), smem, (cudaStream_t)stream, map_a, map_w, map_c, 0, bias, (float*)C, ldc,
-                     M, N, K, act, bn, error);
+      e = launch_pdl(kern, grid, dim3(TC_THREADS), smem, (cudaStream_t)stream, map_a, map_w, map_c, c_by_tma, bias, (float*)C,
+                     ldc, M, N, K, act, bn, error);
     } else {
       return CBIS_ERR_BAD_DTYPE;
     }

@@ -71,6 +71,8 @@ class StepContext:
         self.max_ctx = 0
         self.pool: Optional[CachePool] = None
         self.position_encoding = None          # the model's position encoding: mixers call it if it acts inside them
+        self.residual = None                   # while a block runs a part: the 32-bit residual rows, for a part that adds
+                                               # its result there itself (it then hands back nothing to be added)
         self.runner = None
         self.fixed_shapes = False              # the step is being captured for replay: no size may depend on this batch
         self.max_positions = 0

@@ -204,6 +204,9 @@ def _next_of(w_nk):
     return _ptr(nxt), ctypes.c_ulonglong(min(nxt.numel() * 2, PREFETCH_CAP) if nxt is not None else 0)
 
 
+SMALL_WEIGHT = 1 << 20
+
+
 def gemm_small_m(x, w_nk, bias, act, out, accumulate=False):
     """out = act(x @ w_nk^T + bias) for up to 64 rows of bfloat16, 32-bit accumulation (weight streaming).
     ``accumulate`` (32-bit ``out`` only): the result is added to what ``out`` holds."""
@@ -348,12 +351,13 @@ def tcgen05_error_flag(device) -> torch.Tensor:
     return _tc_error[key]
 
 
-def gemm_tcgen05(x, w_nk, bias, act, out, spin_limit: int = 0, starve: bool = False):
+def gemm_tcgen05(x, w_nk, bias, act, out, spin_limit: int = 0, starve: bool = False, accumulate: bool = False):
     """out = act(x @ w_nk^T + bias) on the tcgen05 tensor cores (TMA operands, accumulator in tensor
     memory, bias and activation on the 32-bit sums).  bfloat16, K a multiple of 8.
     ``spin_limit`` (0: the service limit) bounds every wait inside the kernel; ``starve`` (up to 128 rows,
     for the test of the give-up path) makes the kernel request no operands, so that its waits run out:
-    it then sets the error flag (``tcgen05_error_flag``), frees its tensor memory and returns."""
+    it then sets the error flag (``tcgen05_error_flag``), frees its tensor memory and returns.
+    ``accumulate`` (32-bit ``out``, more than 128 rows): the result is added into ``out`` (a TMA reduction)."""
     _need_cuda(x, w_nk, bias, out)
     M, K = x.shape
     N = w_nk.shape[0]
@@ -362,8 +366,30 @@ def gemm_tcgen05(x, w_nk, bias, act, out, spin_limit: int = 0, starve: bool = Fa
     st = kernels().cbis_gemm_tcgen05_bf16_ex(_ptr(x), c_int(x.stride(0)), _ptr(w_nk), _ptr(bias), _ptr(out),
                                              c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(ACT[act]),
                                              c_int(dtype_code(out.dtype)), _ptr(tcgen05_error_flag(x.device)), _stream(),
-                                             ctypes.c_uint(spin_limit), c_int(1 if starve else 0))
-    _check(st, "gemm_tcgen05", f"M={M} N={N} K={K}")
+                                             ctypes.c_uint(spin_limit), c_int(1 if starve else 0), c_int(1 if accumulate else 0))
+    _check(st, "gemm_tcgen05", f"M={M} N={N} K={K}" + (" accumulate" if accumulate else ""))
+
+
+# 1: products whose result is added to the residual stream (attention output, feed-forward output) add it there
+# themselves where the TMA + tcgen05 product has tiles enough (prompts): bias and sum in its epilogue, a TMA reduction
+# into the 32-bit rows; 0: the library product writes 32-bit sums and the next norm adds them.
+USE_LINEAR_ADD = __import__("os").environ.get("CBIS_LINEAR_ADD", "1") != "0"
+USE_TCGEN05_PAIR = __import__("os").environ.get("CBIS_TCGEN05_PAIR", "1") != "0"    # the kernel library reads the same variable
+
+
+def linear_add_takes(x, w_nk, residual) -> bool:
+    """Whether ``linear_add`` takes this product: bfloat16 rows enough for the tcgen05 product's tiles, aligned."""
+    if not (USE_LINEAR_ADD and USE_TCGEN05 and USE_TCGEN05_PAIR) or residual is None or x.dtype != torch.bfloat16:
+        return False
+    M, K = x.shape
+    N = w_nk.shape[0]
+    return (M > 128 and tc_tiles(M, N) and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and residual.dtype == torch.float32 and residual.stride(0) % 4 == 0 and residual.data_ptr() % 16 == 0 and N >= 16)
+
+
+def linear_add(x, w_nk, bias, residual) -> None:
+    """residual += x @ w_nk^T + bias (32-bit residual rows, bfloat16 operands, 32-bit sums)."""
+    gemm_tcgen05(x, w_nk, bias, None, residual, accumulate=True)
 
 
 def linear(x, w_nk, bias, act=None, out_dtype=None):
@@ -383,7 +409,9 @@ def linear(x, w_nk, bias, act=None, out_dtype=None):
     _need_cuda(x, w_nk)
     out_dtype = out_dtype or x.dtype
     aligned = K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-    if M <= SMALL_M and aligned:
+    # up to 16 rows; up to 64 where the weight is small (a million elements: any kernel takes a few microseconds, and the
+    # library's call costs the host 15-60 us, this one 6, with the epilogue inside)
+    if aligned and (M <= SMALL_M or (M <= 64 and N * K <= SMALL_WEIGHT)):
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         gemm_small_m(x, w_nk, bias, act, out)
         return out

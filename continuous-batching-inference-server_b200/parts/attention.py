@@ -64,6 +64,9 @@ class PagedAttention(Mixer):
 
     def forward(self, ctx, h, cache, state):
         out = self._attend(ctx, ops.linear(h, self.w_qkv, self.b_qkv), cache)
+        if ops.linear_add_takes(out, self.w_o, ctx.residual):      # the product adds into the residual stream itself
+            ops.linear_add(out, self.w_o, self.b_o, ctx.residual)
+            return None
         return Delta(ops.linear(out, self.w_o, None, None, out_dtype=torch.float32), self.b_o)
 
     def _attend(self, ctx, qkv, cache):

@@ -127,7 +127,9 @@ class Mixer(Part):
         """``cache``: the ``LayerCache`` of this layer (or of the layer it reads), None if it keeps none;
         ``cache.arrays[name]`` are its pages ``[num_pages, heads, page_size, width]``, addressed through
         ``ctx.groups[cache.group]`` (block table per segment, token slot per row).
-        ``state``: ``[max_requests, *shape]`` if it declared a state; row ``ctx.seg_slot[s]`` belongs to segment s."""
+        ``state``: ``[max_requests, *shape]`` if it declared a state; row ``ctx.seg_slot[s]`` belongs to segment s.
+        Returns what is to be added to the residual stream; or None after adding it itself into ``ctx.residual``
+        (the 32-bit rows, set while a block runs its parts), which a part is free to ignore."""
         raise NotImplementedError
 
     # Optional: a mixer may take the residual stream itself, normalise it inside its first kernel and add its result

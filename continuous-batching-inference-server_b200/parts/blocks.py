@@ -33,14 +33,19 @@ class PreNormBlock(Block):
             d = None
         else:
             h = self.norm_mixer.forward(ctx, x, pending)
+            ctx.residual = x          # a part may add its result into the stream itself and hand back None
             d = self.mixer.forward(ctx, h, cache, state)
+            ctx.residual = None
         if self.feed_forward.fuses_norm(ctx, self.norm_feed_forward):
             if d is not None:
                 ops.add_delta(x, d.value, d.bias)
             self.feed_forward.forward_residual(ctx, x, self.norm_feed_forward)
             return None
         h = self.norm_feed_forward.forward(ctx, x, d)
-        return self.feed_forward.forward(ctx, h)
+        ctx.residual = x
+        d = self.feed_forward.forward(ctx, h)
+        ctx.residual = None
+        return d
 
     # ---- a run of layers in one kernel ----------------------------------------------------------------
     def _static_run_key(self, cache):

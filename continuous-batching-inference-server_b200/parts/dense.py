@@ -46,6 +46,9 @@ class DenseFeedForward(FeedForward):
 
     def forward(self, ctx, h):
         a = ops.linear(h, self.w1, self.b1, self.activation)
+        if ops.linear_add_takes(a, self.w2, ctx.residual):         # the product adds into the residual stream itself
+            ops.linear_add(a, self.w2, self.b2, ctx.residual)
+            return None
         return Delta(ops.linear(a, self.w2, None, None, out_dtype=torch.float32), self.b2)
 
 

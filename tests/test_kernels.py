@@ -433,6 +433,33 @@ def test_ln_linear_and_accumulating_product(ops, M, N, K):
     assert (accd.double().cpu() - want).abs().max() < 1e-5 * max(1.0, want.abs().max().item()) * math.sqrt(K)
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2048, 2048), (300, 1000, 264), (129, 4800, 72), (513, 24, 4104)])
+def test_tcgen05_product_adds_into_a_32_bit_matrix(ops, M, N, K):
+    """C += A W^T + bias through the TMA reduction of the pair kernel's epilogue, and the plain 32-bit result through
+    its TMA store: rows that are no multiple of the 32-row pieces, a width that is no multiple of the 16-column
+    pieces or of the tile, a matrix wider than the result (columns beside it stay as they are)."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    acc = torch.randn(M, N + 4, generator=g)
+    prod = a.double() @ w.double().t() + b.double()
+    tol = 1e-5 * max(1.0, prod.abs().max().item()) * math.sqrt(K)
+    big = dev(acc.clone())
+    ops.gemm_tcgen05(dev(a), dev(w), dev(b), None, big[:, :N], accumulate=True)
+    assert (big[:, :N].double().cpu() - (acc[:, :N].double() + prod)).abs().max() < tol
+    assert torch.equal(big[:, N:].cpu(), acc[:, N:])
+    ops.gemm_tcgen05(dev(a), dev(w), dev(b), None, big[:, :N], accumulate=True)      # and once more: twice the product
+    assert (big[:, :N].double().cpu() - (acc[:, :N].double() + 2 * prod)).abs().max() < 2 * tol
+    out = torch.full((M, N + 4), float("nan"), device="cuda")
+    ops.gemm_tcgen05(dev(a), dev(w), None, None, out[:, :N])
+    assert (out[:, :N].double().cpu() - (prod - b.double())).abs().max() < tol
+    assert torch.isnan(out[:, N:]).all()
+    assert ops.tcgen05_error_flag("cuda").item() == 0
+    with pytest.raises(ops.KernelError):              # up to 128 rows the single-block form runs, which does not add
+        ops.gemm_tcgen05(dev(a)[:100], dev(w), dev(b), None, big[:100, :N], accumulate=True)
+
+
 def test_ln_linear_refuses_what_it_does_not_take(ops):
     w = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
     v = torch.ones(64, device="cuda")
