@@ -96,6 +96,7 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def_readonly("n_rows", &PackInfo::n_rows)
       .def_readonly("n_tokens", &PackInfo::n_tokens)
       .def_readonly("n_wanting", &PackInfo::n_wanting)
+      .def_readonly("n_wanted", &PackInfo::n_wanted)
       .def_readonly("n_segments", &PackInfo::n_segments)
       .def_readonly("n_logit_rows", &PackInfo::n_logit_rows)
       .def_readonly("n_decode", &PackInfo::n_decode)
@@ -111,9 +112,9 @@ PYBIND11_MODULE(_cbis_host, m) {
       .def("words", &StepPacker::words)
       .def("layout", &StepPacker::layout)
       .def("pack", &StepPacker::pack, py::arg("buffer"), py::arg("entries"), py::arg("pad_rows") = 0,
-           py::arg("all_logits") = false, py::arg("reserved_ahead") = false)
+           py::arg("all_logits") = false, py::arg("reserved_ahead") = false, py::arg("pad_segments") = 0)
       .def("pack_plan", &StepPacker::pack_plan, py::arg("buffer"), py::arg("plan"), py::arg("pad_rows") = 0,
-           py::arg("all_logits") = false);
+           py::arg("all_logits") = false, py::arg("pad_segments") = 0);
 
   py::class_<Scheduler>(m, "Scheduler")
       .def(py::init<CacheManager*, SchedulerLimits>(), py::arg("cache"), py::arg("limits"),

@@ -29,6 +29,7 @@ struct PackInfo {
   int n_rows = 0, n_segments = 0, n_logit_rows = 0, n_decode = 0, max_seg_rows = 0, max_ctx = 0;
   int n_tokens = 0;        // tokens of the entries (n_rows counts the padding rows of a fixed-size step too)
   int n_wanting = 0;       // entries that want logits at one place or more
+  int n_wanted = 0;        // places at which logits are wanted (n_logit_rows counts the padding of a fixed-size step too)
   std::vector<int> seg_rows, seg_ctx;  // per segment, in the step's order (padding segments included)
 };
 
@@ -56,7 +57,8 @@ class StepPacker {
   int words() const { return words_; }
   const std::map<std::string, std::pair<int, int>>& layout() const { return layout_; }
 
-  PackInfo pack_plan(uintptr_t buffer, const std::vector<PlannedEntry>& plan, int pad_rows, bool all_logits) const {
+  PackInfo pack_plan(uintptr_t buffer, const std::vector<PlannedEntry>& plan, int pad_rows, bool all_logits,
+                     int pad_segments = 0) const {
     std::vector<PackEntry> es(plan.size());
     for (size_t i = 0; i < plan.size(); ++i) {
       es[i].slot = plan[i].slot;
@@ -64,13 +66,17 @@ class StepPacker {
       es[i].tokens = plan[i].tokens;
       if (plan[i].sample) es[i].want.push_back((int)plan[i].tokens.size() - 1);
     }
-    return pack(buffer, es, pad_rows, all_logits, false);
+    return pack(buffer, es, pad_rows, all_logits, false, pad_segments);
   }
 
   // `reserved_ahead`: the cache may already hold room beyond the step's tokens (a run of decode steps
   // whose pages were taken beforehand).
+  // `pad_rows` alone: a step of single tokens laid out for exactly that many rows and segments (rows beyond the
+  // entries belong to no segment).  With `pad_segments`: any step laid out for pad_rows rows, pad_segments segments
+  // (those beyond the entries hold no rows) and pad_segments wanted rows (those beyond the entries' repeat row 0);
+  // it counts as a step without one-token segments, so that every segment goes the way of the longer ones.
   PackInfo pack(uintptr_t buffer, const std::vector<PackEntry>& entries, int pad_rows, bool all_logits,
-                bool reserved_ahead) const {
+                bool reserved_ahead, int pad_segments = 0) const {
     validate(entries, reserved_ahead);
     int32_t* buf = reinterpret_cast<int32_t*>(buffer);
     auto at = [&](const std::string& name) { return buf + layout_.at(name).first; };
@@ -105,7 +111,24 @@ class StepPacker {
     }
     int T = r, S = n;
     const int real_rows = T, real_segs = S;
-    if (pad_rows > 0) {
+    if (pad_rows > 0 && pad_segments > 0) {
+      if (pad_rows < T || pad_rows > T_ || pad_segments < n || pad_segments > S_ || all_logits)
+        throw std::invalid_argument("a step laid out for fixed sizes must fit them");
+      for (int i = T; i < pad_rows; ++i) {
+        tokens[i] = 0;
+        positions[i] = 0;
+        row_seq[i] = -1;
+      }
+      for (int s = S; s < pad_segments; ++s) {
+        seg_slot[s] = seg_start[s] = seg_ctx[s] = 0;
+        cu[s + 1] = real_rows;
+        info.seg_rows.push_back(0);
+        info.seg_ctx.push_back(0);
+      }
+      T = pad_rows;
+      S = pad_segments;
+      info.n_decode = 0;
+    } else if (pad_rows > 0) {
       if (info.n_decode != n || pad_rows < n || pad_rows > T_ || pad_rows > S_)
         throw std::invalid_argument("a padded step holds single tokens only and fits the engine's limits");
       for (int i = T; i < pad_rows; ++i) {
@@ -129,6 +152,11 @@ class StepPacker {
     } else {
       for (int i = 0; i < n; ++i)
         for (int w : entries[i].want) logit_rows[R++] = row0[i] + w;
+    }
+    info.n_wanted = all_logits ? real_rows : R;
+    if (pad_segments > 0) {
+      if (R > pad_segments) throw std::invalid_argument("a step laid out for fixed sizes wants at most one row per segment");
+      while (R < pad_segments) logit_rows[R++] = 0;
     }
     for (int g = 0; g < n_groups_; ++g) {
       const int ps = cache_->page_size(g), mb = max_blocks_[g];

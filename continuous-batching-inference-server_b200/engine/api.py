@@ -189,35 +189,58 @@ class Engine:
             self._not_greedy -= params.temperature > 0
 
     @torch.no_grad()
-    def warm_up(self) -> int:
-        """Captures the graph of a decode step for every batch-size bucket and class of context lengths now, with
-        short requests of its own, so that none is captured in the middle of serving (a capture stalls the engine
-        for tens of milliseconds at 48 layers).  The engine must be idle.  Returns the number of graphs captured."""
+    def warm_up(self, small_steps: bool = True) -> int:
+        """Captures ahead of serving, with short requests of its own, the graph of a decode step for every batch-size
+        bucket and class of context lengths, so that none is captured in the middle of serving (a capture stalls the
+        engine for tens of milliseconds at 48 layers); and, with ``small_steps``, the graphs of small steps with
+        prompt portions, each kept only if a replay measured now is faster than the same step launch by launch.
+        The engine must be idle.  Returns the number of graphs captured and kept."""
         runner, mgr = self.runner, self.pool.manager
         if not runner.use_graphs:
             return 0
-        if not self.scheduler.idle():
+        if not self.scheduler.idle() or self._in_flight is not None:
             raise RuntimeError("warm_up: the engine has requests")
+        kept = 0
         keys = [k for k in runner.decode_graph_keys() if k not in runner._graphs]
-        if not keys:
-            return 0
+        classes = sorted({limit for _, limit in runner.decode_graph_keys()})
         slots = []
         try:
-            for _ in range(max(rows for rows, _ in keys)):
-                slots.append(self.open_request(-1 - len(slots)))
-            per = max(1, runner.max_tokens // 2)
-            for i in range(0, len(slots), per):           # a prompt of two tokens each: decode steps follow it
-                self.forward_step([StepEntry(s, 0, [0, 0], []) for s in slots[i:i + per]])
-            for rows, limit in keys:
-                runner.force_context_class = limit
-                try:
-                    self.forward_step([StepEntry(s, mgr.length(s), [0], [0]) for s in slots[:rows]])
-                finally:
-                    runner.force_context_class = None
+            if keys:
+                for _ in range(max(rows for rows, _ in keys)):
+                    slots.append(self.open_request(-1 - len(slots)))
+                per = max(1, runner.max_tokens // 2)
+                for i in range(0, len(slots), per):           # a prompt of two tokens each: decode steps follow it
+                    self.forward_step([StepEntry(s, 0, [0, 0], []) for s in slots[i:i + per]])
+                for rows, limit in keys:
+                    runner.force_context_class = limit
+                    try:
+                        self.forward_step([StepEntry(s, mgr.length(s), [0], [0]) for s in slots[:rows]])
+                    finally:
+                        runner.force_context_class = None
+                kept += len(keys)
+            for s in slots:
+                self.close_request(s)
+            slots = []
+            if small_steps and runner.small_step_graphs:
+                # one request of its own per size: a prompt portion of that many rows (as many as the positions and the
+                # pages allow), whose step is captured for every context class
+                bucket = 16
+                while bucket <= runner.small_step_rows:
+                    n = min(bucket, self.model.spec.max_positions)
+                    slot = self.open_request(-1)
+                    slots.append(slot)
+                    if n > bucket // 2 and mgr.append(slot, n):
+                        entries = [StepEntry(slot, 0, [0] * n, [n - 1])]
+                        for limit in classes:
+                            if (runner.small_step_bucket(n), limit) not in runner._small_graphs:
+                                kept += bool(runner.capture_small_step(entries, limit))
+                    self.close_request(slot)
+                    slots.pop()
+                    bucket *= 2
         finally:
             for s in slots:
                 self.close_request(s)
-        return len(keys)
+        return kept
 
     def _sample(self, logits: torch.Tensor, plan):
         """One token for every row of ``logits`` (the plan's sampling entries, in order) into ``self._sampled`` on the

@@ -130,6 +130,19 @@ class ModelRunner:
         self._shape_seen: Dict[tuple, int] = {}
         self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self.shape_captures = self.shape_replays = 0
+        # Small steps with prompt portions (up to small_step_rows rows) whose launches cost the host more than the
+        # device needs to run them: one graph per (rows rounded up to a power of two, class of context lengths), laid
+        # out for max_num_seqs segments and wanted rows; every segment, of one token too, goes the way of the longer ones.
+        self.small_step_graphs = os.environ.get("CBIS_SMALL_STEP_GRAPHS", "1") != "0"
+        self.small_step_rows = min(256, self.max_tokens)
+        self.small_graph_after = 8
+        self.small_graph_host_factor = 1.5      # captured when issuing a step costs the host this many times its device time
+        self._small_graphs: Dict[tuple, tuple] = {}
+        self._small_seen: Dict[tuple, list] = {}
+        self._small_pending = None
+        self.small_captures = self.small_replays = 0
+        # padding segments carry state slot 0: only for models whose mixers keep no state of their own
+        self._small_ok = all(layer.mixer.state_need() is None for layer in model.layers)
         worst = heads = 0
         for layer in model.layers:
             m = layer.mixer
@@ -169,17 +182,17 @@ class ModelRunner:
                 self._counters = torch.zeros(n_counters, dtype=torch.int32, device=self.device)
         return self._scratch, self._counters
 
-    def _pack(self, entries, pad_rows: int, all_logits: bool, reserved_ahead: bool):
+    def _pack(self, entries, pad_rows: int, all_logits: bool, reserved_ahead: bool, pad_segments: int = 0):
         """Validates and packs a step (StepEntry objects, or the scheduler's native plan) into the pinned
         buffer and starts its copy to the device; returns the packer's summary."""
         if self._copied is not None:
             self._copied.synchronize()   # the last step's copy must have left the pinned buffer
         try:
             if entries and not isinstance(entries[0], StepEntry):
-                info = self._packer.pack_plan(self._host_ptr, entries, pad_rows, all_logits)
+                info = self._packer.pack_plan(self._host_ptr, entries, pad_rows, all_logits, pad_segments)
             else:
                 native = [host().PackEntry(e.slot, e.start, list(e.tokens), list(e.want)) for e in entries]
-                info = self._packer.pack(self._host_ptr, native, pad_rows, all_logits, reserved_ahead)
+                info = self._packer.pack(self._host_ptr, native, pad_rows, all_logits, reserved_ahead, pad_segments)
         except ValueError as err:
             raise StepError(str(err)) from None
         self._dev.copy_(self._host, non_blocking=True)
@@ -208,13 +221,15 @@ class ModelRunner:
         self._pack(entries, 0, False, reserved_ahead)
 
     def build_context(self, entries, pad_rows: int = 0, all_logits: bool = False,
-                      reserved_ahead: bool = False, fixed_shapes: bool = False, ctx_limit: int = 0) -> StepContext:
+                      reserved_ahead: bool = False, fixed_shapes: bool = False, ctx_limit: int = 0,
+                      pad_segments: int = 0) -> StepContext:
         """Packs the step into the host buffer, copies it over, returns the views.
 
         ``pad_rows`` > 0 (decode-only steps): the step is laid out for exactly that many rows and
         segments; rows beyond the entries are padding (segment -1: no cache write, zero attention
-        output).  ``all_logits``: every row's logits, whatever the entries want."""
-        info = self._pack(entries, pad_rows, all_logits, reserved_ahead)
+        output).  ``all_logits``: every row's logits, whatever the entries want.  ``pad_segments`` with ``pad_rows``:
+        any step, laid out for exactly that many rows, segments and wanted rows (see the packer)."""
+        info = self._pack(entries, pad_rows, all_logits, reserved_ahead, pad_segments)
         pool = self.pool
         T, S, R = info.n_rows, info.n_segments, info.n_logit_rows
         ctx = StepContext()
@@ -227,7 +242,7 @@ class ModelRunner:
         ctx.cu_rows = self._dev_view("cu_rows", S + 1)
         ctx.logit_rows = self._dev_view("logit_rows", R)
         ctx.host_seg_rows, ctx.host_seg_ctx = list(info.seg_rows), list(info.seg_ctx)
-        ctx.max_seg_rows, ctx.max_ctx = info.max_seg_rows, info.max_ctx
+        ctx.max_seg_rows, ctx.max_ctx = (pad_rows if pad_segments else info.max_seg_rows), info.max_ctx
         ctx.ctx_limit = (ctx_limit or ctx.max_positions) if ctx.fixed_shapes else info.max_ctx
         for g in range(self._n_groups):
             mb = pool.max_blocks(g)
@@ -278,6 +293,13 @@ class ModelRunner:
         if self.use_graphs and decode_only:
             out = self._decode_step_graph(entries, native)
             return out if borrow else out.clone()
+        self._small_pending = None
+        if self.use_graphs and self.small_step_graphs and self._small_ok and native and len(entries) <= self.max_seqs:
+            rows = sum(e.n_tokens for e in entries)
+            if rows <= self.small_step_rows:
+                out = self._small_step_graph(entries, rows)
+                if out is not None:
+                    return out if borrow else out.clone()
         shape = None
         if self.use_graphs and self.shape_graphs and entries:
             shape = self._step_shape(entries, native)
@@ -285,13 +307,100 @@ class ModelRunner:
             if out is not None:
                 return out if borrow else out.clone()
         ctx = self.build_context(entries)
+        pending = self._small_pending
+        if pending is not None:     # this run is timed on the device too
+            pending[2] = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            pending[2][0].record(self._current_stream())
         t0 = time.perf_counter()
         out = self.model.forward(ctx)
+        host_s = time.perf_counter() - t0
+        if pending is not None:
+            pending[2][1].record(self._current_stream())
+            pending[1] = host_s
         if shape is not None:      # what issuing this shape's launches costs the host: decides whether a graph pays
             seen = self._shape_seen.get(shape)
             if seen is not None:
-                seen[1] = time.perf_counter() - t0
+                seen[1] = host_s
         return out
+
+    def small_step_bucket(self, rows: int) -> int:
+        bucket = 16
+        while bucket < rows:
+            bucket *= 2
+        return min(bucket, self.max_tokens)
+
+    def _small_step_graph(self, entries, rows: int):
+        """A small step with prompt portions: replays the graph of its size; or captures it, once steps of that size
+        have come often enough and a run timed on both sides has shown the device starved (its span no longer than
+        the host took to issue the launches); or returns None: the caller runs it launch by launch.
+        ``Engine.warm_up`` decides the same ahead of serving, by measurement (``capture_small_step``)."""
+        bucket = self.small_step_bucket(rows)
+        seen = self._small_seen.setdefault(bucket, [0, 0.0, None, None])   # times seen, host s, events of the timed run, device ms
+        if seen[3] == 0.0:             # measured at warm-up: a graph of this size does not pay
+            return None
+        seen[0] += 1
+        if seen[3] is None:
+            if seen[2] is not None and seen[2][1].query():
+                seen[3] = max(seen[2][0].elapsed_time(seen[2][1]), 1e-6)
+            elif seen[0] >= 2 and seen[2] is None:
+                self._small_pending = seen             # the caller times this run
+        starved = seen[3] is not None and seen[3] <= 1.15 * seen[1] * 1e3
+        have_some = any(k[0] == bucket for k in self._small_graphs)
+        if not have_some and (seen[0] < self.small_graph_after or not starved):
+            return None
+        info = self._pack(entries, bucket, False, False, self.max_seqs)
+        limit = self.context_class(info.max_ctx)
+        have = self._small_graphs.get((bucket, limit))
+        if have is None:
+            _, logits = self._capture_small(entries, bucket, limit)      # the step has run, launch by launch
+        else:
+            graph, logits = have
+            graph.replay()
+            self.graph_replays += 1
+            self.small_replays += 1
+        return logits[:self.last_info.n_wanted]
+
+    def _capture_small(self, entries, bucket: int, limit: int):
+        ctx = self.build_context(entries, pad_rows=bucket, pad_segments=self.max_seqs, fixed_shapes=True, ctx_limit=limit)
+        first = self.model.forward(ctx)                  # runs once, launch by launch; the capture only records
+        graph, logits = capture_graph(lambda: self.model.forward(ctx))
+        logits.copy_(first)
+        self._small_graphs[(bucket, limit)] = (graph, logits)
+        self.small_captures += 1
+        return graph, logits
+
+    @torch.no_grad()
+    def capture_small_step(self, entries, limit: int) -> bool:
+        """Warm-up: runs ``entries`` (a step with a prompt portion; every entry wants at most one row) launch by
+        launch, captures the graph of its size for the context class ``limit`` and times a replay against the
+        launch-by-launch run; keeps the graph if it is at least ``small_graph_host_factor`` times faster, else
+        marks the size as not worth a graph.  The step's rows are run more than once: the same keys and values are
+        written each time."""
+        rows = sum(len(e.tokens) for e in entries)
+        bucket = self.small_step_bucket(rows)
+        if not (self.use_graphs and self.small_step_graphs and self._small_ok) or rows > self.small_step_rows:
+            return False
+        seen = self._small_seen.setdefault(bucket, [0, 0.0, None, None])
+        if seen[3] == 0.0:
+            return False
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        self.model.forward(self.build_context(entries))
+        torch.cuda.synchronize()
+        eager_s = time.perf_counter() - t0
+        graph, logits = self._capture_small(entries, bucket, limit)
+        self._pack(entries, bucket, False, False, self.max_seqs)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        graph.replay()
+        torch.cuda.synchronize()
+        replay_s = time.perf_counter() - t0
+        if eager_s < self.small_graph_host_factor * replay_s:
+            del self._small_graphs[(bucket, limit)]
+            seen[3] = 0.0
+            return False
+        seen[0], seen[1], seen[3] = max(seen[0], self.small_graph_after), eager_s, 1e-6
+        return True
 
     @staticmethod
     def _step_shape(entries, native: bool) -> tuple:

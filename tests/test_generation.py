@@ -107,9 +107,9 @@ def test_warm_up_captures_every_decode_graph_and_changes_no_token(tmp_path, dtyp
     cb.write_model_folder(folder, cb.config_from_dict(cfgd), seed=5, scheme=cb.InitScheme(*tc.INIT_B))
     eng = cb.Engine(folder, dtype=dtype, page_size=8, max_tokens=2700, max_num_seqs=3, max_batched_tokens=512)
     free = eng.pool.manager.free_pages(0)
-    n = eng.warm_up()
+    n = eng.warm_up(small_steps=False)
     assert n == len(eng.runner._graphs) == 3 * 3         # buckets 1, 2, 3 (the most requests) x classes 256, 1024, 1300
-    assert eng.warm_up() == 0
+    assert eng.warm_up(small_steps=False) == 0
     assert eng.pool.manager.free_pages(0) == free and eng.pool.manager.check() == "" and eng.scheduler.idle()
     replays = eng.runner.graph_replays
     prompts = prompts_for(cfgd, [250, 1015, 10], seed=9)
@@ -158,6 +158,45 @@ def test_steps_launched_ahead_give_the_tokens_of_steps_in_turn(folder_b, dtype, 
     want, e0 = run(False, none, num_pages=12)
     got, e1 = run(True, none, num_pages=12)
     assert got == want == base and e0.scheduler.preemptions() > 0 and e1.scheduler.preemptions() > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_small_steps_with_prompt_portions_replay_a_graph(folder_a, folder_b, which, dtype):
+    """Small steps that hold prompt portions are captured per size (rows rounded up to a power of two, laid out for
+    all request slots, every segment through the kernels of the longer ones): while serving, once a size has come
+    a few times and a timed run has shown the device waiting for the host (here: from the third time on); or ahead
+    of serving by ``warm_up``, which keeps a graph if its replay is faster than the launches.  Many short requests
+    through few slots: the same tokens as without such graphs, and the plain implementation's."""
+    import cbis_b200 as cb
+    folder, cfg, page = (folder_a, tc.TINY_A, tc.PAGE_A) if which == "a" else (folder_b, tc.TINY_B, tc.PAGE_B)
+    g = torch.Generator().manual_seed(77)
+    lens = [int(n) for n in torch.randint(1, 15, (40,), generator=g)]
+    prompts = prompts_for(cfg, lens, 12)
+    news = [int(n) for n in torch.randint(2, 9, (40,), generator=g)]
+
+    def run(on, warm=False):
+        eng = cb.Engine(folder, dtype=dtype, page_size=page, num_pages=64, max_num_seqs=4, max_batched_tokens=64,
+                        prefill_chunk=16)
+        eng.runner.small_step_graphs = on
+        eng.runner.small_graph_after = 3
+        kept = eng.warm_up() if warm else 0
+        outs = eng.generate(prompts, [cb.SamplingParams(max_new_tokens=n) for n in news])
+        assert eng.pool.manager.check() == "" and eng.pool.manager.free_pages(0) == 64
+        return outs, eng, kept
+
+    base, e0, _ = run(False)
+    assert e0.runner.small_captures == 0
+    got, e1, _ = run(True)
+    assert e1.runner.small_captures >= 1 and e1.runner.small_replays >= 5
+    check_against_plain(folder, prompts, got, 0.0, 0, 0, exact=dtype == "float32")
+    if dtype == "float32":
+        assert got == base
+    warmed, e2, kept = run(True, warm=True)
+    sizes = {k[0] for k in e2.runner._small_graphs}
+    assert sizes == {16, 32, 64} and kept >= len(e2.runner._graphs) + len(sizes)      # 64: the most tokens of a step
+    assert e2.runner.small_replays > e1.runner.small_replays
+    assert warmed == got
 
 
 def test_first_tokens_of_a_sequence(tiny):
