@@ -383,20 +383,23 @@ class ModelRunner:
         seen = self._small_seen.setdefault(bucket, [0, 0.0, None, None])
         if seen[3] == 0.0:
             return False
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        self.model.forward(self.build_context(entries))
-        torch.cuda.synchronize()
-        eager_s = time.perf_counter() - t0
+        for _ in range(2):                  # the second run is the one that counts: the first pays for what is set up once
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            self.model.forward(self.build_context(entries))
+            torch.cuda.synchronize()
+            eager_s = time.perf_counter() - t0
         graph, logits = self._capture_small(entries, bucket, limit)
-        self._pack(entries, bucket, False, False, self.max_seqs)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        graph.replay()
-        torch.cuda.synchronize()
-        replay_s = time.perf_counter() - t0
+        for _ in range(2):
+            self._pack(entries, bucket, False, False, self.max_seqs)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            graph.replay()
+            torch.cuda.synchronize()
+            replay_s = time.perf_counter() - t0
         if eager_s < self.small_graph_host_factor * replay_s:
-            del self._small_graphs[(bucket, limit)]
+            for key in [k for k in self._small_graphs if k[0] == bucket]:      # the size is served launch by launch
+                del self._small_graphs[key]
             seen[3] = 0.0
             return False
         seen[0], seen[1], seen[3] = max(seen[0], self.small_graph_after), eager_s, 1e-6
