@@ -1,5 +1,5 @@
 """The layer sizes of the benchmark configurations (width 2048, 16 heads of 128, inner 8192, vocabulary
-50257; and the GPT-2 XL sizes) with two layers (GPU): here the kernels for head sizes 128 and 64 run inside
+50257; the GPT-2 XL sizes; and the 6.7B sizes, width 4096 and inner 16384) with two layers or one (GPU): here the kernels for head sizes 128 and 64 run inside
 the engine - the tiled prefill attention, the split-KV decode attention, the few-rows product, the TMA +
 tcgen05 products.  The 32-bit path is compared with the plain implementation once (its weights are drawn
 on the CPU so that the plain side can draw them again); every way of cutting a request in bfloat16 must
@@ -21,10 +21,15 @@ XL = dict(architectures=["GPT2LMHeadModel"], n_layer=2, n_embd=1600, n_head=25, 
           n_positions=1024, activation_function="gelu_new", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
 
 
-@pytest.fixture(scope="module", params=["1.3b", "xl"])
+# Cerebras-GPT-6.7B layer sizes, one layer: K = 4096 and 16384, 32 heads of 128
+WIDE = dict(architectures=["GPT2LMHeadModel"], n_layer=1, n_embd=4096, n_head=32, n_inner=16384, vocab_size=50257,
+            n_positions=2048, activation_function="gelu", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+
+
+@pytest.fixture(scope="module", params=["1.3b", "xl", "6.7b"])
 def engines(request):
     import cbis_b200 as cb
-    cfg = BIG if request.param == "1.3b" else XL
+    cfg = {"1.3b": BIG, "xl": XL, "6.7b": WIDE}[request.param]
     opts = dict(page_size=16, num_pages=80, max_num_seqs=4, max_batched_tokens=1024)
     # both engines hold the same bfloat16 values, drawn by the CPU's generator: the plain side draws them again
     e32 = cb.Engine.from_random(cfg, seed=3, dtype="float32", weight_dtype=torch.bfloat16, draw_on="cpu", **opts)
