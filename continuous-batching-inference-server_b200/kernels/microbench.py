@@ -90,6 +90,7 @@ def main():
     ap.add_argument("--splits", type=int, default=0, help="0: the engine's own choice")
     ap.add_argument("--layers", type=int, default=24, help="distinct weight/cache buffers per timed call")
     ap.add_argument("--act", default="gelu_erf", choices=["none", "gelu_erf", "gelu_tanh"], help="gemm_tc: the fused activation")
+    ap.add_argument("--accumulate", action="store_true", help="gemm_tc: 32-bit result added into the output (TMA reduction)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--reps", type=int, default=20)
     a = ap.parse_args()
@@ -125,14 +126,20 @@ def main():
         W = [torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(min(L, 4))]
         bias = torch.randn(a.n, device=dev)
         out = torch.empty(M, a.n, device=dev, dtype=torch.bfloat16)
+        if a.accumulate:         # the result added into 32-bit rows (attention output, feed-forward output of a prompt)
+            out = torch.zeros(M, a.n, device=dev)
+            a.act = "none"
 
         def fn():
             for w in W:
-                ops.gemm_tcgen05(x, w, bias, a.act, out)
+                ops.gemm_tcgen05(x, w, bias, a.act, out, accumulate=a.accumulate)
 
         def lib():
             for w in W:
-                torch.mm(x, w.t(), out=out)
+                if a.accumulate:
+                    torch.mm(x, w.t(), out_dtype=torch.float32)
+                else:
+                    torch.mm(x, w.t(), out=out)
         fl = 2.0 * M * a.n * a.k
         t = timed(fn, not a.no_graph, a.reps) / len(W)
         tl = timed(lib, not a.no_graph, a.reps) / len(W)
