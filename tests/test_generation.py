@@ -199,6 +199,44 @@ def test_small_steps_with_prompt_portions_replay_a_graph(folder_a, folder_b, whi
     assert warmed == got
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_everything_at_once_gives_the_plain_tokens(folder_b, seed):
+    """Sixty requests of random lengths, some greedy and some with a temperature, some with an end-of-sequence
+    token that they do produce, arriving a few at a time while others run, through four slots and so few pages that
+    requests are preempted; with steps launched ahead, small steps replaying graphs and freed pages filled with NaN.
+    32-bit path: every request's tokens are the plain implementation's (cut at the end-of-sequence token)."""
+    import random
+    import cbis_b200 as cb
+    rng = random.Random(seed)
+    cfg, w = plain_gpt.read_model_folder(folder_b, torch.float64)
+    eng = cb.Engine(folder_b, dtype="float32", page_size=tc.PAGE_B, num_pages=14, max_num_seqs=4, max_batched_tokens=40,
+                    prefill_chunk=12, poison_freed_pages=True)
+    eng.runner.small_graph_after = 2
+    work = []
+    for i in range(60):
+        prompt = [rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(1, 30))]
+        n = rng.randint(1, 20)
+        temp = rng.choice([0.0, 0.0, 0.7, 1.3])
+        want = plain_gpt.generate(cfg, w, prompt, n, temp, 11, i)
+        eos = None
+        if len(want) > 2 and rng.random() < 0.4:
+            eos = want[rng.randrange(1, len(want))]
+            want = want[:want.index(eos) + 1]
+        work.append((prompt, cb.SamplingParams(max_new_tokens=n, temperature=temp, seed=11, eos_token_id=eos), want))
+    got, nxt = {}, 0
+    while nxt < len(work) or eng.has_unfinished():
+        for _ in range(rng.randint(0, 3)):
+            if nxt < len(work):
+                assert eng.add_request(work[nxt][0], work[nxt][1]) == nxt
+                nxt += 1
+        for o in eng.step():
+            got[o.request_id] = o.tokens
+    assert eng._in_flight is None and eng.pool.manager.check() == "" and eng.pool.manager.free_pages(0) == 14
+    for i, (_, _, want) in enumerate(work):
+        assert got[i] == want, f"request {i}"
+    assert eng.steps_ahead > 3 and eng.scheduler.preemptions() > 0 and eng.runner.small_replays > 0 and eng.pages_poisoned > 0
+
+
 def test_first_tokens_of_a_sequence(tiny):
     import cbis_b200 as cb
     folder, cfg, page = tiny
