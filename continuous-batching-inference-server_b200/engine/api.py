@@ -126,6 +126,12 @@ class Engine:
     def has_unfinished(self) -> bool:
         return not self.scheduler.idle()
 
+    def abort(self, request_id: int) -> bool:
+        """Drops a request wherever it is (waiting or running); its pages go back at once.  If a step launched ahead
+        holds a row of it, that row is computed for nothing and passed over.  False if there is no such request."""
+        self._forget(request_id)
+        return bool(self.scheduler.abort(int(request_id)))
+
     @torch.no_grad()
     def step(self) -> List[RequestOutput]:
         """One engine step: plan, run, sample, update.  Returns the requests that finished.

@@ -141,8 +141,10 @@ class ModelRunner:
         self._small_seen: Dict[tuple, list] = {}
         self._small_pending = None
         self.small_captures = self.small_replays = 0
-        # padding segments carry state slot 0: only for models whose mixers keep no state of their own
-        self._small_ok = all(layer.mixer.state_need() is None for layer in model.layers)
+        # only for models whose mixers are attention over the pages through this package's kernels (they take empty
+        # segments and rows that belong to none) and keep no state of their own (a padding segment carries state slot 0)
+        self._small_ok = all(isinstance(layer.mixer, AttentionLike) and layer.mixer.state_need() is None
+                             for layer in model.layers)
         worst = heads = 0
         for layer in model.layers:
             m = layer.mixer

@@ -351,6 +351,27 @@ def test_a_refused_prompt_leaves_nothing_of_the_call_behind(folder_a):
     assert len(out) == 1 and len(out[0]) == 4 and eng.pool.manager.free_pages(0) == 8
 
 
+def test_abort_while_a_step_is_on_its_way(folder_a):
+    """A request dropped in the middle of decoding, while the step launched ahead holds a row of it: the others
+    end with the tokens they would have had anyway, the pages are all back."""
+    import cbis_b200 as cb
+    prompts = prompts_for(tc.TINY_A, [6, 11, 4], 3)
+    eng = cb.Engine(folder_a, dtype="float32", page_size=tc.PAGE_A, num_pages=16, max_num_seqs=3, max_batched_tokens=64)
+    want = eng.generate(prompts, cb.SamplingParams(max_new_tokens=12))
+    ids = [eng.add_request(p, cb.SamplingParams(max_new_tokens=12)) for p in prompts]
+    got = {}
+    for _ in range(5):
+        for o in eng.step():
+            got[o.request_id] = o.tokens
+    assert eng._in_flight is not None
+    assert eng.abort(ids[1]) and not eng.abort(ids[1])
+    while eng.has_unfinished():
+        for o in eng.step():
+            got[o.request_id] = o.tokens
+    assert got == {ids[0]: want[0], ids[2]: want[2]}
+    assert eng._in_flight is None and eng.pool.manager.check() == "" and eng.pool.manager.free_pages(0) == 16
+
+
 def test_eos_stops_a_request(folder_a):
     import cbis_b200 as cb
     eng = cb.Engine(folder_a, dtype="float32", page_size=16, num_pages=8, max_num_seqs=2, max_batched_tokens=32)
