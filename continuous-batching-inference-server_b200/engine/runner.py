@@ -136,7 +136,8 @@ class ModelRunner:
         self.small_step_graphs = os.environ.get("CBIS_SMALL_STEP_GRAPHS", "1") != "0"
         self.small_step_rows = min(256, self.max_tokens)
         self.small_graph_after = 8
-        self.small_graph_host_factor = 1.5      # captured when issuing a step costs the host this many times its device time
+        self.small_graph_host_factor = 1.5      # warm-up keeps a graph whose replay is this many times faster than the launches
+        self.small_graph_span_factor = 1.15     # while serving: the device counts as starved if a step's span on it is no longer than this times the host's time to issue it
         self._small_graphs: Dict[tuple, tuple] = {}
         self._small_seen: Dict[tuple, list] = {}
         self._small_pending = None
@@ -346,7 +347,7 @@ class ModelRunner:
                 seen[3] = max(seen[2][0].elapsed_time(seen[2][1]), 1e-6)
             elif seen[0] >= 2 and seen[2] is None:
                 self._small_pending = seen             # the caller times this run
-        starved = seen[3] is not None and seen[3] <= 1.15 * seen[1] * 1e3
+        starved = seen[3] is not None and seen[3] <= self.small_graph_span_factor * seen[1] * 1e3
         have_some = any(k[0] == bucket for k in self._small_graphs)
         if not have_some and (seen[0] < self.small_graph_after or not starved):
             return None

@@ -180,6 +180,8 @@ def test_small_steps_with_prompt_portions_replay_a_graph(folder_a, folder_b, whi
                         prefill_chunk=16)
         eng.runner.small_step_graphs = on
         eng.runner.small_graph_after = 3
+        eng.runner.small_graph_span_factor = 100.0       # the mechanism is under test here, not the measurement
+        eng.runner.small_graph_host_factor = 0.0         # (warm_up keeps every graph it captures)
         kept = eng.warm_up() if warm else 0
         outs = eng.generate(prompts, [cb.SamplingParams(max_new_tokens=n) for n in news])
         assert eng.pool.manager.check() == "" and eng.pool.manager.free_pages(0) == 64
@@ -212,6 +214,7 @@ def test_everything_at_once_gives_the_plain_tokens(folder_b, seed):
     eng = cb.Engine(folder_b, dtype="float32", page_size=tc.PAGE_B, num_pages=14, max_num_seqs=4, max_batched_tokens=40,
                     prefill_chunk=12, poison_freed_pages=True)
     eng.runner.small_graph_after = 2
+    eng.runner.small_graph_span_factor = 100.0
     work = []
     for i in range(60):
         prompt = [rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(1, 30))]
